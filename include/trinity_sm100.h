@@ -1,0 +1,196 @@
+/*
+ * trinity_sm100.h -- C ABI of the sm_100a (B200) kernel library behind Trinity Lowering's
+ * native CUDA provider.
+ *
+ * Every entry point takes plain device pointers, extents and a CUDA stream handle (void*,
+ * a cudaStream_t / CUstream).  No PyTorch, C++ or Rust type crosses this boundary.  All
+ * launches are asynchronous on the given stream, allocate nothing and never synchronise,
+ * so they may be issued during CUDA-Graph stream capture.
+ *
+ * Return value: 0 on success, otherwise one of the TRINITY_SM100_E_* codes (negative).
+ * trinity_sm100_last_error() returns a thread-local, NUL-terminated explanation of the
+ * most recent non-zero return on the calling thread.
+ *
+ * Each declaration cites the interface of the reference project (youngchan2/Trinity-BE,
+ * paths relative to that project) whose role it takes.
+ */
+#ifndef TRINITY_SM100_H
+#define TRINITY_SM100_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRINITY_SM100_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define TRINITY_SM100_API __attribute__((visibility("default")))
+#else
+#define TRINITY_SM100_API
+#endif
+
+enum trinity_sm100_error {
+  TRINITY_SM100_OK = 0,
+  TRINITY_SM100_E_INVALID = -1,     /* null pointer, bad extent, misaligned pointer or stride */
+  TRINITY_SM100_E_UNSUPPORTED = -2, /* shape or mode the kernels do not implement            */
+  TRINITY_SM100_E_CUDA = -3,        /* a CUDA runtime or driver call failed                  */
+  TRINITY_SM100_E_DEVICE = -4,      /* current device is not compute capability 10.x         */
+  TRINITY_SM100_E_TIMEOUT = -5      /* a bounded in-kernel wait gave up (see device_status)  */
+};
+
+enum trinity_sm100_dtype { TRINITY_SM100_BF16 = 0, TRINITY_SM100_FP32 = 1 };
+
+/* How the epilogue's side operand is broadcast against the [M,N] accumulator. */
+enum trinity_sm100_bias_mode {
+  TRINITY_SM100_BIAS_NONE = 0,
+  TRINITY_SM100_BIAS_COL_VECTOR = 1, /* bias[N], same for every row:   (bcast (load bias) 0) */
+  TRINITY_SM100_BIAS_ROW_VECTOR = 2, /* bias[M], same for every column:(bcast (load bias) 1) */
+  TRINITY_SM100_BIAS_MATRIX = 3      /* bias[M,N] with leading dimension ld_bias             */
+};
+
+enum trinity_sm100_activation {
+  TRINITY_SM100_ACT_NONE = 0,
+  TRINITY_SM100_ACT_RELU = 1,     /* max(x, 0), NaN propagates, -0 kept as the reference does */
+  TRINITY_SM100_ACT_SILU = 2,     /* x * sigmoid(x)                                           */
+  TRINITY_SM100_ACT_SILU_GATE = 3 /* (A@B) * ((A@B2) * sigmoid(A@B2)): two accumulators       */
+};
+
+/*
+ * GEMM with fused epilogue:  out = act(A @ B + bias)   (BF16 x BF16 -> FP32 accumulate).
+ *
+ *   a   [m,k]  bf16 row-major, leading dimension lda (elements, multiple of 8)
+ *   b   [k,n]  bf16 row-major, leading dimension ldb (elements, multiple of 8)
+ *   b2  [k,n]  second right operand, only for TRINITY_SM100_ACT_SILU_GATE (same ldb)
+ *   out [m,n]  bf16 or fp32 row-major, leading dimension ldo (bytes per row multiple of 16)
+ *
+ * All base pointers must be 16-byte aligned.  m, n, k need not be multiples of the tile:
+ * loads past an edge read zero and stores past an edge are dropped.
+ *
+ * Replaces the Hopper WGMMA tile kernel plus its register "follower" epilogue
+ * (src/emit/provider/cute/operator/gemm/hopper/mod.rs:32-157,
+ *  src/emit/provider/cute/operator/pointwise/render.rs:304-370) as launched by the generated
+ * host code (src/emit/native/cuda/templates/host.cu.j2:52-76).
+ */
+typedef struct trinity_sm100_gemm {
+  const void* a;
+  const void* b;
+  const void* b2;
+  const void* bias;
+  void* out;
+  int64_t m, n, k;
+  int64_t lda, ldb, ldo, ld_bias;
+  int32_t bias_mode;  /* trinity_sm100_bias_mode  */
+  int32_t activation; /* trinity_sm100_activation */
+  int32_t out_dtype;  /* trinity_sm100_dtype      */
+  int32_t reserved;
+} trinity_sm100_gemm;
+
+TRINITY_SM100_API int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* stream);
+
+/*
+ * RMSNorm over the last axis:
+ *   y[r,c] = x[r,c] / sqrt(sum_c(x[r,c]^2) / cols + eps) * gain[c]      (FP32 math, BF16 I/O)
+ * gain may be NULL (no gain) and eps may be 0, which keeps the reference's 0/0 -> NaN for an
+ * all-zero row.  x and y are [rows, cols] row-major and contiguous; cols % 8 == 0.
+ *
+ * Replaces the three-launch square / row-sum / divide chain built from
+ * src/emit/provider/cute/operator/reduce_sum/mod.rs:26-96 and
+ * src/emit/provider/cute/operator/pointwise/mod.rs:37-134 (plan shape:
+ * python/tests/tensor_ops.py:115-123) with one pass over the row.
+ */
+TRINITY_SM100_API int trinity_sm100_rmsnorm_bf16(const void* x, const void* gain, void* y, int64_t rows,
+                               int64_t cols, float eps, void* stream);
+
+/*
+ * Numerically stable row softmax over the last axis (FP32 math, BF16 I/O):
+ *   y[r,c] = exp(x[r,c] - max_c x[r,:]) / sum_c exp(x[r,c] - max_c x[r,:])
+ * The equation form is the one the reference recognises in
+ * src/emit/provider/quack/recognition/normalization.rs:138-157.
+ */
+TRINITY_SM100_API int trinity_sm100_softmax_bf16(const void* x, void* y, int64_t rows, int64_t cols, void* stream);
+
+/*
+ * Batched multi-head latent attention decode (one query token per sequence) over a
+ * compressed KV cache, split over the KV axis.
+ *
+ *   q      [batch, heads, d_qk]      bf16   (d_qk = d_v + d_rope; absorbed latent then rope)
+ *   cache  [batch, seq, d_qk]        bf16   (values are cache[..., :d_v])
+ *   out    [batch, heads, d_v]       bf16
+ *   scratch: trinity_sm100_mla_scratch_bytes(...) bytes of device memory, 256-byte aligned,
+ *            holding the per-split partial numerators, running maxima and denominators.
+ *
+ *   out[b,h,:] = softmax_s(scale * q[b,h,:] . cache[b,s,:]) @ cache[b,:,:d_v]
+ *
+ * Supported geometry: heads == 128, d_v == 512, d_qk == 576, seq % 32 == 0, seq >= 32.
+ * The math follows the reference's batched-MLA fixture
+ * (tests/fixtures/batched_mla/batched_mla_postprocessed_stage14.txt:21-23,62-68,210-213;
+ *  split/combine structure of ...stage20.txt:62-76,197-206) with the softmax scale and
+ *  max-subtraction the decode configuration adds.
+ */
+typedef struct trinity_sm100_mla {
+  const void* q;
+  const void* cache;
+  void* out;
+  void* scratch;
+  size_t scratch_bytes;
+  int32_t batch, heads, seq, d_qk, d_v;
+  int32_t kv_splits; /* 0 = choose from the SM count */
+  float scale;
+  int32_t reserved;
+} trinity_sm100_mla;
+
+TRINITY_SM100_API size_t trinity_sm100_mla_scratch_bytes(int32_t batch, int32_t heads, int32_t d_v,
+                                       int32_t kv_splits);
+TRINITY_SM100_API int trinity_sm100_mla_default_splits(int32_t batch, int32_t seq);
+TRINITY_SM100_API int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void* stream);
+
+/*
+ * Sum all-reduce of a BF16 [rows, cols] matrix across `world` GPUs of one NVLink domain,
+ * through peer-mapped memory (no NVSHMEM, no NCCL on the data path).
+ *
+ *   peers[r]  this buffer on rank r, mapped into the calling process (peers[rank] is local)
+ *   flags[r]  rank r's flag pad (uint32, at least trinity_sm100_allreduce_flag_words() words,
+ *             zeroed once before first use)
+ *   epoch     strictly increasing per call on every rank (flags are never reset)
+ *
+ * Two-shot: rank r reduces row block r of every peer into its own buffer in FP32, then every
+ * rank pulls the reduced blocks.  All waits are bounded; a wait that gives up sets the device
+ * status word and the kernel returns.
+ *
+ * Takes the place of the NVSHMEM symmetric-heap collectives the reference declares
+ * (src/native/world.cpp:122-177, src/emit/implementation/definitions/nvls.rs:59-70,
+ *  src/emit/implementation/definitions/peer.rs:9-11); the reference has no all-reduce.
+ */
+typedef struct trinity_sm100_allreduce {
+  void* const* peers;     /* host array of `world` device pointers */
+  void* const* flags;     /* host array of `world` device pointers */
+  int64_t rows, cols;     /* cols % 8 == 0 */
+  int32_t world, rank;
+  uint32_t epoch;
+  int32_t reserved;
+} trinity_sm100_allreduce;
+
+TRINITY_SM100_API size_t trinity_sm100_allreduce_flag_words(void);
+TRINITY_SM100_API int trinity_sm100_allreduce_bf16(const trinity_sm100_allreduce* args, void* stream);
+
+/*
+ * Device status word: 0 while every bounded in-kernel wait has completed; otherwise the code
+ * of the first wait that gave up (site id in the low 16 bits).  Reading synchronises the
+ * device.  `clear` != 0 resets it afterwards.
+ * Counterpart of the generated trinity_status() (src/emit/native/cuda/templates/host.cu.j2:78-83).
+ */
+TRINITY_SM100_API int trinity_sm100_device_status(uint32_t* status, int clear);
+
+/* Library identity and diagnostics. */
+TRINITY_SM100_API int trinity_sm100_abi_version(void);
+TRINITY_SM100_API const char* trinity_sm100_last_error(void);
+/* Number of kernels this library has launched in the calling process (all threads). */
+TRINITY_SM100_API uint64_t trinity_sm100_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRINITY_SM100_H */

@@ -1,0 +1,135 @@
+"""GEMM + fused epilogue through the C ABI versus the CPU oracle (B200 only)."""
+import pytest
+import torch
+
+from oracle import workloads as wl
+from parity import assert_close_bf16
+
+pytestmark = pytest.mark.gpu
+
+kernels = None
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _library():
+    global kernels
+    from trinity_lowering import kernels as k
+    k.library()
+    kernels = k
+    yield
+    assert k.device_status() == 0
+
+
+def run_gemm(a, w, bias=None, **kw):
+    dev = torch.device("cuda:0")
+    out = kernels.gemm(a.to(dev), w.to(dev), bias=None if bias is None else bias.to(dev), **kw)
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+# The reference's exact-arithmetic cases (hopper/tests.rs:179-225 shapes: K widths 64..256,
+# a clipped M tile) plus multi-tile and ragged shapes.
+@pytest.mark.parametrize("m,n,k", [
+    (128, 128, 64), (128, 128, 128), (128, 128, 192), (128, 128, 256), (1, 128, 64),
+    (133, 128, 192), (256, 256, 192), (384, 520, 328), (1000, 264, 72),
+])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_dyadic_inputs_are_bit_exact(m, n, k, out_dtype):
+    a, b = wl.dyadic_gemm_inputs(m, n, k)
+    exact = (a.double() @ b.double()).float().to(out_dtype)
+    for _ in range(3):  # repeated launches must not leak pipeline state
+        out = run_gemm(a, b, out_dtype=out_dtype)
+        assert torch.equal(out, exact)
+
+
+def test_output_outside_the_matrix_is_untouched():
+    """Sentinel fill (reference.cu:16,39): only [m,n] of a wider allocation may change."""
+    dev = torch.device("cuda:0")
+    a, b = wl.dyadic_gemm_inputs(200, 136, 128)
+    backing = torch.full((256, 192), -123.0, dtype=torch.bfloat16, device=dev)
+    out = backing[:200, :136]
+    kernels.gemm(a.to(dev), b.to(dev), out=out)
+    torch.cuda.synchronize()
+    host = backing.cpu()
+    assert torch.equal(host[:200, :136], (a.double() @ b.double()).float().bfloat16())
+    assert (host[200:] == -123.0).all() and (host[:, 136:] == -123.0).all()
+
+
+@pytest.mark.parametrize("name", ["gemm_bias", "gemm_bias_relu", "gemm_matrix_bias", "gemm_silu"])
+def test_golden_cases(golden, name):
+    case = golden[name]
+    a, w, bias = wl.gemm_inputs(case["m"], case["n"], case["k"], case["seed"], case["distribution"])
+    mode = {"col": kernels.BIAS_COL_VECTOR, "matrix": kernels.BIAS_MATRIX}[case["bias_mode"]]
+    if case["bias_mode"] == "matrix":
+        bias = wl._normal((case["m"], case["n"]), 0.5, wl._gen(case["seed"] + 100))
+    act = {None: kernels.ACT_NONE, "relu": kernels.ACT_RELU, "silu": kernels.ACT_SILU}[
+        case["activation"]]
+    out = run_gemm(a, w, bias, bias_mode=mode, activation=act)
+    expected = case["expected"].view(torch.bfloat16)
+    assert_close_bf16(out, expected, max_ulp=1)
+
+
+def test_gated_golden_case(golden):
+    case = golden["gated"]
+    a, wg, wu, _ = wl.mlp_inputs(case["m"], case["d_model"], case["d_ff"], case["seed"])
+    dev = torch.device("cuda:0")
+    out = kernels.gemm(a.to(dev), wu.to(dev), b2=wg.to(dev), activation=kernels.ACT_SILU_GATE)
+    torch.cuda.synchronize()
+    assert_close_bf16(out.cpu(), case["expected"].view(torch.bfloat16), max_ulp=1)
+
+
+def test_streamed_config_1024_uniform():
+    """A[1024,1024] @ B[1024,1024] + bias[1024], U(-1,1): |y| reaches ~50, so the bound on the
+    raw difference is the reference's atol=0.125, rtol=0.02 (python/tests/test_gpu.py:55)."""
+    a, w, bias = wl.gemm_inputs(1024, 1024, 1024, 1234, "uniform")
+    out = run_gemm(a, w, bias, bias_mode=kernels.BIAS_COL_VECTOR)
+    expected = wl.gemm_oracle(a, w, bias)
+    assert_close_bf16(out, expected, max_ulp=1)
+    torch.testing.assert_close(out.float(), expected.float(), atol=0.125, rtol=0.02)
+
+
+@pytest.mark.parametrize("m,n,k", [(2048, 2304, 1024), (4096, 4096, 512)])
+def test_bias_relu_many_tiles(m, n, k):
+    a, w, bias = wl.gemm_inputs(m, n, k, 1235, "normal")
+    out = run_gemm(a, w, bias, bias_mode=kernels.BIAS_COL_VECTOR, activation=kernels.ACT_RELU)
+    rows = torch.arange(0, m, 37)
+    expected = wl.gemm_oracle(a, w, bias, "relu", rows=rows)
+    assert_close_bf16(out[rows], expected, max_ulp=1, max_abs=2e-2)
+    # linearity in the bias where ReLU is inactive is checked through a second launch
+    out2 = run_gemm(a, w, None)
+    both = (out2.float() + bias.float()).clamp_min(0).bfloat16()
+    assert_close_bf16(out, both, max_ulp=2, ulp_outlier_fraction=1e-3)
+
+
+def test_row_vector_bias_and_fp32_output():
+    a, w, _ = wl.gemm_inputs(300, 200, 136, 77, "normal")
+    bias = wl._normal((300,), 0.5, wl._gen(78))
+    out = run_gemm(a, w, bias, bias_mode=kernels.BIAS_ROW_VECTOR, out_dtype=torch.float32)
+    expected = wl.gemm_oracle(a, w, bias, None, "row", out_dtype="fp32")
+    torch.testing.assert_close(out, expected, rtol=1e-4, atol=1e-4)
+
+
+def test_relu_special_values_in_epilogue():
+    """x < 0 ? 0 : x keeps NaN, +inf and the sign of zero (pointwise/special.rs:3-6)."""
+    dev = torch.device("cuda:0")
+    a = torch.zeros(128, 64, dtype=torch.bfloat16)
+    a[:, 0] = 1.0
+    w = torch.zeros(64, 128, dtype=torch.bfloat16)
+    special = torch.tensor([-float("inf"), -2.0, -0.0, 0.0, 2.0, float("inf"), float("nan"), 1e-8])
+    bias = special.repeat(16).bfloat16()
+    out = run_gemm(a, w, bias, bias_mode=kernels.BIAS_COL_VECTOR, activation=kernels.ACT_RELU)
+    expected = torch.where(bias.float() < 0, torch.zeros(()), bias.float()).bfloat16()
+    row = out[5]
+    assert torch.equal(torch.isnan(row.float()), torch.isnan(expected.float()))
+    ok = ~torch.isnan(expected.float())
+    assert torch.equal(row[ok], expected[ok])
+
+
+def test_invalid_arguments_are_rejected():
+    dev = torch.device("cuda:0")
+    a = torch.zeros(64, 60, dtype=torch.bfloat16, device=dev)  # K pitch not a multiple of 8
+    b = torch.zeros(60, 64, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm(a, b)
+    with pytest.raises(ValueError):
+        kernels.gemm(a.float(), b)

@@ -1,0 +1,429 @@
+// BF16 GEMM with fused epilogue on the 5th-generation tensor cores.
+//
+//   out[M,N] = act(A[M,K] @ B[K,N] + bias)            FP32 accumulation in TMEM
+//   out[M,N] = (A@B) * silu(A@B2)                     gated form, two accumulators per tile
+//
+// One persistent CTA per SM, 192 threads, warp-specialised:
+//   warp 0    TMA producer: A tile [128 x 64] (K-major) and B tile [64 x BN] (N-major, i.e. the
+//             row-major [K,N] weight as it lies in memory) into a multi-stage 128B-swizzled ring
+//   warp 1    MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) four times
+//             per stage and commits the stage's "empty" barrier; accumulators are double
+//             buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps tile i+1
+//   warps 2-5 epilogue: tcgen05.ld 32 columns at a time, bias / activation in FP32, one
+//             rounding to the output type, 128B-swizzled staging and a TMA store per warp
+//
+// Algorithmic traffic per launch: (M*K + K*N [+K*N]) * 2 + bias + M*N*out_bytes.
+#include "host_common.h"
+#include "sm100_ptx.cuh"
+
+namespace trinity_sm100 {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupM = 16;           // tile rasterisation: 16 row blocks share B columns in L2
+constexpr int kStageBytesA = kBM * kBK * 2;
+constexpr int kStoreBufBytes = 32 * 128;  // 32 rows x 128 B per epilogue warp
+constexpr int kStagingBytes = 4 * 2 * kStoreBufBytes;
+
+struct GemmParams {
+  const __nv_bfloat16* bias;
+  long long ld_bias;
+  int bias_mode;
+  int activation;
+  int m, n, k;
+  int tiles_m, tiles_n, num_tiles, num_kb;
+};
+
+template <int kBN>
+__host__ __device__ constexpr int stage_bytes() {
+  return kStageBytesA + kBK * kBN * 2;
+}
+template <int kBN, int kStages>
+__host__ __device__ constexpr int gemm_smem_bytes() {
+  return 1024 + kStages * stage_bytes<kBN>() + kStagingBytes + 256;
+}
+
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m_blk, int& n_blk) {
+  const int group_size = kGroupM * p.tiles_n;
+  const int group = tile / group_size;
+  const int first_m = group * kGroupM;
+  const int rows_in_group = min(kGroupM, p.tiles_m - first_m);
+  const int local = tile - group * group_size;
+  m_blk = first_m + local % rows_in_group;
+  n_blk = local / rows_in_group;
+}
+
+__device__ __forceinline__ float apply_activation(float x, int activation) {
+  if (activation == TRINITY_SM100_ACT_RELU) return x < 0.0f ? 0.0f : x;
+  if (activation == TRINITY_SM100_ACT_SILU) return x * (1.0f / (1.0f + __expf(-x)));
+  return x;
+}
+
+template <int kBN, int kStages, bool kGated, bool kOutF32>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                         const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_b2,
+                         const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
+  constexpr int kOutN = kGated ? kBN / 2 : kBN;      // output columns per tile
+  constexpr int kStage = stage_bytes<kBN>();
+  constexpr int kChunksB = kBN / 64;                 // 64-column TMA boxes per stage
+  constexpr uint32_t kTmemCols = 2 * kBN;            // double-buffered accumulator
+  constexpr uint32_t kIdesc = umma_idesc_bf16(kBM, kBN, 0, 1);
+  static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t staging_base = smem_base + kStages * kStage;
+  uint8_t* staging = smem + kStages * kStage;
+  const uint32_t bar_base = staging_base + kStagingBytes;
+  // barrier layout (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  volatile uint32_t* tmem_holder =
+      reinterpret_cast<volatile uint32_t*>(staging + kStagingBytes + 8 * (2 * kStages + 4));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    if (kGated) tma_prefetch_desc(&map_b2);
+    tma_prefetch_desc(&map_out);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(p, tile, m_blk, n_blk);
+        const int m0 = m_blk * kBM;
+        const int n0 = n_blk * kOutN;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1u;
+          if (!mbar_wait(empty_bar(s), phase ^ 1u, 0x101)) { ok = false; break; }
+          mbar_arrive_expect_tx(full_bar(s), kStage);
+          const uint32_t a_dst = smem_base + s * kStage;
+          const uint32_t b_dst = a_dst + kStageBytesA;
+          tma_load_2d(a_dst, &map_a, full_bar(s), kb * kBK, m0);
+#pragma unroll
+          for (int j = 0; j < kChunksB; ++j) {
+            if (kGated && j >= kChunksB / 2)
+              tma_load_2d(b_dst + j * 8192, &map_b2, full_bar(s), n0 + (j - kChunksB / 2) * 64,
+                          kb * kBK);
+            else
+              tma_load_2d(b_dst + j * 8192, &map_b, full_bar(s), n0 + j * 64, kb * kBK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1u;
+        const uint32_t acc_phase = (local_tile >> 1) & 1u;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, 0x201)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t phase = (it / kStages) & 1u;
+          if (!mbar_wait(full_bar(s), phase, 0x202)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + s * kStage;
+          const uint32_t b_addr = a_addr + kStageBytesA;
+#pragma unroll
+          for (int k4 = 0; k4 < kBK / 16; ++k4) {
+            // A: K-major, rows 128 B apart, 8-row groups 1024 B apart; 16 K elements = 32 B.
+            const uint64_t a_desc = umma_smem_desc(a_addr + k4 * 32, 16, 1024);
+            // B: N-major, 64-column chunks 8192 B apart, 8-row K groups 1024 B apart.
+            const uint64_t b_desc = umma_smem_desc(b_addr + k4 * 2048, 8192, 1024);
+            umma_bf16_ss(d_tmem, a_desc, b_desc, kIdesc, (kb | k4) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));
+        }
+        if (ok) umma_commit(tmem_full_bar(acc));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    uint8_t* my_staging = staging + quad * 2 * kStoreBufBytes;
+    const uint32_t my_staging_u32 = staging_base + quad * 2 * kStoreBufBytes;
+    constexpr int kSubPerStore = kOutF32 ? 1 : 2;       // 32-column sub-chunks per 128 B row
+    constexpr int kColsPerStore = 32 * kSubPerStore;
+    uint32_t local_tile = 0;
+    uint32_t store_buf = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      const int m0 = m_blk * kBM;
+      const int n0 = n_blk * kOutN;
+      const uint32_t acc = local_tile & 1u;
+      const uint32_t acc_phase = (local_tile >> 1) & 1u;
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, 0x301)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
+      float row_bias = 0.0f;
+      if (p.bias_mode == TRINITY_SM100_BIAS_ROW_VECTOR && row < p.m)
+        row_bias = __bfloat162float(p.bias[row]);
+
+      for (int c0 = 0; c0 < kOutN; c0 += kColsPerStore) {
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* buf = my_staging + store_buf * kStoreBufBytes;
+#pragma unroll
+        for (int sub = 0; sub < kSubPerStore; ++sub) {
+          const int col = c0 + sub * 32;
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_row + col, v);
+          float x[32];
+          if (kGated) {
+            uint32_t g[32];
+            tmem_ld_32x32b_x32(t_row + kOutN + col, g);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float gate = __uint_as_float(g[j]);
+              x[j] = __uint_as_float(v[j]) * (gate * (1.0f / (1.0f + __expf(-gate))));
+            }
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(v[j]);
+          }
+          const int gcol = n0 + col;
+          if (p.bias_mode == TRINITY_SM100_BIAS_COL_VECTOR) {
+            if (gcol + 32 <= p.n) {
+              const uint4* src = reinterpret_cast<const uint4*>(p.bias + gcol);
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) {
+                const uint4 b = __ldg(src + v4);
+                const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  x[v4 * 8 + e * 2] += bf16_lo(w[e]);
+                  x[v4 * 8 + e * 2 + 1] += bf16_hi(w[e]);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (gcol + j < p.n) x[j] += __bfloat162float(p.bias[gcol + j]);
+            }
+          } else if (p.bias_mode == TRINITY_SM100_BIAS_ROW_VECTOR) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] += row_bias;
+          } else if (p.bias_mode == TRINITY_SM100_BIAS_MATRIX) {
+            if (row < p.m) {
+              const __nv_bfloat16* brow = p.bias + static_cast<long long>(row) * p.ld_bias + gcol;
+              if (gcol + 32 <= p.n) {
+                const uint4* src = reinterpret_cast<const uint4*>(brow);
+#pragma unroll
+                for (int v4 = 0; v4 < 4; ++v4) {
+                  const uint4 b = __ldg(src + v4);
+                  const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    x[v4 * 8 + e * 2] += bf16_lo(w[e]);
+                    x[v4 * 8 + e * 2 + 1] += bf16_hi(w[e]);
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (gcol + j < p.n) x[j] += __bfloat162float(brow[j]);
+              }
+            }
+          }
+          if (!kGated && p.activation != TRINITY_SM100_ACT_NONE) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = apply_activation(x[j], p.activation);
+          }
+          // Staging row `lane` is 128 B = eight 16 B units; unit u lives at u ^ (lane & 7).
+          uint8_t* srow = buf + lane * 128;
+          if (kOutF32) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              uint4 o;
+              o.x = __float_as_uint(x[u * 4 + 0]);
+              o.y = __float_as_uint(x[u * 4 + 1]);
+              o.z = __float_as_uint(x[u * 4 + 2]);
+              o.w = __float_as_uint(x[u * 4 + 3]);
+              *reinterpret_cast<uint4*>(srow + ((u ^ (lane & 7)) << 4)) = o;
+            }
+          } else {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 o;
+              o.x = pack_bf16x2(x[u * 8 + 0], x[u * 8 + 1]);
+              o.y = pack_bf16x2(x[u * 8 + 2], x[u * 8 + 3]);
+              o.z = pack_bf16x2(x[u * 8 + 4], x[u * 8 + 5]);
+              o.w = pack_bf16x2(x[u * 8 + 6], x[u * 8 + 7]);
+              const int unit = sub * 4 + u;
+              *reinterpret_cast<uint4*>(srow + ((unit ^ (lane & 7)) << 4)) = o;
+            }
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (m0 + quad * 32 < p.m && n0 + c0 < p.n)
+            tma_store_2d(&map_out, my_staging_u32 + store_buf * kStoreBufBytes, n0 + c0,
+                         m0 + quad * 32);
+          tma_store_commit();
+        }
+        store_buf ^= 1u;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  // Common exit: every role leaves its loop (normally or after a wait gave up) and meets here.
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (g_device_status != 0) {
+      // A wait gave up somewhere: give copies still in flight time to land before the
+      // shared memory and TMEM of this CTA are released.
+      for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int kBN, int kStages, bool kGated, bool kOutF32>
+int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream) {
+  constexpr int kOutN = kGated ? kBN / 2 : kBN;
+  constexpr int kSmem = gemm_smem_bytes<kBN, kStages>();
+  static_assert(kSmem <= 232448, "exceeds the 227 KB shared-memory limit");
+  auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32>;
+  static bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (!configured[device & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess)
+      return fail(TRINITY_SM100_E_CUDA, "gemm: shared memory opt-in (%d B): %s", kSmem,
+                  cudaGetErrorString(e));
+    configured[device & 63] = true;
+  }
+  CUtensorMap map_a, map_b, map_b2, map_out;
+  int rc;
+  if ((rc = make_tensor_map_2d(&map_a, g.a, 2, g.k, g.m, g.lda * 2, kBK, kBM, true))) return rc;
+  if ((rc = make_tensor_map_2d(&map_b, g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK, true))) return rc;
+  if ((rc = make_tensor_map_2d(&map_b2, kGated ? g.b2 : g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK,
+                               true)))
+    return rc;
+  const int out_bytes = kOutF32 ? 4 : 2;
+  if ((rc = make_tensor_map_2d(&map_out, g.out, out_bytes, g.n, g.m, g.ldo * out_bytes,
+                               128 / out_bytes, 32, true)))
+    return rc;
+  GemmParams p;
+  p.bias = static_cast<const __nv_bfloat16*>(g.bias);
+  p.ld_bias = g.ld_bias;
+  p.bias_mode = g.bias_mode;
+  p.activation = g.activation;
+  p.m = int(g.m);
+  p.n = int(g.n);
+  p.k = int(g.k);
+  p.tiles_m = int((g.m + kBM - 1) / kBM);
+  p.tiles_n = int((g.n + kOutN - 1) / kOutN);
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.num_kb = int((g.k + kBK - 1) / kBK);
+  const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
+  kernel<<<grid, kGemmThreads, kSmem, stream>>>(map_a, map_b, map_b2, map_out, p);
+  count_launch();
+  return check_launch("gemm_bf16_tcgen05");
+}
+
+}  // namespace
+}  // namespace trinity_sm100
+
+using namespace trinity_sm100;
+
+extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* stream_handle) {
+  if (!args) return fail(TRINITY_SM100_E_INVALID, "gemm: null argument block");
+  const trinity_sm100_gemm& g = *args;
+  if (!g.a || !g.b || !g.out) return fail(TRINITY_SM100_E_INVALID, "gemm: null operand");
+  if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.m > INT32_MAX || g.n > INT32_MAX || g.k > INT32_MAX)
+    return fail(TRINITY_SM100_E_INVALID, "gemm: extents must be in [1, 2^31)");
+  const bool gated = g.activation == TRINITY_SM100_ACT_SILU_GATE;
+  if (gated && !g.b2) return fail(TRINITY_SM100_E_INVALID, "gemm: gated form needs b2");
+  if (g.activation < TRINITY_SM100_ACT_NONE || g.activation > TRINITY_SM100_ACT_SILU_GATE)
+    return fail(TRINITY_SM100_E_INVALID, "gemm: unknown activation %d", g.activation);
+  if (g.bias_mode < TRINITY_SM100_BIAS_NONE || g.bias_mode > TRINITY_SM100_BIAS_MATRIX)
+    return fail(TRINITY_SM100_E_INVALID, "gemm: unknown bias mode %d", g.bias_mode);
+  if (g.bias_mode != TRINITY_SM100_BIAS_NONE && !g.bias)
+    return fail(TRINITY_SM100_E_INVALID, "gemm: bias mode %d without a bias pointer", g.bias_mode);
+  if (gated && g.bias_mode != TRINITY_SM100_BIAS_NONE)
+    return fail(TRINITY_SM100_E_UNSUPPORTED, "gemm: the gated form takes no bias");
+  if (g.out_dtype != TRINITY_SM100_BF16 && g.out_dtype != TRINITY_SM100_FP32)
+    return fail(TRINITY_SM100_E_INVALID, "gemm: unknown output dtype %d", g.out_dtype);
+  if (g.lda < g.k || g.ldb < g.n || g.ldo < g.n)
+    return fail(TRINITY_SM100_E_INVALID, "gemm: leading dimension smaller than the row");
+  const int out_bytes = g.out_dtype == TRINITY_SM100_FP32 ? 4 : 2;
+  if (g.lda % 8 || g.ldb % 8 || (g.ldo * out_bytes) % 16)
+    return fail(TRINITY_SM100_E_INVALID,
+                "gemm: row pitches must be multiples of 16 bytes (lda %lld, ldb %lld, ldo %lld)",
+                (long long)g.lda, (long long)g.ldb, (long long)g.ldo);
+  if (!aligned16(g.a) || !aligned16(g.b) || !aligned16(g.out) || (gated && !aligned16(g.b2)))
+    return fail(TRINITY_SM100_E_INVALID, "gemm: operand pointers must be 16-byte aligned");
+  if (g.bias_mode == TRINITY_SM100_BIAS_COL_VECTOR && !aligned16(g.bias))
+    return fail(TRINITY_SM100_E_INVALID, "gemm: bias vector must be 16-byte aligned");
+  if (g.bias_mode == TRINITY_SM100_BIAS_MATRIX &&
+      (!aligned16(g.bias) || g.ld_bias % 8 || g.ld_bias < g.n))
+    return fail(TRINITY_SM100_E_INVALID, "gemm: bias matrix needs 16-byte aligned rows");
+  int sm_count = 0;
+  if (int rc = require_sm100(&sm_count)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  const bool f32 = g.out_dtype == TRINITY_SM100_FP32;
+  if (gated) {
+    return f32 ? launch_gemm<256, 4, true, true>(g, sm_count, stream)
+               : launch_gemm<256, 4, true, false>(g, sm_count, stream);
+  }
+  // Wide tiles once there are enough of them to fill the machine, narrow ones otherwise.
+  const long long wide_tiles = ((g.m + kBM - 1) / kBM) * ((g.n + 255) / 256);
+  if (wide_tiles >= sm_count) {
+    return f32 ? launch_gemm<256, 4, false, true>(g, sm_count, stream)
+               : launch_gemm<256, 4, false, false>(g, sm_count, stream);
+  }
+  return f32 ? launch_gemm<128, 6, false, true>(g, sm_count, stream)
+             : launch_gemm<128, 6, false, false>(g, sm_count, stream);
+}

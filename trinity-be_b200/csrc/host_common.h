@@ -1,0 +1,39 @@
+// Host-side helpers shared by the kernel launchers: error text, device checks, the launch
+// counter and TMA tensor-map construction through the driver entry point (no libcuda link).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/trinity_sm100.h"
+
+namespace trinity_sm100 {
+
+// Records a formatted message for trinity_sm100_last_error() and returns `code`.
+int fail(int code, const char* format, ...);
+
+// Ensures the current device is compute capability 10.x; caches the SM count per device.
+int require_sm100(int* sm_count);
+
+void count_launch(unsigned n = 1);
+
+// Checks cudaGetLastError() after a launch; `what` names the kernel.
+int check_launch(const char* what);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// 2-D tiled tensor map over a row-major matrix: `inner` contiguous elements per row,
+// `outer` rows, `row_pitch_bytes` between rows; box = box_inner x box_outer elements.
+// swizzle128 selects the 128-byte shared-memory swizzle (box_inner * elem_bytes must be 128).
+int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
+                       uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner,
+                       uint32_t box_outer, bool swizzle128);
+
+// 3-D variant: dims (inner, mid, outer) with byte pitches for mid and outer.
+int make_tensor_map_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
+                       uint64_t mid, uint64_t outer, uint64_t mid_pitch_bytes,
+                       uint64_t outer_pitch_bytes, uint32_t box_inner, uint32_t box_mid,
+                       uint32_t box_outer, bool swizzle128);
+
+}  // namespace trinity_sm100

@@ -1,0 +1,260 @@
+"""ctypes binding of the sm_100a kernel library (``include/trinity_sm100.h``).
+
+This is the only route from Python to the CUDA kernels.  There is no CPU or PyTorch
+fallback: when the shared library is missing or a call fails, an exception is raised.
+PyTorch tensors are used for device memory and streams only; the C ABI sees raw pointers.
+"""
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parents[1] / "lib" / "libtrinity_sm100.so"
+
+BIAS_NONE, BIAS_COL_VECTOR, BIAS_ROW_VECTOR, BIAS_MATRIX = 0, 1, 2, 3
+ACT_NONE, ACT_RELU, ACT_SILU, ACT_SILU_GATE = 0, 1, 2, 3
+DT_BF16, DT_FP32 = 0, 1
+
+EXPORTS = (
+    "trinity_sm100_gemm_bf16",
+    "trinity_sm100_rmsnorm_bf16",
+    "trinity_sm100_softmax_bf16",
+    "trinity_sm100_mla_scratch_bytes",
+    "trinity_sm100_mla_default_splits",
+    "trinity_sm100_mla_decode_bf16",
+    "trinity_sm100_allreduce_flag_words",
+    "trinity_sm100_allreduce_bf16",
+    "trinity_sm100_device_status",
+    "trinity_sm100_abi_version",
+    "trinity_sm100_last_error",
+    "trinity_sm100_launch_count",
+)
+
+
+class KernelError(RuntimeError):
+    """A kernel-library call returned a non-zero code."""
+
+    def __init__(self, code, message):
+        super().__init__(f"trinity_sm100 error {code}: {message}")
+        self.code = code
+
+
+class GemmArgs(ctypes.Structure):
+    _fields_ = [
+        ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("b2", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("m", ctypes.c_int64), ("n", ctypes.c_int64), ("k", ctypes.c_int64),
+        ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldo", ctypes.c_int64),
+        ("ld_bias", ctypes.c_int64),
+        ("bias_mode", ctypes.c_int32), ("activation", ctypes.c_int32),
+        ("out_dtype", ctypes.c_int32), ("reserved", ctypes.c_int32),
+    ]
+
+
+class MlaArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("cache", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+        ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seq", ctypes.c_int32),
+        ("d_qk", ctypes.c_int32), ("d_v", ctypes.c_int32), ("kv_splits", ctypes.c_int32),
+        ("scale", ctypes.c_float), ("reserved", ctypes.c_int32),
+    ]
+
+
+class AllReduceArgs(ctypes.Structure):
+    _fields_ = [
+        ("peers", ctypes.POINTER(ctypes.c_void_p)), ("flags", ctypes.POINTER(ctypes.c_void_p)),
+        ("rows", ctypes.c_int64), ("cols", ctypes.c_int64),
+        ("world", ctypes.c_int32), ("rank", ctypes.c_int32),
+        ("epoch", ctypes.c_uint32), ("reserved", ctypes.c_int32),
+    ]
+
+
+_lock = threading.Lock()
+_lib = None
+
+
+def library_path():
+    return _LIB_PATH
+
+
+def library():
+    """Loads the kernel library once; raises if it has not been built."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            if not _LIB_PATH.exists():
+                raise RuntimeError(
+                    f"{_LIB_PATH} is missing: build it with `python -m __graft_entry__` "
+                    "(there is no fallback path)")
+            lib = ctypes.CDLL(str(_LIB_PATH))
+            lib.trinity_sm100_gemm_bf16.argtypes = [ctypes.POINTER(GemmArgs), ctypes.c_void_p]
+            lib.trinity_sm100_rmsnorm_bf16.argtypes = [
+                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                ctypes.c_float, ctypes.c_void_p]
+            lib.trinity_sm100_softmax_bf16.argtypes = [
+                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
+            lib.trinity_sm100_mla_scratch_bytes.argtypes = [ctypes.c_int32] * 4
+            lib.trinity_sm100_mla_scratch_bytes.restype = ctypes.c_size_t
+            lib.trinity_sm100_mla_default_splits.argtypes = [ctypes.c_int32] * 2
+            lib.trinity_sm100_mla_decode_bf16.argtypes = [ctypes.POINTER(MlaArgs), ctypes.c_void_p]
+            lib.trinity_sm100_allreduce_flag_words.restype = ctypes.c_size_t
+            lib.trinity_sm100_allreduce_bf16.argtypes = [
+                ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
+            lib.trinity_sm100_device_status.argtypes = [
+                ctypes.POINTER(ctypes.c_uint32), ctypes.c_int]
+            lib.trinity_sm100_last_error.restype = ctypes.c_char_p
+            lib.trinity_sm100_launch_count.restype = ctypes.c_uint64
+            _lib = lib
+    return _lib
+
+
+def _check(code):
+    if code != 0:
+        raise KernelError(code, library().trinity_sm100_last_error().decode())
+
+
+def _stream(stream=None):
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return ctypes.c_void_p(stream.cuda_stream)
+
+
+def _require(t, dtype, name):
+    if not t.is_cuda or t.dtype != dtype:
+        raise ValueError(f"{name}: expected a CUDA tensor of {dtype}, got {t.device} {t.dtype}")
+
+
+def launch_count():
+    return int(library().trinity_sm100_launch_count())
+
+
+def device_status(clear=False):
+    value = ctypes.c_uint32(0)
+    _check(library().trinity_sm100_device_status(ctypes.byref(value), int(clear)))
+    return value.value
+
+
+def gemm(a, b, *, bias=None, bias_mode=None, activation=ACT_NONE, b2=None, out=None,
+         out_dtype=torch.bfloat16, stream=None):
+    """out = act(a @ b + bias); see ``trinity_sm100_gemm_bf16``.  Row-major 2-D tensors."""
+    _require(a, torch.bfloat16, "a")
+    _require(b, torch.bfloat16, "b")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+        raise ValueError("gemm: a must be [m,k] and b [k,n]")
+    if a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("gemm: operands must be row-major with unit inner stride")
+    m, k = a.shape
+    n = b.shape[1]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    if out.shape != (m, n) or out.stride(1) != 1:
+        raise ValueError("gemm: out must be a row-major [m,n] tensor")
+    args = GemmArgs()
+    args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.m, args.n, args.k = m, n, k
+    args.lda, args.ldb, args.ldo = a.stride(0), b.stride(0), out.stride(0)
+    args.activation = activation
+    args.out_dtype = DT_FP32 if out.dtype == torch.float32 else DT_BF16
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError("gemm: out dtype must be bf16 or fp32")
+    if b2 is not None:
+        _require(b2, torch.bfloat16, "b2")
+        if b2.shape != b.shape or b2.stride() != b.stride():
+            raise ValueError("gemm: b2 must match b")
+        args.b2 = b2.data_ptr()
+    if bias is not None:
+        _require(bias, torch.bfloat16, "bias")
+        if bias_mode is None:
+            bias_mode = BIAS_MATRIX if bias.dim() == 2 else BIAS_COL_VECTOR
+        expected = {BIAS_COL_VECTOR: (n,), BIAS_ROW_VECTOR: (m,), BIAS_MATRIX: (m, n)}[bias_mode]
+        if tuple(bias.shape) != expected or bias.stride(-1) != 1:
+            raise ValueError(f"gemm: bias shape {tuple(bias.shape)} does not fit mode {bias_mode}")
+        args.bias = bias.data_ptr()
+        args.ld_bias = bias.stride(0) if bias.dim() == 2 else 0
+        args.bias_mode = bias_mode
+    with torch.cuda.device(a.device):
+        _check(library().trinity_sm100_gemm_bf16(ctypes.byref(args), _stream(stream)))
+    return out
+
+
+def rmsnorm(x, gain=None, eps=0.0, out=None, stream=None):
+    _require(x, torch.bfloat16, "x")
+    if x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("rmsnorm: x must be a contiguous [rows, cols] tensor")
+    if out is None:
+        out = torch.empty_like(x)
+    if gain is not None:
+        _require(gain, torch.bfloat16, "gain")
+        if tuple(gain.shape) != (x.shape[1],) or not gain.is_contiguous():
+            raise ValueError("rmsnorm: gain must be [cols]")
+    with torch.cuda.device(x.device):
+        _check(library().trinity_sm100_rmsnorm_bf16(
+            x.data_ptr(), gain.data_ptr() if gain is not None else None, out.data_ptr(),
+            x.shape[0], x.shape[1], float(eps), _stream(stream)))
+    return out
+
+
+def softmax(x, out=None, stream=None):
+    _require(x, torch.bfloat16, "x")
+    if x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("softmax: x must be a contiguous [rows, cols] tensor")
+    if out is None:
+        out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        _check(library().trinity_sm100_softmax_bf16(
+            x.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], _stream(stream)))
+    return out
+
+
+def mla_default_splits(batch, seq):
+    return int(library().trinity_sm100_mla_default_splits(batch, seq))
+
+
+def mla_scratch_bytes(batch, heads, d_v, kv_splits):
+    return int(library().trinity_sm100_mla_scratch_bytes(batch, heads, d_v, kv_splits))
+
+
+def mla_decode(q, cache, scale, d_v=512, kv_splits=0, out=None, scratch=None, stream=None):
+    """out[b,h,:] = softmax_s(scale * q[b,h] . cache[b,s]) @ cache[b,:,:d_v]."""
+    _require(q, torch.bfloat16, "q")
+    _require(cache, torch.bfloat16, "cache")
+    if q.dim() != 3 or cache.dim() != 3 or not q.is_contiguous() or not cache.is_contiguous():
+        raise ValueError("mla_decode: q [batch,heads,d_qk] and cache [batch,seq,d_qk], contiguous")
+    batch, heads, d_qk = q.shape
+    if cache.shape[0] != batch or cache.shape[2] != d_qk:
+        raise ValueError("mla_decode: q and cache disagree on batch or width")
+    seq = cache.shape[1]
+    if kv_splits == 0:
+        kv_splits = mla_default_splits(batch, seq)
+    if out is None:
+        out = torch.empty((batch, heads, d_v), dtype=torch.bfloat16, device=q.device)
+    need = mla_scratch_bytes(batch, heads, d_v, kv_splits)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+    args = MlaArgs()
+    args.q, args.cache, args.out = q.data_ptr(), cache.data_ptr(), out.data_ptr()
+    args.scratch, args.scratch_bytes = scratch.data_ptr(), scratch.numel() * scratch.element_size()
+    args.batch, args.heads, args.seq, args.d_qk, args.d_v = batch, heads, seq, d_qk, d_v
+    args.kv_splits = kv_splits
+    args.scale = float(scale)
+    with torch.cuda.device(q.device):
+        _check(library().trinity_sm100_mla_decode_bf16(ctypes.byref(args), _stream(stream)))
+    return out
+
+
+def allreduce_flag_words():
+    return int(library().trinity_sm100_allreduce_flag_words())
+
+
+def allreduce(peer_ptrs, flag_ptrs, rows, cols, rank, epoch, stream=None):
+    """In-place sum all-reduce over peer-mapped BF16 buffers (see the C header)."""
+    world = len(peer_ptrs)
+    peers = (ctypes.c_void_p * world)(*peer_ptrs)
+    flags = (ctypes.c_void_p * world)(*flag_ptrs)
+    args = AllReduceArgs()
+    args.peers = ctypes.cast(peers, ctypes.POINTER(ctypes.c_void_p))
+    args.flags = ctypes.cast(flags, ctypes.POINTER(ctypes.c_void_p))
+    args.rows, args.cols, args.world, args.rank, args.epoch = rows, cols, world, rank, epoch
+    _check(library().trinity_sm100_allreduce_bf16(ctypes.byref(args), _stream(stream)))
