@@ -1,0 +1,430 @@
+#!/usr/bin/env python
+"""Benchmark of the native-provider hot path on B200.
+
+Default workload (the configuration the headline metric is quoted on): GEMM + bias + ReLU,
+A[8192,8192] @ W[8192,8192] + bias[8192], BF16 in / FP32 accumulate / BF16 out, captured once
+in a CUDA Graph; one step = one graph replay.  Inputs are synthetic and seeded.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload gemm_relu|gemm_bias_1024|rmsnorm|softmax|mla]
+
+Prints one JSON line (rank 0).  With N > 1 (launched under torch.distributed.run) every rank
+runs an independent replica of the workload on its own GPU ("replicas only": the path has no
+exchange step), timing is the maximum over ranks and `value` is the aggregate.
+"""
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+sys.path.insert(0, str(REPO / "trinity-be_b200"))
+
+import torch  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+# DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), per workload.
+# None until a capture exists for that workload.
+NCU_TRAFFIC_BYTES = {
+    "gemm_relu": None,
+    "gemm_bias_1024": None,
+    "rmsnorm": None,
+    "softmax": None,
+    "mla": None,
+}
+
+
+def peaks():
+    path = REPO / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": data["hbm_gbs"], "bf16_tflops": data["bf16_tflops"],
+                "bf16_tflops_sustained": data["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # NVML missing: clocks are reported as unknown
+            self.nvml = None
+
+    def _loop(self):
+        n = self.nvml
+        names = {
+            getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                try:
+                    mask = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self.nvml:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": []}
+        ordered = sorted(self.samples)
+        return {"sm_mhz": ordered[len(ordered) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(ordered)}
+
+
+# ---------------------------------------------------------------- workloads
+class Workload:
+    """name, metric, unit, bound, work per step, device step, end-to-end step, CPU sample."""
+
+
+def make_workload(name, device):
+    from oracle import workloads as wl  # seeded input generators only (no oracle math here)
+    from trinity_lowering import kernels as k
+
+    w = Workload()
+    w.name = name
+    on_gpu = device.type == "cuda"
+
+    def pin(t):
+        return t.pin_memory() if on_gpu else t
+    if name in ("gemm_relu", "gemm_bias_1024"):
+        if name == "gemm_relu":
+            m = n = kk = 8192
+            a, wt, bias = wl.gemm_inputs(m, n, kk, 1235, "normal")
+            act = k.ACT_RELU
+            w.label = "gemm_bias_relu A[8192,8192]@W[8192,8192]+bias[8192], CUDA-Graph replay"
+        else:
+            m = n = kk = 1024
+            a, wt, bias = wl.gemm_inputs(m, n, kk, 1234, "uniform")
+            act = k.ACT_NONE
+            w.label = "gemm_bias A[1024,1024]@B[1024,1024]+bias[1024], CUDA-Graph replay"
+        w.metric, w.unit, w.bound, w.dtype = "bf16_gemm_epilogue_tflops", "TFLOP/s", "tensor", "bf16"
+        w.work = 2.0 * m * n * kk / 1e12                       # TFLOP per step
+        w.alg_bytes = (m * kk + kk * n + n + m * n) * 2
+        host = [pin(t) for t in (a, wt, bias)]
+        host_out = pin(torch.empty((m, n), dtype=torch.bfloat16))
+        dev = [t.to(device) for t in (a, wt, bias)]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+        w.kernels_per_step = 1
+        w.l2_note = ("inputs larger than L2" if (m * kk + kk * n) * 2 > L2_BYTES
+                     else "L2 flushed between steps")
+        w.flush = (m * kk + kk * n) * 2 <= L2_BYTES
+
+        def device_step():
+            k.gemm(dev[0], dev[1], bias=dev[2], bias_mode=k.BIAS_COL_VECTOR, activation=act, out=out)
+
+        def e2e_step():
+            for src, dst in zip(host, dev):
+                dst.copy_(src, non_blocking=True)
+            device_step()
+            host_out.copy_(out, non_blocking=True)
+
+        w.h2d = sum(t.numel() * 2 for t in host)
+        w.d2h = host_out.numel() * 2
+
+        def cpu_sample(threads, budget_s):
+            torch.set_num_threads(threads)
+            af, wf, bf = a.float(), wt.float(), bias.float()
+            rows = min(m, 256)
+            t0 = time.perf_counter()
+            torch.relu(torch.addmm(bf, af[:rows], wf)) if act else torch.addmm(bf, af[:rows], wf)
+            probe = max(time.perf_counter() - t0, 1e-4)
+            rows = int(min(m, max(256, rows * budget_s / probe / 2)))
+            t0 = time.perf_counter()
+            y = torch.addmm(bf, af[:rows], wf)
+            if act:
+                y = torch.relu(y)
+            y = y.bfloat16()
+            dt = time.perf_counter() - t0
+            return 2.0 * rows * n * kk / 1e12 / dt, f"{rows} of {m} rows, torch CPU FP32 addmm" + \
+                ("+relu" if act else ""), dt
+
+    elif name in ("rmsnorm", "softmax"):
+        rows, cols = 32768, 4096
+        x, g = wl.rownorm_inputs(rows, cols, 1236)
+        w.label = f"{name} X[32768,4096] bf16" + (", gain[4096], eps 1e-6" if name == "rmsnorm" else "")
+        w.metric, w.unit, w.bound, w.dtype = f"{name}_hbm_gbs", "GB/s", "hbm", "bf16"
+        w.alg_bytes = rows * cols * 4 + (cols * 2 if name == "rmsnorm" else 0)
+        w.work = w.alg_bytes / 1e9
+        host_x = pin(x)
+        host_y = pin(torch.empty_like(x))
+        xd, gd = x.to(device), g.to(device)
+        yd = torch.empty_like(xd)
+        w.kernels_per_step = 1
+        w.l2_note, w.flush = "inputs larger than L2", False
+
+        def device_step():
+            if name == "rmsnorm":
+                k.rmsnorm(xd, gd, 1e-6, out=yd)
+            else:
+                k.softmax(xd, out=yd)
+
+        def e2e_step():
+            xd.copy_(host_x, non_blocking=True)
+            device_step()
+            host_y.copy_(yd, non_blocking=True)
+
+        w.h2d, w.d2h = x.numel() * 2, x.numel() * 2
+
+        def cpu_sample(threads, budget_s):
+            torch.set_num_threads(threads)
+            sample = x[:4096]
+            t0 = time.perf_counter()
+            if name == "rmsnorm":
+                wl.rmsnorm_oracle(sample, g, 1e-6)
+            else:
+                wl.softmax_oracle(sample)
+            dt = time.perf_counter() - t0
+            return sample.numel() * 4 / 1e9 / dt, "4096 of 32768 rows, CPU oracle (FP32 torch)", dt
+
+    elif name == "mla":
+        batch, heads, seq, d_qk, d_v = 64, 128, 4096, 576, 512
+        q, cache = wl.mla_inputs(batch, heads, seq, d_qk, 1237)
+        scale = 1.0 / math.sqrt(192.0)
+        w.label = "mla_decode batch64 x 128 heads, cache[64,4096,576] bf16"
+        w.metric, w.unit, w.bound, w.dtype = "mla_decode_hbm_gbs", "GB/s", "hbm", "bf16"
+        w.alg_bytes = (q.numel() + cache.numel() + batch * heads * d_v) * 2
+        w.work = w.alg_bytes / 1e9
+        host_q, host_c = pin(q), pin(cache)
+        qd, cd = q.to(device), cache.to(device)
+        od = torch.empty((batch, heads, d_v), dtype=torch.bfloat16, device=device)
+        host_o = pin(torch.empty_like(od, device="cpu"))
+        splits = k.mla_default_splits(batch, seq) if on_gpu else 1
+        scratch = torch.empty(max(256, k.mla_scratch_bytes(batch, heads, d_v, splits)) if on_gpu
+                              else 256, dtype=torch.uint8, device=device)
+        w.kernels_per_step = 1 if splits == 1 else 2
+        w.l2_note, w.flush = "inputs larger than L2", False
+
+        def device_step():
+            k.mla_decode(qd, cd, scale, kv_splits=splits, out=od, scratch=scratch)
+
+        def e2e_step():
+            qd.copy_(host_q, non_blocking=True)
+            cd.copy_(host_c, non_blocking=True)
+            device_step()
+            host_o.copy_(od, non_blocking=True)
+
+        w.h2d, w.d2h = (q.numel() + cache.numel()) * 2, od.numel() * 2
+
+        def cpu_sample(threads, budget_s):
+            torch.set_num_threads(threads)
+            t0 = time.perf_counter()
+            wl.mla_oracle(q, cache, scale, d_v, batches=[0, 1])
+            dt = time.perf_counter() - t0
+            return (w.alg_bytes * 2 / batch) / 1e9 / dt, "2 of 64 sequences, CPU oracle", dt
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    w.device_step, w.e2e_step, w.cpu_sample = device_step, e2e_step, cpu_sample
+    return w
+
+
+def flush_l2(buffer):
+    buffer.zero_()
+
+
+def timed(step, steps, flush_buffer, stream):
+    """CUDA-event time (ms) of `steps` calls on `stream`; L2 flushes are excluded from the sum."""
+    if flush_buffer is None:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(steps):
+            step()
+        stop.record(stream)
+        stop.synchronize()
+        return start.elapsed_time(stop)
+    total = 0.0
+    events = []
+    for _ in range(steps):
+        flush_l2(flush_buffer)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        step()
+        b.record(stream)
+        events.append((a, b))
+    torch.cuda.synchronize()
+    for a, b in events:
+        total += a.elapsed_time(b)
+    return total
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU evaluation of the path on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    w = make_workload(args.workload, torch.device("cpu"))
+    values = []
+    sample = ""
+    for i in range(args.warmup + args.steps):
+        value, sample, _ = w.cpu_sample(threads, budget_s=2.0)
+        if i >= args.warmup:
+            values.append(value)
+    value = sum(values) / len(values)
+    line = {
+        "impl": "reference", "metric": w.metric, "value": value, "unit": w.unit,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": w.dtype, "data": "synthetic",
+        "config": {"workload": w.label, "note": "reference plan evaluation on host cores"},
+        "cpu_baseline": {"value": value, "unit": w.unit, "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=100)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default="gemm_relu")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        # The CPU workload construction needs no GPU; ranks other than 0 do no work.
+        if rank == 0:
+            run_reference(args, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    distributed = world > 1
+    if distributed:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    from trinity_lowering import kernels as k
+    k.library()
+    w = make_workload(args.workload, device)
+    stream = torch.cuda.Stream(device=device)
+    flush_buffer = (torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device) if w.flush else None)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if distributed:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        # Capture one step (all launches of the hot path) in a CUDA Graph, as the configuration asks.
+        w.device_step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            w.device_step()
+        for _ in range(args.warmup):
+            graph.replay()
+        barrier()
+        launches_before = k.launch_count()
+        with ClockSampler(local_rank) as clocks:
+            ms = timed(graph.replay, args.steps, flush_buffer, stream)
+        barrier()
+        # end to end: host buffers in, result out, every step
+        for _ in range(3):
+            w.e2e_step()
+        barrier()
+        e2e_steps = max(3, min(args.steps, 10))
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(e2e_steps):
+            w.e2e_step()
+        stop.record(stream)
+        stop.synchronize()
+        e2e_ms = start.elapsed_time(stop)
+        barrier()
+    launches = args.steps * w.kernels_per_step + (k.launch_count() - launches_before)
+
+    if distributed:
+        t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+
+    status = k.device_status()
+    if status:
+        raise SystemExit(f"device status word {status:#x}: a bounded in-kernel wait gave up")
+
+    pk = peaks()
+    per_step_ms = ms / args.steps
+    value = world * w.work * args.steps / (ms / 1e3)
+    e2e_value = world * w.work * e2e_steps / (e2e_ms / 1e3)
+    achieved = w.work / (per_step_ms / 1e3)            # per GPU, dominant kernel
+    if w.bound == "tensor":
+        long_run = ms > 1000.0
+        peak = pk["bf16_tflops_sustained"] if long_run else pk["bf16_tflops"]
+        peak_note = ("sustained" if long_run else "burst") + " cuBLAS bf16, " + pk["source"]
+        roof_unit = "TFLOP/s"
+    else:
+        peak, peak_note, roof_unit = pk["hbm_gbs"], "copy bandwidth, " + pk["source"], "GB/s"
+    line = {
+        "metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per_step_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "config": {"workload": w.label, "l2": w.l2_note,
+                   "parallelism": "replicas only" if world > 1 else "single GPU",
+                   "launch": "CUDA Graph replay"},
+        "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": roof_unit,
+                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name),
+                     "algorithmic_bytes": w.alg_bytes, "peak_kind": peak_note},
+        "e2e": {"value": e2e_value, "unit": w.unit, "h2d_bytes_per_step": w.h2d,
+                "d2h_bytes_per_step": w.d2h, "steps": e2e_steps},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        v, sample, _ = w.cpu_sample(threads, budget_s=10.0)
+        line["cpu_baseline"] = {"value": v, "unit": w.unit, "cores": threads, "kind": "port",
+                                "sample": sample}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

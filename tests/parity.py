@@ -44,6 +44,8 @@ def assert_close_bf16(actual, expected, max_ulp=1, max_abs=None, rel_l2=REL_L2,
     if max_abs is not None:
         worst = (a - e).abs().max().item()
         assert worst <= max_abs, f"max-abs {worst:.3e} > {max_abs}"
+    if max_ulp is None:
+        return
     distance = ulp_distance(actual, expected)[finite]
     floor = abs_floor_scale * e.square().mean().sqrt().item()
     over = ((distance > max_ulp) & ((a - e).abs() > floor)).float().mean().item()

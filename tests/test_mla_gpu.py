@@ -1,0 +1,83 @@
+"""Batched MLA decode through the C ABI versus the CPU oracle (B200 only).
+
+Tolerance: the path's stated floating-point bar, rel-L2 <= 1e-2 and max-abs <= 2e-2 against
+the FP32 oracle rounded to BF16.  Probabilities are rounded to BF16 before the value product
+(as in any fused attention), so a per-element ulp bound does not apply to outputs that are
+weighted means close to zero."""
+import math
+
+import pytest
+import torch
+
+from oracle import workloads as wl
+from parity import assert_close_bf16
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+SCALE = 1.0 / math.sqrt(192.0)
+
+
+@pytest.fixture(scope="module")
+def kernels():
+    from trinity_lowering import kernels as k
+    k.library()
+    yield k
+    assert k.device_status() == 0
+
+
+def test_golden_case(kernels, golden):
+    case = golden["mla"]
+    q, cache = wl.mla_inputs(case["batch"], case["heads"], case["seq"], case["d_qk"], case["seed"])
+    for splits in (1, 2, 3):
+        out = kernels.mla_decode(q.to(DEV), cache.to(DEV), case["scale"], kv_splits=splits).cpu()
+        assert_close_bf16(out, case["expected"].view(torch.bfloat16), max_ulp=None, max_abs=2e-2)
+
+
+@pytest.mark.parametrize("batch,heads,seq,splits", [
+    (1, 128, 32, 1), (2, 128, 64, 1), (1, 128, 4096, 1), (3, 128, 1000, 0), (2, 64, 257, 2),
+    (1, 16, 2048, 4), (4, 128, 512, 3), (1, 128, 40, 2),
+])
+def test_against_oracle(kernels, batch, heads, seq, splits):
+    q, cache = wl.mla_inputs(batch, heads, seq, 576, 1237 + seq)
+    out = kernels.mla_decode(q.to(DEV), cache.to(DEV), SCALE, kv_splits=splits).cpu()
+    expected = wl.mla_oracle(q, cache, SCALE, 512)
+    assert_close_bf16(out, expected, max_ulp=None, max_abs=2e-2)
+
+
+def test_rescale_path_with_growing_scores(kernels):
+    """Scores that grow along the sequence force the accumulator rescale again and again."""
+    q, cache = wl.mla_inputs(1, 128, 1024, 576, 4242)
+    ramp = torch.linspace(0.2, 3.0, 1024).view(1, 1024, 1)
+    cache = (cache.float() * ramp).bfloat16()
+    q = (q.float() * 2).bfloat16()
+    out = kernels.mla_decode(q.to(DEV), cache.to(DEV), SCALE, kv_splits=1).cpu()
+    expected = wl.mla_oracle(q, cache, SCALE, 512)
+    # outputs reach |y| ~ 10 here, where one BF16 ulp is 0.0625: bound the error by one ulp of
+    # the largest output instead of the O(1)-output bound
+    top = expected.float().abs().max().item()
+    assert_close_bf16(out, expected, max_ulp=None, max_abs=2.0 ** (math.floor(math.log2(top)) - 7))
+
+
+def test_full_size_properties(kernels):
+    """batch 64 x 128 heads x 4096 positions: oracle on two batches, and the convexity
+    property: with a cache whose value part is constant per batch, the output is that constant."""
+    q, cache = wl.mla_inputs(64, 128, 4096, 576, 1237)
+    qd, cd = q.to(DEV), cache.to(DEV)
+    out = kernels.mla_decode(qd, cd, SCALE)
+    picks = [0, 37]
+    expected = wl.mla_oracle(q, cache, SCALE, 512, batches=picks)
+    assert_close_bf16(out[picks].cpu(), expected, max_ulp=None, max_abs=2e-2)
+    # split invariance: 1 split and 2 splits agree to rounding
+    out2 = kernels.mla_decode(qd, cd, SCALE, kv_splits=2)
+    assert_close_bf16(out2.cpu(), out.cpu(), max_ulp=None, max_abs=2e-2)
+    const = torch.linspace(-1, 1, 512).bfloat16()
+    cd[:, :, :512] = const.to(DEV)
+    flat = kernels.mla_decode(qd, cd, SCALE).cpu()
+    assert (flat.float() - const.float()).abs().max().item() <= 1.0 / 128
+
+
+def test_rejects_unsupported_geometry(kernels):
+    q = torch.zeros(1, 128, 512, dtype=torch.bfloat16, device=DEV)
+    c = torch.zeros(1, 64, 512, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(kernels.KernelError):
+        kernels.mla_decode(q, c, SCALE)

@@ -3,4 +3,5 @@
 #include "host_common.cu"
 #include "gemm_tcgen05.cu"
 #include "rownorm.cu"
-#include "pending.cu"
+#include "mla_decode.cu"
+#include "allreduce.cu"
