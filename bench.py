@@ -30,13 +30,13 @@ import torch  # noqa: E402
 L2_BYTES = 126 * 1024 * 1024
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), per workload.
-# None until a capture exists for that workload.
+# None until a capture exists for that workload.  Sources: profiles/*.md.
 NCU_TRAFFIC_BYTES = {
-    "gemm_relu": None,
+    "gemm_relu": 1.153e9,
     "gemm_bias_1024": None,
-    "rmsnorm": None,
-    "softmax": None,
-    "mla": None,
+    "rmsnorm": 4.889e8,
+    "softmax": 4.866e8,
+    "mla": 3.154e8,
 }
 
 
@@ -316,6 +316,8 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="gemm_relu")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-graph", action="store_true",
+                        help="launch directly instead of replaying a CUDA Graph (for profilers)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -354,15 +356,19 @@ def main():
         # Capture one step (all launches of the hot path) in a CUDA Graph, as the configuration asks.
         w.device_step()
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            w.device_step()
+        if args.no_graph:
+            replay = w.device_step
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                w.device_step()
+            replay = graph.replay
         for _ in range(args.warmup):
-            graph.replay()
+            replay()
         barrier()
         launches_before = k.launch_count()
         with ClockSampler(local_rank) as clocks:
-            ms = timed(graph.replay, args.steps, flush_buffer, stream)
+            ms = timed(replay, args.steps, flush_buffer, stream)
         barrier()
         # end to end: host buffers in, result out, every step
         for _ in range(3):
@@ -377,7 +383,9 @@ def main():
         stop.synchronize()
         e2e_ms = start.elapsed_time(stop)
         barrier()
-    launches = args.steps * w.kernels_per_step + (k.launch_count() - launches_before)
+    launches = k.launch_count() - launches_before
+    if not args.no_graph:
+        launches += args.steps * w.kernels_per_step  # replays do not pass through the library
 
     if distributed:
         t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
@@ -406,7 +414,7 @@ def main():
         "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
         "config": {"workload": w.label, "l2": w.l2_note,
                    "parallelism": "replicas only" if world > 1 else "single GPU",
-                   "launch": "CUDA Graph replay"},
+                   "launch": "direct" if args.no_graph else "CUDA Graph replay"},
         "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": roof_unit,
                      "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name),
                      "algorithmic_bytes": w.alg_bytes, "peak_kind": peak_note},
