@@ -148,6 +148,27 @@ TRINITY_SM100_API int trinity_sm100_mla_default_splits(int32_t batch, int32_t se
 TRINITY_SM100_API int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void* stream);
 
 /*
+ * The same decode for callers that cannot obtain scratch memory: a streamed artifact's launch
+ * function, for example, is handed only the plan's buffers, has no workspace in its format, and
+ * may be running under stream capture, so it can neither bring scratch nor allocate it.  This
+ * entry point keeps the split partials in a fixed array inside the library instead
+ * (TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES per GPU, held from library load to process exit) and
+ * calls no cudaMalloc, cudaFree or other allocating routine.  args->scratch and
+ * args->scratch_bytes are ignored.
+ *
+ * Limit: trinity_sm100_mla_scratch_bytes(batch, heads, d_v, splits) must not exceed the array;
+ * larger requests return TRINITY_SM100_E_UNSUPPORTED with an explanation.
+ * First use on a device looks up the array's device address (one cudaGetSymbolAddress with
+ * that device current); make that first call outside any stream capture.
+ * All calls on one GPU share the array: calls that overlap in time on the GPU race on it.
+ * Nothing in the array needs clearing between calls.
+ *
+ * This entry point has no counterpart in the reference project.
+ */
+#define TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES (32u << 20)
+TRINITY_SM100_API int trinity_sm100_mla_decode_bf16_noalloc(const trinity_sm100_mla* args, void* stream);
+
+/*
  * Sum all-reduce of a BF16 [rows, cols] matrix across `world` GPUs of one NVLink domain,
  * through peer-mapped memory (no NVSHMEM, no NCCL on the data path).
  *

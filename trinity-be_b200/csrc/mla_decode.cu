@@ -488,3 +488,71 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   }
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some callers have nowhere to get scratch memory from.  The launch function of a streamed
+// artifact (trinity_launch in a program.so) is such a caller: it receives nothing but the
+// plan's buffer bindings, the artifact format gives streamed programs no workspace, and the
+// function may run while its stream is being captured into a CUDA Graph, where asking the
+// driver or a framework allocator for memory is not an option.  For them the split partials
+// live in the fixed device array below instead of caller-provided scratch.
+//
+// The array is part of the library image: every GPU that loads the library carries these
+// TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES until the process exits.  All calls on a device share
+// it, so two calls that overlap on the GPU (different streams, or graph branches) race on the
+// partials.  Nothing in it has to start at zero: every slot the merge step reads is written by
+// the split kernel of the same call first, so stale contents of an earlier call are never seen.
+static __device__ __align__(256) unsigned char g_mla_static_scratch[TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of the array for the current device.  In host code the array's name is only
+// a stand-in, so the address is looked up once per device with that device current.
+int static_scratch_address(void** address) {
+  static std::mutex mutex;
+  static void* cached[64] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess)
+    return fail(TRINITY_SM100_E_CUDA, "mla (no-alloc): cudaGetDevice: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= 64)
+    return fail(TRINITY_SM100_E_DEVICE, "mla (no-alloc): device index %d", device);
+  std::lock_guard<std::mutex> lock(mutex);
+  if (!cached[device]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_mla_static_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(TRINITY_SM100_E_CUDA, "mla (no-alloc): cudaGetSymbolAddress: %s",
+                  cudaGetErrorString(e));
+    cached[device] = p;
+  }
+  *address = cached[device];
+  return 0;
+}
+}  // namespace
+
+extern "C" int trinity_sm100_mla_decode_bf16_noalloc(const trinity_sm100_mla* args,
+                                                     void* stream_handle) {
+  if (!args) return fail(TRINITY_SM100_E_INVALID, "mla (no-alloc): null argument block");
+  trinity_sm100_mla call = *args;
+  if (call.batch <= 0 || call.heads <= 0 || call.seq <= 0)
+    return fail(TRINITY_SM100_E_INVALID, "mla (no-alloc): empty extent");
+  int splits =
+      call.kv_splits > 0 ? call.kv_splits : trinity_sm100_mla_default_splits(call.batch, call.seq);
+  const int chunks = (call.seq + kKv - 1) / kKv;
+  if (splits > chunks) splits = chunks;
+  const size_t need = scratch_bytes(call.batch, call.heads, call.d_v, splits);
+  if (need > size_t(TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES))
+    return fail(TRINITY_SM100_E_UNSUPPORTED,
+                "mla (no-alloc): batch %d x %d splits x %d heads needs %zu scratch bytes, above the "
+                "built-in %zu; use fewer splits or trinity_sm100_mla_decode_bf16 with your own "
+                "scratch",
+                call.batch, splits, call.heads, need, size_t(TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES));
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  call.kv_splits = splits;
+  call.scratch = scratch;
+  call.scratch_bytes = TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES;
+  return trinity_sm100_mla_decode_bf16(&call, stream_handle);
+}

@@ -23,6 +23,7 @@ EXPORTS = (
     "trinity_sm100_mla_scratch_bytes",
     "trinity_sm100_mla_default_splits",
     "trinity_sm100_mla_decode_bf16",
+    "trinity_sm100_mla_decode_bf16_noalloc",
     "trinity_sm100_allreduce_flag_words",
     "trinity_sm100_allreduce_bf16",
     "trinity_sm100_device_status",
@@ -99,6 +100,8 @@ def library():
             lib.trinity_sm100_mla_scratch_bytes.restype = ctypes.c_size_t
             lib.trinity_sm100_mla_default_splits.argtypes = [ctypes.c_int32] * 2
             lib.trinity_sm100_mla_decode_bf16.argtypes = [ctypes.POINTER(MlaArgs), ctypes.c_void_p]
+            lib.trinity_sm100_mla_decode_bf16_noalloc.argtypes = [
+                ctypes.POINTER(MlaArgs), ctypes.c_void_p]
             lib.trinity_sm100_allreduce_flag_words.restype = ctypes.c_size_t
             lib.trinity_sm100_allreduce_bf16.argtypes = [
                 ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
@@ -241,6 +244,33 @@ def mla_decode(q, cache, scale, d_v=512, kv_splits=0, out=None, scratch=None, st
     args.scale = float(scale)
     with torch.cuda.device(q.device):
         _check(library().trinity_sm100_mla_decode_bf16(ctypes.byref(args), _stream(stream)))
+    return out
+
+
+MLA_STATIC_SCRATCH_BYTES = 32 << 20
+
+
+def mla_decode_noalloc(q, cache, scale, d_v=512, kv_splits=0, out=None, stream=None):
+    """``mla_decode`` for callers that cannot bring or allocate scratch memory: the split
+    partials live in a fixed array inside the kernel library (``MLA_STATIC_SCRATCH_BYTES`` per
+    GPU).  ``out`` must be passed by such callers; it is created here only as a convenience for
+    tests.  Calls that overlap on one GPU race on the shared array."""
+    _require(q, torch.bfloat16, "q")
+    _require(cache, torch.bfloat16, "cache")
+    if q.dim() != 3 or cache.dim() != 3 or not q.is_contiguous() or not cache.is_contiguous():
+        raise ValueError("mla_decode: q [batch,heads,d_qk] and cache [batch,seq,d_qk], contiguous")
+    batch, heads, d_qk = q.shape
+    if cache.shape[0] != batch or cache.shape[2] != d_qk:
+        raise ValueError("mla_decode: q and cache disagree on batch or width")
+    if out is None:
+        out = torch.empty((batch, heads, d_v), dtype=torch.bfloat16, device=q.device)
+    args = MlaArgs()
+    args.q, args.cache, args.out = q.data_ptr(), cache.data_ptr(), out.data_ptr()
+    args.batch, args.heads, args.seq, args.d_qk, args.d_v = batch, heads, cache.shape[1], d_qk, d_v
+    args.kv_splits = kv_splits
+    args.scale = float(scale)
+    with torch.cuda.device(q.device):
+        _check(library().trinity_sm100_mla_decode_bf16_noalloc(ctypes.byref(args), _stream(stream)))
     return out
 
 
