@@ -148,10 +148,21 @@ def make_workload(name, device):
         def device_step():
             k.gemm(dev[0], dev[1], bias=dev[2], bias_mode=k.BIAS_COL_VECTOR, activation=act, out=out)
 
+        # End to end goes through the public path: plan -> emit -> compile -> load -> prepare,
+        # then per step host->device copies, execution.run(), device->host copy.
+        api = {}
+
         def e2e_step():
+            if not api:
+                import trinity_lowering as tl
+                from trinity_lowering import plans
+                artifact = tl.compile(tl.emit(plans.gemm_bias(m, n, kk, "relu" if act else None)))
+                api["module"] = tl.load(artifact, device)
+                artifact.close()
+                api["execution"] = api["module"].prepare({"A": dev[0], "W": dev[1], "bias": dev[2]}, out=out)
             for src, dst in zip(host, dev):
                 dst.copy_(src, non_blocking=True)
-            device_step()
+            api["execution"].run()
             host_out.copy_(out, non_blocking=True)
 
         w.h2d = sum(t.numel() * 2 for t in host)

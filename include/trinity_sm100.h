@@ -113,6 +113,71 @@ TRINITY_SM100_API int trinity_sm100_rmsnorm_bf16(const void* x, const void* gain
 TRINITY_SM100_API int trinity_sm100_softmax_bf16(const void* x, void* y, int64_t rows, int64_t cols, void* stream);
 
 /*
+ * Generic pointwise evaluation in FP32 with one rounding at the store.
+ *
+ *   out[r,c] = f(operands..., constants)        out is [rows, cols] row-major (1-D: rows == 1)
+ *
+ * f is a postfix program: TRINITY_SM100_PW_OPERAND | (index << 8) pushes an operand element,
+ * TRINITY_SM100_PW_CONST pushes the FP32 bit pattern in the next word, binary opcodes pop two
+ * values (left operand pushed first) and unary opcodes replace the top.  An operand is a full
+ * [rows, cols] tensor, a per-row vector [rows] (the reference's `bcast ... 1`) or a per-column
+ * vector [cols] (`bcast ... 0`).  ReLU is `x < 0 ? 0 : x` (NaN and the sign of zero are kept),
+ * sigmoid is `1 / (1 + exp(-x))`.
+ *
+ * Replaces the SIMT pointwise tile kernel
+ * (src/emit/provider/cute/operator/pointwise/mod.rs:37-134, special.rs:3-10).
+ */
+#define TRINITY_SM100_PW_MAX_OPERANDS 4
+#define TRINITY_SM100_PW_MAX_PROGRAM 32
+enum trinity_sm100_pw_opcode {
+  TRINITY_SM100_PW_OPERAND = 1,
+  TRINITY_SM100_PW_CONST = 2,
+  TRINITY_SM100_PW_ADD = 16,
+  TRINITY_SM100_PW_SUB = 17,
+  TRINITY_SM100_PW_MUL = 18,
+  TRINITY_SM100_PW_DIV = 19,
+  TRINITY_SM100_PW_MAX = 20,
+  TRINITY_SM100_PW_SQR = 32,
+  TRINITY_SM100_PW_SQRT = 33,
+  TRINITY_SM100_PW_SIGMOID = 34,
+  TRINITY_SM100_PW_RELU = 35,
+  TRINITY_SM100_PW_EXP = 36
+};
+typedef struct trinity_sm100_pw_operand {
+  const void* data;
+  int32_t dtype;     /* trinity_sm100_dtype */
+  int32_t broadcast; /* 0 = [rows, cols], 1 = [rows] per row, 2 = [cols] per column */
+} trinity_sm100_pw_operand;
+typedef struct trinity_sm100_pointwise_args {
+  trinity_sm100_pw_operand operands[TRINITY_SM100_PW_MAX_OPERANDS];
+  int32_t operand_count;
+  int32_t out_dtype; /* trinity_sm100_dtype */
+  void* out;
+  int64_t rows, cols;
+  int32_t program_length;
+  uint32_t program[TRINITY_SM100_PW_MAX_PROGRAM];
+} trinity_sm100_pointwise_args;
+TRINITY_SM100_API int trinity_sm100_pointwise(const trinity_sm100_pointwise_args* args, void* stream);
+
+/*
+ * y[r] = sum_c x[r,c] (square == 0) or sum_c x[r,c]^2 (square != 0); x is BF16 or FP32
+ * [rows, cols], y is FP32 [rows], FP32 accumulation.
+ * Replaces src/emit/provider/cute/operator/reduce_sum/mod.rs:26-96.
+ */
+TRINITY_SM100_API int trinity_sm100_row_reduce_sum(const void* x, int32_t x_dtype, void* y, int64_t rows,
+                                 int64_t cols, int32_t square, void* stream);
+
+/*
+ * Plumbing a generated program.so needs without touching the CUDA runtime itself:
+ * device check at prepare time (the capability test of
+ * src/emit/native/cuda/templates/host.cu.j2:18-50), the current device, and the stream
+ * synchronisation of trinity_status (host.cu.j2:78-83).
+ */
+TRINITY_SM100_API int trinity_sm100_prepare_device(int32_t* device_index);
+TRINITY_SM100_API int trinity_sm100_current_device(int32_t* device_index);
+TRINITY_SM100_API int trinity_sm100_stream_synchronize(void* stream);
+
+/*
  * Batched multi-head latent attention decode (one query token per sequence) over a
  * compressed KV cache, split over the KV axis.
  *

@@ -1,0 +1,315 @@
+"""Planner / emitter / artifact builder on the CPU (no GPU): the C++ host library through its
+C ABI, checked against the behaviour the reference's tests pin."""
+import json
+import subprocess
+
+import pytest
+
+import trinity_lowering as tl
+from trinity_lowering import plans
+
+
+def copy_builder():
+    b = tl.PhysicalPlanBuilder()
+    x = b.add_value("fp32", [64], "external", name="X")
+    y = b.add_value("fp32", [64], "external", name="Y")
+    b.bind_input("X", x)
+    return b, x, y
+
+
+def expression(access):
+    return ("(store (view (output Y) (layout (axis a 64))) (sqrt (load (view (input X) (layout (axis a 64))) "
+            f"(keyed_index (slot a {access})))) (keyed_index (slot a {access})))")
+
+
+def test_operation_metadata_and_no_inferred_loop():
+    # python/tests/test_explicit_plan.py:40-60 of the reference
+    b, x, y = copy_builder()
+    with pytest.raises(TypeError, match="expression"):
+        b.add_operation([x], [y])
+    node = b.add_operation(inflows=[x], outflows=[y], expression=expression("fulltile"))
+    metadata = json.loads(b.build([node], "Y", y).metadata_json())
+    assert metadata["statements"] == [{"operations": [0]}]
+    assert metadata["operations"] == [{"id": 0, "inflows": [metadata["inputs"][0]["value"]],
+                                       "outflows": [metadata["output"]["value"]]}]
+
+
+def test_serial_domain_is_preserved_and_matches_text_ir():
+    # python/tests/test_explicit_plan.py:58-73
+    b, x, y = copy_builder()
+    body = expression("(tile i 16)")
+    op = b.add_operation([x], [y], expression=body)
+    loop = b.add_loop("sequential", "i", 16, 64, 16, [op])
+    plan = json.loads(b.build([loop], "Y", y).metadata_json())
+    assert plan["statements"][0]["loop"]["domain"] == {
+        "variable": "lv0", "start": {"Constant": 16}, "stop": {"Constant": 64}, "step": {"Constant": 16}}
+    assert plan["statements"][0]["loop"]["body"] == [{"operations": [0]}]
+    (ir,) = tl.lower_ir(f"(sloop 16 64 16 i {body})", {}, {"X": "fp32", "Y": "fp32"})
+    assert json.loads(ir.metadata_json()) == plan
+
+
+def test_nested_bounds_are_renamed_and_duplicate_membership_is_rejected():
+    # python/tests/test_explicit_plan.py:76-95
+    b, x, y = copy_builder()
+    op = b.add_operation([x], [y], expression=expression("fulltile"))
+    inner = b.add_loop("sequential", "j", "i", "(+ i 1)", 1, [op])
+    outer = b.add_loop("parallel", "i", 0, 2, 1, [inner])
+    plan = json.loads(b.build([outer], "Y", y).metadata_json())
+    inner = plan["statements"][0]["loop"]["body"][0]["loop"]
+    assert inner["domain"]["start"] == {"Variable": "lv0"}
+    assert inner["domain"]["stop"] == {"Add": [{"Variable": "lv0"}, {"Constant": 1}]}
+    b, x, y = copy_builder()
+    op = b.add_operation([x], [y], expression=expression("fulltile"))
+    loop = b.add_loop("parallel", "i", 0, 1, 1, [op])
+    with pytest.raises(ValueError, match="multiple statements"):
+        b.build([op, loop], "Y", y)
+
+
+def test_inputs_sorted_by_name_and_ids_in_first_use_order():
+    # tests/physical_plan.rs:82-88, src/tests.rs:147-158
+    def build(order):
+        b = tl.PhysicalPlanBuilder()
+        ids = {}
+        for name in order:
+            ids[name] = b.add_value("bf16", [128, 128], "external")
+        for name in order:
+            if name != "Y":
+                b.bind_input(name, ids[name])
+        acc = index = "(keyed_index (slot a0 (tile r 1)) (slot a1 (clipped_tile c 128)))"
+        def v(i):
+            return f"(view (tensor v{i}) (layout (axis a0 128) (axis a1 128)))"
+        body = f"(store {v(ids['Y'])} (+ (load {v(ids['B'])} {index}) (load {v(ids['A'])} {index})) {acc})"
+        op = b.add_operation([ids["A"], ids["B"]], [ids["Y"]], expression=body)
+        col = b.add_loop("parallel", "c", 0, 128, 128, [op])
+        row = b.add_loop("parallel", "r", 0, 128, 1, [col])
+        return b.build([row], "Y", ids["Y"])
+    first, second = build(["A", "B", "Y"]), build(["Y", "B", "A"])
+    assert first == second and hash(first) == hash(second)
+    data = json.loads(first.metadata_json())
+    assert [i["name"] for i in data["inputs"]] == ["A", "B"]
+    assert data["operations"][0]["inflows"] == [data["inputs"][1]["value"], data["inputs"][0]["value"]]
+
+
+def test_zero_started_accumulation_is_not_an_inflow():
+    # src/tests.rs:252-300: inside a single-operation sequential loop the destination load is the
+    # implicit zero; outside such a loop the same spelling needs a producer
+    data = json.loads(plans.gemm_bias(256, 256, 128, bias=None).metadata_json())
+    acc = data["operations"][0]["outflows"][0]
+    assert acc not in data["operations"][0]["inflows"]
+    b = tl.PhysicalPlanBuilder()
+    x = b.add_value("fp32", [64], "external", name="X")
+    y = b.add_value("fp32", [64], "external", name="Y")
+    b.bind_input("X", x)
+    body = ("(store (view (output Y) (layout (axis a 64))) (+ (load (view (output Y) (layout (axis a 64))) "
+            "(keyed_index (slot a fulltile))) (load (view (input X) (layout (axis a 64))) (keyed_index (slot a fulltile)))) "
+            "(keyed_index (slot a fulltile)))")
+    op = b.add_operation([x, y], [y], expression=body)
+    with pytest.raises(ValueError, match="MissingProducer"):
+        b.build([op], "Y", y)
+
+
+def test_error_taxonomy():
+    b, x, y = copy_builder()
+    b.bind_input("X", y)
+    op = b.add_operation([x], [y], expression=expression("fulltile"))
+    with pytest.raises(ValueError, match="DuplicateInputTensor"):
+        b.build([op], "Y", y)
+    b, x, y = copy_builder()
+    with pytest.raises(ValueError, match="unknown value"):
+        b.add_operation([999], [y], expression="(store invalid)")
+    b, x, y = copy_builder()
+    op = b.add_operation([x], [y], expression=expression("(tile i 16)"))
+    with pytest.raises(ValueError, match="unbound index"):
+        b.build([op], "Y", y)
+    b, x, y = copy_builder()
+    with pytest.raises(ValueError, match="declared inflows"):
+        op = b.add_operation([], [y], expression=expression("fulltile"))
+        b.build([op], "Y", y)
+    b, x, y = copy_builder()
+    t = b.add_value("fp32", [64], "global", name="T")
+    with pytest.raises(ValueError, match="declared outflow"):
+        op = b.add_operation([x], [t], expression=expression("fulltile"))
+        b.build([op], "Y", y)
+    with pytest.raises(ValueError, match="unexpected trailing input"):
+        tl.lower_ir("(seq dummy dummy) x", {}, {})
+    with pytest.raises(ValueError, match="unclosed expression"):
+        tl.lower_ir("(seq dummy", {}, {})
+
+
+def test_register_values_cannot_cross_statements():
+    b = tl.PhysicalPlanBuilder()
+    x = b.add_value("fp32", [64], "external", name="X")
+    t = b.add_value("fp32", [64], "register", name="T")
+    y = b.add_value("fp32", [64], "external", name="Y")
+    b.bind_input("X", x)
+    def unary(dst, src, role_dst, role_src):
+        return (f"(store (view ({role_dst} {dst}) (layout (axis a 64))) (sqrt (load (view ({role_src} {src}) "
+                "(layout (axis a 64))) (keyed_index (slot a fulltile)))) (keyed_index (slot a fulltile)))")
+    a = b.add_operation([x], [t], expression=unary("T", "X", "tensor", "input"))
+    c = b.add_operation([t], [y], expression=unary("Y", "T", "output", "tensor"))
+    with pytest.raises(ValueError, match="CrossStatementStorage"):
+        b.build([a, c], "Y", y)
+
+
+def test_bind_symbols_binds_tile_widths_and_bounds_together():
+    # tests/plan_access.rs:53-99
+    b, x, y = copy_builder()
+    op = b.add_operation([x], [y], expression=expression("(tile i T)"))
+    loop = b.add_loop("parallel", "i", 0, 64, "T", [op])
+    plan = b.build([loop], "Y", y)
+    assert plan.symbols == ["T"]
+    with pytest.raises(ValueError, match="bind_symbols"):
+        tl.emit(plan)
+    with pytest.raises(ValueError):
+        plan.bind_symbols({})
+    with pytest.raises(ValueError):
+        plan.bind_symbols({"T": 0})
+    bound = plan.bind_symbols({"T": 16})
+    assert bound.symbols == []
+    b, x, y = copy_builder()
+    op = b.add_operation([x], [y], expression=expression("(tile i 16)"))
+    loop = b.add_loop("parallel", "i", 0, 64, 16, [op])
+    assert bound == b.build([loop], "Y", y)
+
+
+def test_identity_plan_emits_without_a_launch():
+    # python/tests/test_explicit_plan.py:16-23
+    b = tl.PhysicalPlanBuilder()
+    x = b.add_value("fp32", [4], "external")
+    b.bind_input("X", x)
+    source = tl.emit(b.build([], "Y", x))
+    assert source.launch_count == 0 and "trinity_sm100_gemm_bf16(&" not in source.code
+    assert source.requirements.buffers[0].alignment == 4
+    assert source.requirements.buffers[0].input_names == ("X",) and source.requirements.buffers[0].output_name == "Y"
+
+
+def test_emit_is_deterministic_and_counts_launches():
+    # tests/streamed.rs:117-173
+    p = plans.gemm_bias(1024, 1024, 1024)
+    assert tl.emit(p).code == tl.emit(plans.gemm_bias(1024, 1024, 1024)).code
+    assert tl.emit(p).launch_count == 1                       # K loop + bias fused into one launch
+    ref = plans.reference_gemm(256, 256, 192, relu=True)      # three statements, three launches
+    source = tl.emit(ref)
+    assert source.launch_count == 3
+    assert sum(not b.external for b in source.requirements.buffers) == 2
+    assert all(b.dtype == "bf16" for b in source.requirements.buffers)
+    data = json.loads(ref.metadata_json())
+    assert {b["name"] for b in data["inputs"]} == {"X", "W", "bias"}
+    assert len(data["operations"]) == len(data["statements"]) == 3
+    # only External / Global values get buffer slots
+    fused = tl.emit(plans.rmsnorm(64, 4096))
+    assert [b.shape for b in fused.requirements.buffers] == [(64, 4096), (4096,), (64, 4096)]
+
+
+def test_world_size_other_than_one_is_refused_like_the_reference():
+    # tests/streamed.rs:202-209, python/tests/test_tensor_ops.py:25-28
+    with pytest.raises(NotImplementedError, match="Persistent"):
+        tl.emit(plans.gemm_bias(256, 256, 128, world_size=2))
+
+
+def test_hazards_are_errors():
+    # tests/plan_access.rs:213-249: overlapping tiles and partial coverage
+    def tiled(step, stop):
+        b, x, y = copy_builder()
+        op = b.add_operation([x], [y], expression=expression("(clipped_tile i 16)"))
+        loop = b.add_loop("parallel", "i", 0, stop, step, [op])
+        return b.build([loop], "Y", y)
+    with pytest.raises(ValueError, match="overlap between CTAs"):
+        tl.emit(tiled(8, 64))
+    with pytest.raises(ValueError, match="output region is not fully produced"):
+        tl.emit(tiled(16, 32))
+    assert tl.emit(tiled(16, 64)).launch_count == 1
+
+
+def test_unsupported_operations_report_no_provider():
+    b = tl.PhysicalPlanBuilder()
+    x = b.add_value("fp16", [64], "external", name="X")
+    b.bind_input("X", x)
+    with pytest.raises(NotImplementedError):
+        tl.emit(b.build([], "Y", x))
+
+
+def test_artifact_exports_exactly_five_symbols_and_cleans_up():
+    # src/compile/cuda/tests.rs:243-266, python/tests/test_compiler.py:22-73
+    source = tl.emit(plans.gemm_bias(256, 256, 128, "relu"))
+    first, second = tl.compile(source), tl.compile(source)
+    assert first.directory != second.directory
+    names = subprocess.run(["nm", "-D", "--defined-only", str(first.artifact_path)], capture_output=True,
+                           text=True, check=True).stdout.split()
+    exported = sorted(n for n in names if n.startswith("trinity_"))
+    assert exported == ["trinity_abi", "trinity_launch", "trinity_prepare", "trinity_release", "trinity_status"]
+    assert {p.name for p in first.directory.iterdir()} == {
+        "source.cu", "exports.map", "program.so", "manifest.json", "diagnostics.json"}
+    on_disk = json.loads((first.directory / "manifest.json").read_text())
+    assert on_disk["requirements"] == json.loads(source._native.requirements_json())
+    assert on_disk["execution"] == "streamed" and on_disk["library"] == "program.so"
+    assert first.diagnostics["exit_code"] == 0
+    directory = first.directory
+    first.close()
+    assert not directory.exists()
+    kept = second.persist()
+    second.close()
+    assert (kept / "program.so").exists()
+    import shutil
+    shutil.rmtree(kept)
+
+
+def test_compile_failure_carries_diagnostics():
+    source = tl.emit(plans.softmax(8, 256))
+    with pytest.raises(tl.CompileError) as info:
+        tl.compile(source, tl.CompileConfig(host_compiler="/nonexistent/bin/g++"))
+    assert "MissingCompiler" in str(info.value)
+    assert info.value.diagnostics["exit_code"] != 0
+    with pytest.raises(tl.CompileError) as info:   # a "compiler" that runs but produces nothing
+        tl.compile(source, tl.CompileConfig(host_compiler="/bin/true"))
+    assert "MissingArtifact" in str(info.value)
+
+
+def test_requirements_validation_rejects_corruption():
+    # python/tests/test_tensor_ops.py:88-102
+    from trinity_lowering.metadata import requirements
+    data = json.loads(tl.emit(plans.softmax(8, 256))._native.requirements_json())
+    assert requirements(data).buffers[-1].bytes == 8 * 256 * 2
+    for update in ({"bytes": 258}, {"strides": [2, 1]}, {"shape": [1, 1, 1, 8], "strides": [8, 8, 8, 1]},
+                   {"dtype": "fp64"}, {"alignment": 3}):
+        corrupted = json.loads(json.dumps(data))
+        corrupted["buffers"][-1].update(update)
+        with pytest.raises(ValueError):
+            requirements(corrupted)
+
+
+def test_implementation_enumeration():
+    # python/tests/test_tensor_ops.py:66-86
+    def definition(name):
+        return next(d for d in tl.pointwise_implementations() if d.id == f"cuda.{name}")
+    assert [d.id for d in tl.gemm_implementations()][0] == "blackwell.tcgen05.bf16"
+    with pytest.raises(ValueError):
+        definition("add").enumerate(["fp32"] * 3, [[16], [17], [16]])
+    with pytest.raises(ValueError):
+        definition("square").enumerate(["fp32"] * 3, [[16]] * 3)
+    with pytest.raises(ValueError):
+        definition("scalar_div").enumerate(["fp32"] * 2, [[16]] * 2)
+    with pytest.raises(ValueError):
+        definition("sqrt").enumerate(["fp32"] * 2, [[16]] * 2, scalar=2.0)
+    with pytest.raises(ValueError):
+        tl.reduce_sum_implementations()[0].enumerate(["fp32"] * 2, [[16, 32], [33]])
+    with pytest.raises(ValueError):
+        tl.broadcast_implementations()[0].enumerate(["fp32", "bf16"], [[16], [16, 32]])
+    assert tl.reduce_sum_implementations()[0].enumerate(["bf16"] * 2, [[16, 32], [16]]) == []
+    assert tl.reduce_sum_implementations()[0].enumerate(["fp32"] * 2, [[16, 32], [32]], axis=0) == []
+
+
+def test_c_abi_libraries_export_every_declared_symbol():
+    import ctypes
+    import re
+    from pathlib import Path
+    from trinity_lowering import _host, kernels
+    root = Path(__file__).resolve().parents[1]
+    for header, lib, prefix in (("trinity_sm100.h", kernels.library_path(), "trinity_sm100_"),
+                                ("trinity_host.h", _host._LIB_PATH, "th_")):
+        declared = set(re.findall(r"\b(" + prefix + r"\w+)\s*\(", (root / "include" / header).read_text()))
+        declared -= {"trinity_sm100_mla", "trinity_sm100_gemm"}
+        handle = ctypes.CDLL(str(lib))
+        missing = [name for name in sorted(declared) if not hasattr(handle, name)]
+        assert not missing, missing
+        assert len(declared) >= 15

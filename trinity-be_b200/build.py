@@ -63,8 +63,10 @@ def build_host(force=False):
     deps = sources + list(HOST.glob("*.hpp")) + list(HOST.glob("*.h")) + list(
         (REPO / "include").glob("*.h"))
     if force or _stale(target, deps):
+        cuda = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
         _run(["g++", "-std=c++17", "-O2", "-shared", "-fPIC", "-fvisibility=hidden",
-              "-I", str(REPO / "include"), "-o", str(target), *map(str, sources), "-ldl",
+              "-I", str(REPO / "include"), "-I", str(cuda / "include"), "-o", str(target),
+              *map(str, sources), "-L", str(cuda / "lib64"), "-lcudart_static", "-ldl", "-lrt",
               "-lpthread"])
     return target
 

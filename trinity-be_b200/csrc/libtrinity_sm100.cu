@@ -4,5 +4,6 @@
 #include "host_common.cu"
 #include "gemm_tcgen05.cu"
 #include "rownorm.cu"
+#include "pointwise.cu"
 #include "mla_decode.cu"
 #include "allreduce.cu"

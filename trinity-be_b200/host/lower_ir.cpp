@@ -1,0 +1,217 @@
+// Text reader for loop/tensor IR: (seq a b), (ploop start stop step var body),
+// (sloop start stop step var body), (store view rhs index), `dummy` subtrees dropped.
+//
+// Restates the part of the reference reader the native path needs
+// (src/analysis/plan/ir.rs:85-128, :494-633) and its storage rule in brief
+// (src/analysis/storage/mod.rs:127-141, :197-234): declared inputs and outputs are External; a
+// written tensor touched by one top-level kernel only and always through the same index and
+// view lives in a Register; every other tensor is Global.  mloop (split loops) are not read:
+// the native provider rejects them anyway (src/emit/native/mod.rs:174-185).
+#include <functional>
+
+#include "plan.hpp"
+
+namespace trinity::host {
+
+namespace {
+
+struct TensorInfo {
+  std::string role;            // input | output | tensor
+  std::vector<int64_t> shape;  // first view seen = base shape
+  std::set<int> kernels;       // top-level kernels touching it
+  std::set<std::string> regions;  // distinct (view, index) spellings
+  bool written = false;
+  int value = -1;
+};
+
+std::string spelling(const Node& n) {
+  if (n.is_atom) return n.text;
+  std::string s = "(" + n.text;
+  for (auto& c : n.children) s += " " + spelling(c);
+  return s + ")";
+}
+
+struct Reader {
+  const std::map<std::string, int64_t>& symbols;
+  const std::map<std::string, std::string>& dtypes;
+  std::map<std::string, TensorInfo> tensors;
+  std::vector<std::string> order;
+
+  int64_t number(const Node& n) const {
+    const std::string& a = n.atom();
+    char* end = nullptr;
+    long long v = strtoll(a.c_str(), &end, 10);
+    if (!a.empty() && !*end) return v;
+    auto it = symbols.find(a);
+    if (it == symbols.end()) throw SyntaxError(n.offset, "unresolved symbol " + a);
+    return it->second;
+  }
+
+  void flatten(const Node& n, std::vector<const Node*>& kernels) const {
+    if (n.is_atom) {
+      if (n.text == "dummy") return;
+      throw SyntaxError(n.offset, "expected a statement");
+    }
+    if (n.op() == "seq") {
+      const auto& a = n.args(2);
+      flatten(a[0], kernels);
+      flatten(a[1], kernels);
+    } else if (n.op() != "dummy") {
+      kernels.push_back(&n);
+    }
+  }
+
+  void collect(const Node& n, int kernel, bool is_store_destination) {
+    if (n.is_atom) return;
+    if (n.op() == "store") {
+      const auto& a = n.args(3);
+      note_access(a[0], a[2], kernel, true);
+      collect(a[1], kernel, false);
+      return;
+    }
+    if (n.op() == "load") {
+      const auto& a = n.args(2);
+      note_access(a[0], a[1], kernel, false);
+      return;
+    }
+    (void)is_store_destination;
+    for (auto& c : n.children) collect(c, kernel, false);
+  }
+
+  void note_access(const Node& view, const Node& index, int kernel, bool write) {
+    if (view.is_atom || view.op() != "view") throw SyntaxError(view.offset, "expected view");
+    const auto& v = view.args(2);
+    const std::string role = v[0].is_atom ? "" : v[0].op();
+    if (role != "input" && role != "output" && role != "tensor") throw SyntaxError(view.offset, "unsupported view base");
+    const std::string& name = v[0].args(1)[0].atom();
+    if (v[1].is_atom || v[1].op() != "layout") throw SyntaxError(view.offset, "expected layout");
+    std::vector<int64_t> shape;
+    for (auto& axis : v[1].children) {
+      const auto& a = axis.args(2);
+      const int64_t size = number(a[1]);
+      if (size <= 0) throw SyntaxError(axis.offset, "nonpositive tensor extent");
+      shape.push_back(size);
+    }
+    if (shape.empty() || shape.size() > 3) throw SyntaxError(view.offset, "supported tensor ranks are 1, 2, 3");
+    auto it = tensors.find(name);
+    if (it == tensors.end()) {
+      TensorInfo info;
+      info.role = role;
+      info.shape = shape;
+      it = tensors.emplace(name, info).first;
+      order.push_back(name);
+    } else {
+      int64_t a = 1, b = 1;
+      for (auto d : shape) a *= d;
+      for (auto d : it->second.shape) b *= d;
+      if (it->second.role != role || a != b) throw SyntaxError(view.offset, "inconsistent view for " + name);
+    }
+    it->second.kernels.insert(kernel);
+    it->second.regions.insert(spelling(v[1]) + spelling(index));
+    it->second.written |= write;
+  }
+};
+
+}  // namespace
+
+std::vector<PhysicalPlan> lower_ir(const std::string& text, const std::map<std::string, int64_t>& symbols,
+                                   const std::map<std::string, std::string>& dtypes, Target target, int world_size) {
+  Node root;
+  try {
+    root = parse_sexpr(text);
+  } catch (const SyntaxError& e) {
+    invalid(e.what());
+  }
+  try {
+    Reader reader{symbols, dtypes, {}, {}};
+    std::vector<const Node*> kernels;
+    reader.flatten(root, kernels);
+    for (size_t k = 0; k < kernels.size(); ++k) reader.collect(*kernels[k], int(k), false);
+
+    PlanBuilder builder(world_size, target);
+    std::string output_name;
+    int output_value = -1;
+    for (const std::string& name : reader.order) {
+      TensorInfo& t = reader.tensors[name];
+      auto dt = dtypes.find(name);
+      if (dt == dtypes.end()) invalid("missing dtype for " + name);
+      Storage storage = Storage::Global;
+      if (t.role == "input" || t.role == "output") storage = Storage::External;
+      else if (t.written && t.kernels.size() == 1 && t.regions.size() == 1) storage = Storage::Register;
+      t.value = builder.add_value(parse_dtype(dt->second), t.shape, storage, name);
+      if (t.role == "input") builder.bind_input(name, t.value);
+      if (t.role == "output") {
+        if (output_value >= 0) invalid("the native path takes exactly one output tensor");
+        output_name = name;
+        output_value = t.value;
+      }
+    }
+    if (output_value < 0) invalid("the program declares no output tensor");
+
+    std::function<IndexExpr(const Node&, const std::set<std::string>&)> index = [&](const Node& n, const std::set<std::string>& scope) {
+      if (n.is_atom) {
+        if (scope.count(n.text)) return IndexExpr::variable(n.text);
+        char* end = nullptr;
+        long long v = strtoll(n.text.c_str(), &end, 10);
+        if (!n.text.empty() && !*end) return IndexExpr::constant(v);
+        auto it = symbols.find(n.text);
+        if (it != symbols.end()) return IndexExpr::constant(it->second);
+        return IndexExpr::variable(n.text);  // stays symbolic until bind_symbols
+      }
+      const auto& a = n.args(2);
+      IndexExpr e;
+      if (n.op() == "+") e.kind = IndexExpr::Add;
+      else if (n.op() == "-") e.kind = IndexExpr::Sub;
+      else if (n.op() == "*") e.kind = IndexExpr::Mul;
+      else if (n.op() == "/") e.kind = IndexExpr::Div;
+      else throw SyntaxError(n.offset, "unsupported range expression");
+      e.operands = {index(a[0], scope), index(a[1], scope)};
+      return e;
+    };
+
+    std::function<std::vector<int>(const Node&, std::set<std::string>)> statements = [&](const Node& n, std::set<std::string> scope) {
+      std::vector<int> out;
+      if (n.is_atom) {
+        if (n.text == "dummy") return out;
+        throw SyntaxError(n.offset, "expected a statement");
+      }
+      if (n.op() == "seq") {
+        const auto& a = n.args(2);
+        for (int part = 0; part < 2; ++part)
+          for (int id : statements(a[part], scope)) out.push_back(id);
+        return out;
+      }
+      if (n.op() == "ploop" || n.op() == "sloop") {
+        const auto& a = n.args(5);
+        const std::string& variable = a[3].atom();
+        IndexExpr start = index(a[0], scope), stop = index(a[1], scope), step = index(a[2], scope);
+        auto nested = scope;
+        if (!nested.insert(variable).second) throw SyntaxError(n.offset, "shadowed loop variable " + variable);
+        std::vector<int> body = statements(a[4], nested);
+        if (body.empty()) throw SyntaxError(n.offset, "empty loop body");
+        out.push_back(builder.add_loop_expr(n.op() == "ploop" ? LoopKind::Parallel : LoopKind::Sequential, variable,
+                                            start, stop, step, body));
+        return out;
+      }
+      if (n.op() == "mloop") throw SyntaxError(n.offset, "split loops (mloop) are not read by the native path");
+      if (n.op() == "store") {
+        ExprPtr e = decode_expression(n, builder.values(), &symbols);
+        std::vector<int> reads;
+        e->args[0]->reads(reads);
+        out.push_back(builder.add_operation_expr(reads, {e->access.value}, e));
+        return out;
+      }
+      throw SyntaxError(n.offset, "unsupported statement " + n.op());
+    };
+    std::vector<int> top;
+    for (const Node* k : kernels)
+      for (int id : statements(*k, {})) top.push_back(id);
+    std::vector<PhysicalPlan> plans;
+    plans.push_back(builder.build(top, output_name, output_value));
+    return plans;
+  } catch (const SyntaxError& e) {
+    invalid(e.what());
+  }
+}
+
+}  // namespace trinity::host

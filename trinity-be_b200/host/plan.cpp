@@ -177,6 +177,7 @@ static const char* op_token(Expression::Kind k) {
     case Expression::Sigmoid: return "sigmoid";
     case Expression::Relu: return "relu";
     case Expression::Exp: return "exp";
+    case Expression::Transpose: return "transpose";
     case Expression::ReduceSum: return "rsum";
     case Expression::ReduceMax: return "rmax";
     case Expression::Broadcast: return "bcast";
@@ -260,11 +261,16 @@ namespace {
 
 struct Decoder {
   const std::vector<Value>& values;
+  const std::map<std::string, int64_t>* symbols = nullptr;
 
   int64_t integer(const Node& n) const {
     int64_t v;
-    if (!parse_int(n.atom(), v)) throw SyntaxError(n.offset, "unresolved integer or symbol " + n.text);
-    return v;
+    if (parse_int(n.atom(), v)) return v;
+    if (symbols) {
+      auto it = symbols->find(n.text);
+      if (it != symbols->end()) return it->second;
+    }
+    throw SyntaxError(n.offset, "unresolved integer or symbol " + n.text);
   }
   int axis(const Node& n) const {
     int64_t v = integer(n);
@@ -296,7 +302,7 @@ struct Decoder {
     auto e = std::make_shared<Expression>();
     if (n.is_atom) {
       int64_t v;
-      if (parse_int(n.text, v)) {
+      if (parse_int(n.text, v) || (symbols && symbols->count(n.text) && ((v = symbols->at(n.text)), true))) {
         e->kind = Expression::ConstInt;
         e->integer = v;
         return e;
@@ -333,6 +339,7 @@ struct Decoder {
     if (op == "sigmoid") return unary(Expression::Sigmoid, n);
     if (op == "relu") return unary(Expression::Relu, n);
     if (op == "exp") return unary(Expression::Exp, n);
+    if (op == "transpose") return unary(Expression::Transpose, n);
     if (op == "rsum") return with_axis(Expression::ReduceSum, n);
     if (op == "rmax") return with_axis(Expression::ReduceMax, n);
     if (op == "bcast") return with_axis(Expression::Broadcast, n);
@@ -364,7 +371,7 @@ struct Decoder {
   TileWidth tile_width(const Node& n) const {
     TileWidth w;
     int64_t v;
-    if (parse_int(n.atom(), v)) {
+    if (parse_int(n.atom(), v) || (symbols && symbols->count(n.text) && ((v = symbols->at(n.text)), true))) {
       if (v <= 0) throw SyntaxError(n.offset, "extent must be positive");
       w.constant = v;
     } else if (is_symbol_name(n.text)) {
@@ -510,6 +517,11 @@ void statement_text(const Statement& s, const std::vector<Operation>& ops, std::
 }
 
 }  // namespace
+
+ExprPtr decode_expression(const Node& node, const std::vector<Value>& values,
+                          const std::map<std::string, int64_t>* symbols) {
+  return Decoder{values, symbols}.expression(node);
+}
 
 // ------------------------------------------------------------------ PhysicalPlan
 std::set<std::string> PhysicalPlan::symbols() const {
@@ -747,7 +759,29 @@ int PlanBuilder::add_operation(std::vector<int> inflows, std::vector<int> outflo
     if (v < 0 || v >= int(values_.size())) invalid("unknown value");
   for (int v : outflows)
     if (v < 0 || v >= int(values_.size())) invalid("unknown value");
-  Operation op{std::move(inflows), std::move(outflows), parse_expression(expression)};
+  return add_operation_expr(std::move(inflows), std::move(outflows), parse_expression(expression));
+}
+int PlanBuilder::add_loop_expr(LoopKind kind, const std::string& variable, IndexExpr start, IndexExpr stop,
+                               IndexExpr step, const std::vector<int>& body) {
+  require_open();
+  Statement s;
+  s.is_loop = true;
+  s.kind = kind;
+  s.domain = {variable, std::move(start), std::move(stop), std::move(step)};
+  for (int id : body) {
+    if (id < 0 || id >= int(nodes_.size())) invalid("unknown statement");
+    s.body.push_back(nodes_[id]);
+  }
+  nodes_.push_back(std::move(s));
+  return int(nodes_.size()) - 1;
+}
+int PlanBuilder::add_operation_expr(std::vector<int> inflows, std::vector<int> outflows, ExprPtr expression) {
+  require_open();
+  for (int v : inflows)
+    if (v < 0 || v >= int(values_.size())) invalid("unknown value");
+  for (int v : outflows)
+    if (v < 0 || v >= int(values_.size())) invalid("unknown value");
+  Operation op{std::move(inflows), std::move(outflows), std::move(expression)};
   operations_.push_back(std::move(op));
   Statement s;
   s.operation = int(operations_.size()) - 1;

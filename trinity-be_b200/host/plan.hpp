@@ -71,6 +71,7 @@ struct AccessIndex {
   bool operator==(const AccessIndex& o) const {
     return kind == o.kind && variable == o.variable && width == o.width;
   }
+  bool operator!=(const AccessIndex& o) const { return !(*this == o); }
 };
 
 struct TensorAccess {
@@ -87,7 +88,7 @@ using ExprPtr = std::shared_ptr<Expression>;
 struct Expression {
   enum Kind {
     ConstInt, ConstF32, Load, Store, Add, Sub, Mul, Div, Matmul, Max, Sqr, Sqrt, Sigmoid, Relu,
-    Exp, ReduceSum, ReduceMax, Broadcast, Unsqueeze, AllGather, AllReduce
+    Exp, Transpose, ReduceSum, ReduceMax, Broadcast, Unsqueeze, AllGather, AllReduce
   } kind = ConstInt;
   int64_t integer = 0;
   uint32_t f32_bits = 0;
@@ -164,6 +165,12 @@ class PlanBuilder {
 
   ExprPtr parse_expression(const std::string& text) const;
 
+  // Entry points for the text reader, which has already parsed its input.
+  int add_operation_expr(std::vector<int> inflows, std::vector<int> outflows, ExprPtr expression);
+  int add_loop_expr(LoopKind kind, const std::string& variable, IndexExpr start, IndexExpr stop, IndexExpr step,
+                    const std::vector<int>& body);
+  const std::vector<Value>& values() const { return values_; }
+
  private:
   void require_open() const;
   Target target_;
@@ -179,6 +186,10 @@ class PlanBuilder {
 std::vector<PhysicalPlan> lower_ir(const std::string& text, const std::map<std::string, int64_t>& symbols,
                                    const std::map<std::string, std::string>& dtypes, Target target,
                                    int world_size);
+
+// Decodes expression notation against `values`; `symbols` (may be null) resolves named integers.
+ExprPtr decode_expression(const Node& node, const std::vector<Value>& values,
+                          const std::map<std::string, int64_t>* symbols);
 
 std::string json_escape(const std::string& s);
 

@@ -1,3 +1,26 @@
-"""B200-native provider for Trinity Lowering's CUDA path (host-side mirror of the reference's
-``trinity_lowering`` Python package; the kernels live behind ``include/trinity_sm100.h``)."""
+"""B200-native provider for Trinity Lowering's CUDA path.
+
+Host-side mirror of the reference's ``trinity_lowering`` package: plans are built with
+``PhysicalPlanBuilder`` or ``lower_ir``, ``emit`` selects sm_100a kernels, ``compile`` builds a
+``program.so`` with the five-symbol artifact ABI, ``load`` / ``prepare`` / ``run`` / ``Graph`` execute
+it on PyTorch tensors.  ``trinity_lowering.kernels`` is the direct ctypes binding of the kernel
+library (``include/trinity_sm100.h``).
+"""
 from . import kernels  # noqa: F401
+from .compiler import (CompileConfig, CompileError, CudaArtifact, CudaSource, Implementation,
+                       PhysicalPlan, PhysicalPlanBuilder, all_gather_implementations,
+                       broadcast_implementations, compile, emit, gemm_implementations,
+                       kernel_candidates, lower_ir, pointwise_implementations,
+                       reduce_sum_implementations)
+from .errors import DistributedFailure, ResourceBusy, RuntimeFailure
+from .graph import Graph
+from .runtime import IOBuffers, LoadedModule, PreparedExecution, load
+from .world import World
+
+__all__ = [
+    "CompileConfig", "CompileError", "CudaArtifact", "CudaSource", "Implementation", "PhysicalPlan",
+    "PhysicalPlanBuilder", "all_gather_implementations", "pointwise_implementations",
+    "reduce_sum_implementations", "broadcast_implementations", "compile", "emit", "gemm_implementations",
+    "kernel_candidates", "lower_ir", "DistributedFailure", "ResourceBusy", "RuntimeFailure", "Graph",
+    "IOBuffers", "LoadedModule", "PreparedExecution", "load", "World", "kernels",
+]

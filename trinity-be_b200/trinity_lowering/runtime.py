@@ -1,0 +1,279 @@
+"""Loading compiled plans and running them on PyTorch tensors and streams.
+
+Importing this module does not initialise CUDA.  PyTorch supplies device memory, streams and
+events; validation of tensors against the artifact's buffer metadata happens here, everything
+after that (launch, completion, graph capture) in the C++ runtime.
+"""
+import ctypes
+import hashlib
+import json
+import threading
+from collections.abc import Mapping
+from dataclasses import dataclass
+from pathlib import Path
+from types import MappingProxyType
+
+from . import _host as h
+from .compiler import CudaArtifact
+from .errors import ResourceBusy
+from .metadata import TARGET_CAPABILITIES, freeze, manifest
+
+_TORCH_DTYPE = {"bf16": "bfloat16", "fp32": "float32"}
+
+
+def native():
+    """The host library (kept under the reference's accessor name)."""
+    return _Native
+
+
+class _Native:
+    @staticmethod
+    def collect_local():
+        return int(h.library().th_collect_local())
+
+    @staticmethod
+    def retire_pending():
+        return int(h.library().th_retire_pending())
+
+    @staticmethod
+    def cuda_version():
+        return h.library().th_cuda_runtime_version()
+
+
+def device_of(device, target="sm100"):
+    import torch
+    d = torch.device(device)
+    if d.type != "cuda":
+        raise ValueError("a CUDA device is required")
+    if d.index is None:
+        d = torch.device("cuda", torch.cuda.current_device())
+    if target not in TARGET_CAPABILITIES:
+        raise ValueError("unsupported artifact target")
+    if torch.cuda.get_device_capability(d) != TARGET_CAPABILITIES[target]:
+        raise ValueError(f"this artifact requires a {target} device")
+    return d
+
+
+def stream_of(device, stream=None, wait_for=()):
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream(device)
+    if not isinstance(stream, torch.cuda.Stream) or stream.device != device:
+        raise ValueError("stream must be a torch.cuda.Stream on the execution device")
+    events = tuple(wait_for)
+    if any(not isinstance(e, torch.cuda.Event) for e in events):
+        raise ValueError("wait_for must contain recorded CUDA events on the execution device")
+    for event in events:
+        stream.wait_event(event)
+    return stream
+
+
+def tensor_check(tensor, b, device, world=None):
+    """dtype, shape, stride, device, alignment and storage size against one buffer requirement."""
+    import torch
+    if not isinstance(tensor, torch.Tensor):
+        raise TypeError(f"binding {b.value} requires a Tensor")
+    if (tensor.device != device or tensor.layout != torch.strided
+            or tensor.dtype != getattr(torch, _TORCH_DTYPE[b.dtype])
+            or tuple(tensor.shape) != b.shape or tuple(tensor.stride()) != b.strides):
+        raise ValueError(f"binding {b.value}: dtype/shape/stride/device mismatch")
+    if torch.is_grad_enabled() and tensor.requires_grad:
+        raise ValueError("use no_grad or inference_mode for gradient Tensors")
+    available = tensor.untyped_storage().nbytes() - tensor.storage_offset() * tensor.element_size()
+    if tensor.data_ptr() % b.alignment or available < b.bytes:
+        raise ValueError(f"binding {b.value}: alignment/storage mismatch")
+    if b.symmetric and world is None:
+        raise ValueError(f"binding {b.value} requires this world's symmetric allocation")
+
+
+def resolve_bindings(req, inputs, out, device, world=None, allow_missing=False):
+    if not isinstance(inputs, Mapping):
+        raise TypeError("inputs must be a mapping of binding names to Tensors")
+    names = {name for b in req.buffers for name in b.input_names}
+    if set(inputs) - names or (not allow_missing and set(inputs) != names):
+        raise ValueError(f"expected exactly input names {sorted(names)}")
+    bound = {}
+    for b in req.buffers:
+        candidates = [inputs[name] for name in b.input_names if name in inputs]
+        if b.output_name is not None and out is not None:
+            candidates.append(out)
+        for tensor in candidates:
+            tensor_check(tensor, b, device, world)
+        if candidates:
+            if any(t.data_ptr() != candidates[0].data_ptr() for t in candidates[1:]):
+                raise ValueError("names referring to the same value must share one Tensor region")
+            bound[b.value] = candidates[0]
+    regions = [(t.data_ptr(), req.buffers[i].bytes) for i, t in bound.items()]
+    for i, (address, length) in enumerate(regions):
+        if any(address < other + size and other < address + length for other, size in regions[:i]):
+            raise ValueError("different canonical values overlap")
+    return bound
+
+
+@dataclass(frozen=True)
+class IOBuffers:
+    inputs: Mapping
+    output: object
+
+
+def outside_capture(device):
+    import torch
+    with torch.cuda.device(device):
+        if torch.cuda.is_current_stream_capturing():
+            raise ResourceBusy("load, prepare and Trinity allocation must finish before capture")
+
+
+class LoadedModule:
+    def __init__(self, handle, data, req, device, fingerprint):
+        self._handle, self._requirements, self._device = handle, req, device
+        self._manifest, self._fingerprint = freeze(data), fingerprint
+        self._closed = False
+        self._lock = threading.RLock()
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        try:
+            if handle:
+                h.library().th_module_free(handle)
+        except Exception:  # interpreter shutdown: the library wrapper is already gone
+            pass
+
+    requirements = property(lambda self: self._requirements)
+    manifest = property(lambda self: self._manifest)
+    device = property(lambda self: self._device)
+    world = property(lambda self: None)
+    fingerprint = property(lambda self: self._fingerprint)
+
+    def _open(self):
+        if self._closed:
+            raise RuntimeError("module is closed")
+
+    def _allocate(self, b):
+        import torch
+        # Over-allocated byte storage supports alignments stronger than the allocator's.
+        owner = torch.empty(b.bytes + b.alignment - 1, dtype=torch.uint8, device=self.device)
+        offset = (-owner.data_ptr()) % b.alignment
+        dtype = getattr(torch, _TORCH_DTYPE[b.dtype])
+        return owner[offset:offset + b.bytes].view(dtype).view(b.shape)
+
+    def _bindings(self, inputs, out, allow_missing=False):
+        self._open()
+        outside_capture(self.device)
+        return resolve_bindings(self.requirements, inputs, out, self.device, None, allow_missing)
+
+    def allocate_io(self, inputs=None):
+        with self._lock:
+            bound = self._bindings({} if inputs is None else inputs, None, True)
+            for b in self.requirements.buffers:
+                if b.external and b.value not in bound:
+                    bound[b.value] = self._allocate(b)
+            return IOBuffers(
+                MappingProxyType({name: bound[b.value] for b in self.requirements.buffers
+                                  for name in b.input_names}),
+                next(bound[b.value] for b in self.requirements.buffers if b.output_name is not None))
+
+    def prepare(self, inputs, out=None, workers=None):
+        import torch
+        with self._lock:
+            bound = self._bindings(inputs, out)
+            lib = h.library()
+            maximum = ctypes.c_uint(0)
+            with torch.cuda.device(self.device):
+                if lib.th_module_prepare(self._handle, ctypes.byref(maximum)) != 0:
+                    h.raise_last()
+            chosen = maximum.value if workers is None else workers
+            if type(chosen) is not int or not 1 <= chosen <= maximum.value:
+                raise ValueError(f"workers must be within [1, {maximum.value}]")
+            for b in self.requirements.buffers:
+                if b.value not in bound:
+                    bound[b.value] = self._allocate(b)
+            tensors = [bound[b.value] for b in self.requirements.buffers]
+            pointers = (ctypes.c_void_p * max(1, len(tensors)))(*[t.data_ptr() for t in tensors])
+            stream = torch.cuda.current_stream(self.device)
+            handle = h.check_ptr(lib.th_execution_create(self._handle, pointers, len(tensors),
+                                                         ctypes.c_void_p(stream.cuda_stream)))
+            output = next(bound[b.value] for b in self.requirements.buffers if b.output_name is not None)
+            named = {n: bound[b.value] for b in self.requirements.buffers for n in b.input_names}
+            return PreparedExecution(self, handle, named, tensors, output)
+
+    def close(self, wait=True):
+        with self._lock:
+            if not self._closed:
+                if h.library().th_module_close(self._handle) != 0:
+                    h.raise_last()
+                self._closed = True
+
+
+class PreparedExecution:
+    """A module bound to concrete tensors.  The tensors are kept alive here; their addresses and
+    storages must not change while the execution is open."""
+
+    def __init__(self, module, handle, inputs, tensors, output):
+        self._module, self._handle = module, handle
+        self._inputs = MappingProxyType(inputs)
+        self._tensors, self._output = tensors, output
+        self._snapshot = [(t.data_ptr(), t.untyped_storage().data_ptr()) for t in tensors]
+        self._closed = False
+        self._graph = None
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        try:
+            if handle:
+                h.library().th_execution_free(handle)
+        except Exception:  # interpreter shutdown: the library wrapper is already gone
+            pass
+
+    module = property(lambda self: self._module)
+    inputs = property(lambda self: self._inputs)
+    output = property(lambda self: self._output)
+    world = property(lambda self: None)
+
+    def _validate(self):
+        if self._closed:
+            raise RuntimeError("execution is closed")
+        for tensor, (address, storage) in zip(self._tensors, self._snapshot):
+            if tensor.data_ptr() != address or tensor.untyped_storage().data_ptr() != storage:
+                raise ValueError("a bound tensor's storage was replaced after prepare")
+
+    def run(self, stream=None, wait_for=()):
+        self._validate()
+        st = stream_of(self._module.device, stream, wait_for)
+        if h.library().th_execution_run(self._handle, ctypes.c_void_p(st.cuda_stream)) != 0:
+            h.raise_last()
+        return self._output
+
+    def wait(self, timeout=None):
+        if self._closed:
+            return
+        if h.library().th_execution_wait(self._handle, -1.0 if timeout is None else float(timeout)) != 0:
+            h.raise_last()
+
+    def close(self, wait=True):
+        if self._closed:
+            return
+        if h.library().th_execution_close(self._handle, 1 if wait else 0) != 0:
+            h.raise_last()
+        self._closed = True
+        self._inputs = MappingProxyType({})
+
+
+def load(artifact_or_directory, device, world=None):
+    """Loads an artifact (or a persisted artifact directory) onto ``device``."""
+    if world is not None:
+        raise NotImplementedError("Persistent (multi-rank) artifacts are not loaded by this runtime")
+    artifact = artifact_or_directory
+    directory = artifact.directory if isinstance(artifact, CudaArtifact) else Path(artifact)
+    data, req = manifest((directory / "manifest.json").read_text())
+    d = device_of(device, req.target)
+    outside_capture(d)
+    if req.nvshmem:
+        raise ValueError("artifact requires a matching world")
+    fingerprint = hashlib.sha256((directory / "source.cu").read_bytes()
+                                 + json.dumps(data["requirements"], sort_keys=True).encode()).hexdigest()
+    lib = h.library()
+    handle = h.check_ptr(lib.th_module_load(str(directory / "program.so").encode(), d.index, 1))
+    if json.loads(h.text(lib.th_module_requirements_json(handle))) != data["requirements"]:
+        lib.th_module_free(handle)
+        raise ValueError("artifact manifest differs from the loaded module")
+    return LoadedModule(handle, data, req, d, fingerprint)
