@@ -4,44 +4,64 @@
 //   P = exp(S - max) (online)                        FP32 in registers, BF16 back into TMEM
 //   O = P @ cache[:, :512] / sum(P)  [heads x 512]  tcgen05, FP32 accumulator in TMEM
 //
-// A 128-row FP32 accumulator for all 512 latent columns would fill TMEM by itself, so one CTA
-// owns one (batch, KV split, latent half): 256 accumulator columns, two 32-column score
-// buffers, and the first 384 query features as a TMEM-resident A operand (packed BF16 pairs).
-// The remaining 192 query features stay in shared memory, which leaves room for a four-stage
-// ring of 32-position cache chunks (each chunk is read from HBM once per latent half and
-// serves both products: K-major as the score operand, N-major as the value operand).
+// A 128-row FP32 accumulator for all 512 latent columns would fill TMEM by itself, and a
+// tcgen05.mma costs about 45 cycles however narrow it is, so the work of one (batch, KV split)
+// is shared by a cluster of two CTAs that split the *feature* axis:
 //
-//   warp 0    TMA producer (query tail boxes, then the cache chunk ring)
-//   warp 1    MMA issuer: QK(j) = 24 TMEM-A + 12 SMEM-A MMAs (N=32), PV(j-1) = 2 TMEM-A MMAs
-//             (N=256); scores of chunk j are issued before the values of chunk j-1 so the
-//             tensor pipe works while the softmax warps process chunk j-1
-//   warps 2-5 one thread per head: score load, running max / sum, conditional rescale of the
-//             accumulator, BF16 probabilities written over the score buffer, final epilogue
+//   CTA c owns latent columns [256c, 256c+256) and rope features [32c, 32c+32).
+//   scores:  each CTA contracts only its 288 features (18 K-steps, N = 64 positions) into a
+//            partial score tile.  The partial tiles are scaled into the log2 domain, rounded
+//            to FP16 and exchanged through distributed shared memory with a bulk asynchronous
+//            copy (16 KB per chunk and direction; the copy of chunk j+1 overlaps the softmax of
+//            chunk j); both CTAs add the same two rounded tiles, so they hold identical scores.
+//            FP16 halves the exchange, which measures ~18 B/clk per SM and would otherwise
+//            bound the kernel; it costs 2^-11 relative precision on each partial logit.
+//   values:  each CTA multiplies the (identical) probabilities with its own 256 latent
+//            columns, which are exactly the cache bytes it already loaded for the scores
+//
+// So every cache byte is loaded once per cluster (plus the 64-feature rope box, which both
+// CTAs load), no score FLOP is duplicated, and the query half (256 latent features) lives in
+// TMEM as the A operand.  TMEM: accumulator 256 columns, two 64-column score buffers, query
+// 128 columns.  Shared memory: three 40 KB cache stages, the query's rope box, two receive and
+// two send tiles of 16 KB.
+//
+//   warp 0    TMA producer (query rope box, then the cache chunk ring: 4 latent boxes + rope)
+//   warp 1    MMA issuer: QK(j) = 16 TMEM-A + 2 SMEM-A MMAs (N=64), PV(j-1) = 4 TMEM-A MMAs
+//             (N=256); scores of chunk j are issued before the values of chunk j-1
+//   warps 2-9 softmax group, two threads per head (32 positions of each chunk apiece):
+//             partial-score load, exchange with the peer CTA, running max / sum, conditional
+//             rescale of the accumulator, BF16 probabilities written over the score buffer,
+//             final epilogue
+//   warp 10   courier: acknowledges consumed exchange tiles to the peer CTA
 //
 // With kv_splits == 1 the CTA writes BF16 output directly.  Otherwise it writes a normalised
 // FP32 partial and its log-sum-exp to scratch and a small kernel merges the splits.
 // Algorithmic traffic: q + cache + out bytes; the scratch adds 2 * splits * batch * heads *
 // 513 * 4 bytes when splits > 1.
 #include "host_common.h"
+#include <cuda_fp16.h>
+
 #include "sm100_ptx.cuh"
 
 namespace trinity_sm100 {
 namespace {
 
-constexpr int kMlaThreads = 192;
-constexpr int kKv = 32;                       // cache positions per chunk
+constexpr int kSoftmaxWarps = 8;                 // two warps per TMEM lane quadrant: 32 positions each
+constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
+constexpr int kMlaThreads = 64 + kSoftmaxThreads + 32;  // producer, MMA issuer, softmax group, courier
+constexpr int kKv = 64;                        // cache positions per chunk
 constexpr int kDqk = 576, kDv = 512;
-constexpr int kBoxes = kDqk / 64;             // 9 feature boxes of 64
-constexpr int kKvStages = 4;
-constexpr int kChunkBytes = kKv * kDqk * 2;   // 36864
-constexpr int kBoxBytes = kKv * 128;          // 4096: one [32 x 64] box
-constexpr int kQTmemFeatures = 384;           // features [0, 384) live in TMEM
-constexpr int kQSmemBoxes = (kDqk - kQTmemFeatures) / 64;  // 3 boxes of [128 x 64]
-constexpr int kQBoxBytes = 128 * 128;
-constexpr int kMlaSmem = 1024 + kQSmemBoxes * kQBoxBytes + kKvStages * kChunkBytes + 256;
+constexpr int kKvStages = 3;
+constexpr int kBoxBytes = kKv * 128;           // 8192: one [64 positions x 64 features] box
+constexpr int kStageBoxes = 5;                 // 4 latent boxes of this CTA's half + rope box
+constexpr int kStageBytes = kStageBoxes * kBoxBytes;  // 40960
+constexpr int kQRopeBytes = 128 * 128;         // [128 heads x 64 rope features]
+constexpr int kXchgBytes = 128 * kKv * 2;      // one partial score tile in FP16: 16384
+// two receive tiles + two send tiles: the exchange of chunk j+1 overlaps the softmax of chunk j
+constexpr int kMlaSmem = 1024 + kQRopeBytes + kKvStages * kStageBytes + 4 * kXchgBytes + 256;
 // TMEM columns
-constexpr uint32_t kColO = 0, kColS = 256, kColQ = 320, kTmemCols = 512;
-constexpr float kRescaleThreshold = 8.0f;     // in log2 units: probabilities stay below 2^8
+constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384, kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;      // in log2 units: probabilities stay below 2^8
 
 struct MlaParams {
   const __nv_bfloat16* q;
@@ -51,6 +71,19 @@ struct MlaParams {
   int batch, heads, seq, splits;
   float scale_log2;
 };
+
+// Optional per-phase cycle counters of the softmax loop: a tuning harness that defines
+// TRINITY_MLA_TIMING reads g_mla_ticks; the library build compiles the hooks away.
+#ifdef TRINITY_MLA_TIMING
+__device__ unsigned long long g_mla_ticks[16];
+#define TRINITY_MLA_TICK_DECL long long tick_last = clock64(); unsigned long long tick_sum[12] = {};
+#define TRINITY_MLA_TICK(i) { const long long now = clock64(); tick_sum[i] += now - tick_last; tick_last = now; }
+#define TRINITY_MLA_TICK_FLUSH if (blockIdx.z == 0 && blockIdx.y == 0 && blockIdx.x == 0 && threadIdx.x == 64) { for (int i = 0; i < 12; ++i) g_mla_ticks[i] = tick_sum[i]; }
+#else
+#define TRINITY_MLA_TICK_DECL
+#define TRINITY_MLA_TICK(i)
+#define TRINITY_MLA_TICK_FLUSH
+#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -93,6 +126,59 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// ---- thread-block-cluster helpers (two CTAs per cluster)
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory offset in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_peer(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void st_peer_v4(uint32_t remote_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"r"(remote_addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+// Arrive on a barrier in the peer CTA; releases this thread's earlier peer stores.
+__device__ __forceinline__ void mbar_arrive_peer(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait that acquires at cluster scope (the arrivals come from the peer CTA).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint32_t site) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long start = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (clock64() - start > kWaitBudgetCycles) {
+      report_timeout(site);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Chunk range [first, first + count) of split `s` when `chunks` are dealt out evenly.
 __host__ __device__ inline void split_range(int chunks, int splits, int s, int& first, int& count) {
   const int base = chunks / splits, extra = chunks % splits;
@@ -104,25 +190,36 @@ __global__ void __launch_bounds__(kMlaThreads, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                   const __grid_constant__ CUtensorMap map_cache, const MlaParams p) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ float row_max[2 * 3 * 128];        // [part][chunk parity | 2 = final sums][head]
+  __shared__ unsigned read_count_storage;       // softmax warps that have read their receive tile
+  volatile unsigned* read_count = &read_count_storage;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t q_smem = smem_base;
-  const uint32_t kv_smem = smem_base + kQSmemBoxes * kQBoxBytes;
-  const uint32_t bar_base = kv_smem + kKvStages * kChunkBytes;
-  // barriers: kv_full[4], kv_empty[4], s_full[2], p_full[2], q_full, q_tmem, pv_done
+  const uint32_t q_smem = smem_base;                                  // query rope box
+  const uint32_t kv_smem = q_smem + kQRopeBytes;                      // cache stage ring
+  const uint32_t xchg_smem = kv_smem + kKvStages * kStageBytes;       // peer's partial scores land here
+  const uint32_t send_smem = xchg_smem + 2 * kXchgBytes;               // my partial scores, staged for the copy
+  const uint32_t bar_base = xchg_smem + 4 * kXchgBytes;
+  uint8_t* xchg = smem + kQRopeBytes + kKvStages * kStageBytes;
+  uint8_t* send = xchg + 2 * kXchgBytes;
+  // barriers: kv_full[3], kv_empty[3], s_full[2], p_full[2], x_full[2], x_empty[2], q_full,
+  //           q_tmem, pv_done
   auto kv_full = [&](int s) { return bar_base + 8u * s; };
   auto kv_empty = [&](int s) { return bar_base + 8u * (kKvStages + s); };
   auto s_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + b); };
   auto p_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + 2 + b); };
-  const uint32_t q_full = bar_base + 8u * (2 * kKvStages + 4);
-  const uint32_t q_tmem = bar_base + 8u * (2 * kKvStages + 5);
-  const uint32_t pv_done = bar_base + 8u * (2 * kKvStages + 6);
+  auto x_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + 4 + b); };
+  auto x_empty = [&](int b) { return bar_base + 8u * (2 * kKvStages + 6 + b); };
+  const uint32_t q_full = bar_base + 8u * (2 * kKvStages + 8);
+  const uint32_t q_tmem = bar_base + 8u * (2 * kKvStages + 9);
+  const uint32_t pv_done = bar_base + 8u * (2 * kKvStages + 10);
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(
-      smem + kQSmemBoxes * kQBoxBytes + kKvStages * kChunkBytes + 8 * (2 * kKvStages + 7));
+      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 11));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int half = blockIdx.x;   // latent half: columns [256*half, 256*half + 256)
+  const uint32_t half = cluster_rank();   // latent half and rope half owned by this CTA
+  const uint32_t peer = half ^ 1u;
   const int split = blockIdx.y;
   const int b = blockIdx.z;
 
@@ -131,16 +228,19 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
   split_range(total_chunks, p.splits, split, first_chunk, num_chunks);
 
   if (threadIdx.x == 0) {
+    read_count_storage = 0;
     for (int s = 0; s < kKvStages; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(s_full(i), 1);
-      mbar_init(p_full(i), 4);
+      mbar_init(p_full(i), kSoftmaxWarps);
+      mbar_init(x_full(i), 1);     // local arm (expect_tx) + the peer's bulk copy bytes
+      mbar_init(x_empty(i), 1);    // one arrival from the peer once all its threads have read
     }
     mbar_init(q_full, 1);
-    mbar_init(q_tmem, 4);
+    mbar_init(q_tmem, kSoftmaxWarps);
     mbar_init(pv_done, 1);
     mbar_fence_init();
     tma_prefetch_desc(&map_q);
@@ -152,25 +252,26 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0 && num_chunks > 0) {
-      mbar_arrive_expect_tx(q_full, kQSmemBoxes * kQBoxBytes);
-      for (int f = 0; f < kQSmemBoxes; ++f)
-        tma_load_3d(q_smem + f * kQBoxBytes, &map_q, q_full, kQTmemFeatures + f * 64, 0, b);
+      mbar_arrive_expect_tx(q_full, kQRopeBytes);
+      tma_load_3d(q_smem, &map_q, q_full, kDv, 0, b);
       for (int j = 0; j < num_chunks; ++j) {
         const int s = j % kKvStages;
         const uint32_t phase = (j / kKvStages) & 1u;
         if (!mbar_wait(kv_empty(s), phase ^ 1u, 0x401)) break;
-        mbar_arrive_expect_tx(kv_full(s), kChunkBytes);
+        mbar_arrive_expect_tx(kv_full(s), kStageBytes);
         const int kv0 = (first_chunk + j) * kKv;
+        const uint32_t dst = kv_smem + s * kStageBytes;
 #pragma unroll
-        for (int f = 0; f < kBoxes; ++f)
-          tma_load_3d(kv_smem + s * kChunkBytes + f * kBoxBytes, &map_cache, kv_full(s), f * 64,
-                      kv0, b);
+        for (int f = 0; f < 4; ++f)
+          tma_load_3d(dst + f * kBoxBytes, &map_cache, kv_full(s), int(half) * 256 + f * 64, kv0, b);
+        tma_load_3d(dst + 4 * kBoxBytes, &map_cache, kv_full(s), kDv, kv0, b);
       }
     }
   } else if (warp == 1) {
@@ -185,21 +286,22 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
           const int s = j % kKvStages;
           if (!mbar_wait(kv_full(s), (j / kKvStages) & 1u, 0x503)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t stage = kv_smem + s * kChunkBytes;
+          const uint32_t stage = kv_smem + s * kStageBytes;
           const uint32_t d_s = tmem_base + kColS + (j & 1) * kKv;
-          // scores: 36 K-steps of 16 features
+          // partial scores over this CTA's 256 latent features: query from TMEM
 #pragma unroll
-          for (int ks = 0; ks < kDqk / 16; ++ks) {
+          for (int ks = 0; ks < 16; ++ks) {
             const uint64_t b_desc =
                 umma_smem_desc(stage + (ks / 4) * kBoxBytes + (ks % 4) * 32, 16, 1024);
-            if (ks < kQTmemFeatures / 16) {
-              umma_bf16_ts(d_s, tmem_base + kColQ + ks * 8, b_desc, kIdescQK, ks != 0);
-            } else {
-              const int t = ks - kQTmemFeatures / 16;
-              const uint64_t a_desc =
-                  umma_smem_desc(q_smem + (t / 4) * kQBoxBytes + (t % 4) * 32, 16, 1024);
-              umma_bf16_ss(d_s, a_desc, b_desc, kIdescQK, 1u);
-            }
+            umma_bf16_ts(d_s, tmem_base + kColQ + ks * 8, b_desc, kIdescQK, ks != 0);
+          }
+          // ... and over its 32 rope features: query from shared memory
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const uint32_t off = (half * 2 + r) * 32;
+            const uint64_t a_desc = umma_smem_desc(q_smem + off, 16, 1024);
+            const uint64_t b_desc = umma_smem_desc(stage + 4 * kBoxBytes + off, 16, 1024);
+            umma_bf16_ss(d_s, a_desc, b_desc, kIdescQK, 1u);
           }
           umma_commit(s_full(j & 1));
         }
@@ -208,11 +310,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
           const int s = jj % kKvStages;
           if (!mbar_wait(p_full(jj & 1), (jj >> 1) & 1u, 0x504)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t stage = kv_smem + s * kChunkBytes + half * 4 * kBoxBytes;
+          const uint32_t stage = kv_smem + s * kStageBytes;
           const uint32_t a_p = tmem_base + kColS + (jj & 1) * kKv;
 #pragma unroll
           for (int ks = 0; ks < kKv / 16; ++ks) {
-            // values: N-major, 64-latent boxes 4096 B apart, 8-position groups 1024 B apart
+            // values: N-major, 64-latent boxes 8192 B apart, 8-position groups 1024 B apart
             const uint64_t b_desc = umma_smem_desc(stage + ks * 2048, kBoxBytes, 1024);
             umma_bf16_ts(tmem_base + kColO, a_p + ks * 8, b_desc, kIdescPV, (jj | ks) != 0);
           }
@@ -221,25 +323,51 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
     }
+  } else if (warp == 2 + kSoftmaxWarps) {
+    // ------------------------------------------------------------ courier
+    // Tells the peer that its tile in my receive buffer has been read by all softmax warps.
+    // A separate warp does it because a release at cluster scope costs close to a thousand
+    // cycles, which the softmax warps cannot afford on their critical path.
+    if (lane == 0) {
+      for (int j = 0; j < num_chunks; ++j) {
+        const unsigned target = unsigned(kSoftmaxWarps) * unsigned(j + 1);
+        const long long start = clock64();
+        bool seen = true;
+        while (*read_count < target) {
+          __nanosleep(32);
+          if (clock64() - start > kWaitBudgetCycles) {
+            report_timeout(0x701);
+            seen = false;
+            break;
+          }
+        }
+        if (!seen) break;
+        __threadfence_block();
+        mbar_arrive_peer(map_to_peer(x_empty(j & 1), peer));
+      }
+    }
   } else {
     // ------------------------------------------------------------ softmax / epilogue warps
+    // Warps 2..9.  Warp w reads TMEM lanes of quadrant (w & 3); warps w and w+4 share the
+    // quadrant's 32 heads and take positions [0,32) and [32,64) of every chunk.
     const int quad = warp & 3;
+    const int part = (warp - 2) >> 2;              // which 32 positions of a chunk
     const int row = quad * 32 + lane;              // head index
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const bool live = row < p.heads;
     if (num_chunks > 0) {
-      // Query features [0, 384) -> TMEM as packed BF16 pairs (word c = features 2c, 2c+1).
+      // This CTA's 256 latent query features -> TMEM as packed BF16 pairs (128 per thread).
       const uint4* qrow = reinterpret_cast<const uint4*>(
-          p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk);
+          p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk + half * 256 + part * 128);
 #pragma unroll 1
-      for (int c = 0; c < kQTmemFeatures / 64; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t w[32];
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
           uint4 x = live ? __ldg(qrow + c * 8 + v) : make_uint4(0, 0, 0, 0);
           w[v * 4 + 0] = x.x; w[v * 4 + 1] = x.y; w[v * 4 + 2] = x.z; w[v * 4 + 3] = x.w;
         }
-        tmem_st_32x32b_x32(lane_base + kColQ + c * 32, w);
+        tmem_st_32x32b_x32(lane_base + kColQ + part * 64 + c * 32, w);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -247,46 +375,130 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
       if (lane == 0) mbar_arrive(q_tmem);
     }
 
-    float m_ref = -INFINITY;   // reference maximum (log2 domain, scaled)
-    float l = 0.0f;            // running sum of probabilities relative to m_ref
-    bool ok = true;
-    for (int j = 0; j < num_chunks && ok; ++j) {
-      if (!mbar_wait(s_full(j & 1), (j >> 1) & 1u, 0x601)) { ok = false; break; }
+    float m_ref = -INFINITY;   // reference maximum (log2 domain, scaled); identical in both parts
+    float l = 0.0f;            // running sum over this thread's positions, relative to m_ref
+    // A wait that gives up only sets `bad`: the thread keeps executing the warp- and
+    // group-collective instructions (on meaningless data) and all softmax threads leave together
+    // at the next vote, so no barrier or collective is ever left half-attended.
+    bool bad = false;
+    TRINITY_MLA_TICK_DECL
+
+    // Reads this thread's 32 partial scores of chunk c from TMEM, scales them into the log2
+    // domain, rounds to FP16 pairs (both CTAs use the rounded value, so they add identical
+    // numbers), stages them in shared memory ([8 groups of 8 positions][128 rows], conflict-free)
+    // and has one thread start the bulk asynchronous copy into the peer's receive tile.
+    auto stage_and_send = [&](int c, uint32_t (&own)[16]) -> bool {
+      const int buf = c & 1;
+      const uint32_t phase = (c >> 1) & 1u;
+      TRINITY_MLA_TICK(0)
+      if (!bad) bad = !mbar_wait(s_full(buf), phase, 0x601);
+      TRINITY_MLA_TICK(1)
       tc_fence_after();
-      const uint32_t s_addr = lane_base + kColS + (j & 1) * kKv;
       uint32_t sv[32];
-      tmem_ld_32x32b_x32(s_addr, sv);
+      tmem_ld_32x32b_x32(lane_base + kColS + buf * kKv + part * 32, sv);
       tmem_ld_wait();
-      const int valid = p.seq - (first_chunk + j) * kKv;  // positions of this chunk inside seq
-      float t[32];
-      float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        t[i] = i < valid ? __uint_as_float(sv[i]) * p.scale_log2 : -INFINITY;
-        mx = fmaxf(mx, t[i]);
+      for (int i = 0; i < 16; ++i) {
+        const __half2 h = __floats2half2_rn(__uint_as_float(sv[2 * i]) * p.scale_log2,
+                                            __uint_as_float(sv[2 * i + 1]) * p.scale_log2);
+        own[i] = *reinterpret_cast<const uint32_t*>(&h);
       }
+      TRINITY_MLA_TICK(2)
+      if (!bad) bad = !mbar_wait_cluster(x_empty(buf), phase ^ 1u, 0x604);
+      TRINITY_MLA_TICK(3)
+      uint4* staged = reinterpret_cast<uint4*>(send + buf * kXchgBytes);
+      if (!bad) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          staged[(part * 4 + g) * 128 + row] = make_uint4(own[4 * g], own[4 * g + 1], own[4 * g + 2], own[4 * g + 3]);
+      }
+      fence_async_smem();
+      uint32_t all_good;
+      asm volatile(
+          "{\n"
+          ".reg .pred p, q;\n"
+          "setp.eq.u32 p, %1, 0;\n"
+          "bar.red.and.pred q, 1, 256, p;\n"   // CTA barrier 1 over the softmax threads + vote
+          "selp.u32 %0, 1, 0, q;\n"
+          "}\n"
+          : "=r"(all_good)
+          : "r"(bad ? 1u : 0u)
+          : "memory");
+      if (all_good && warp == 2 && lane == 0) {
+        mbar_arrive_expect_tx(x_full(buf), kXchgBytes);
+        asm volatile(
+            "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+            ::"r"(map_to_peer(xchg_smem + buf * kXchgBytes, peer)), "r"(send_smem + buf * kXchgBytes),
+              "r"(kXchgBytes), "r"(map_to_peer(x_full(buf), peer))
+            : "memory");
+      }
+      TRINITY_MLA_TICK(4)
+      return all_good != 0;
+    };
+
+    uint32_t cur[16], nxt[16];
+    bool running = num_chunks > 0 && stage_and_send(0, cur);
+    if (num_chunks > 0 && !running) bad = true;
+    for (int j = 0; running && j < num_chunks; ++j) {
+      const int buf = j & 1;
+      const uint32_t use_phase = (j >> 1) & 1u;
+      if (j + 1 < num_chunks && !stage_and_send(j + 1, nxt)) {
+        bad = true;
+        break;
+      }
+      if (!bad) bad = !mbar_wait_cluster(x_full(buf), use_phase, 0x605);
+      TRINITY_MLA_TICK(5)
+      const uint4* mine = reinterpret_cast<const uint4*>(xchg + buf * kXchgBytes);
+      const int valid = p.seq - (first_chunk + j) * kKv - part * 32;  // my positions inside seq
+      float t[32];
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint4 other = mine[(part * 4 + g) * 128 + row];
+        const uint32_t theirs[4] = {other.x, other.y, other.z, other.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&cur[4 * g + e]));
+          const float2 c2 = __half22float2(*reinterpret_cast<const __half2*>(&theirs[e]));
+          const int i = g * 8 + e * 2;
+          t[i] = i < valid ? a.x + c2.x : -INFINITY;
+          t[i + 1] = i + 1 < valid ? a.y + c2.y : -INFINITY;
+          mx4[e] = fmaxf(mx4[e], fmaxf(t[i], t[i + 1]));
+        }
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // this warp has read the receive tile; the courier acknowledges once all eight have
+      __syncwarp();
+      if (lane == 0) atomicAdd(const_cast<unsigned*>(read_count), 1u);
+      // the row maximum spans both parts
+      row_max[(part * 3 + buf) * 128 + row] = mx;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      mx = fmaxf(mx, row_max[((part ^ 1) * 3 + buf) * 128 + row]);
+      TRINITY_MLA_TICK(6)
+
       const bool grow = mx > m_ref + kRescaleThreshold;   // always true for the first chunk
       if (__any_sync(0xffffffffu, grow)) {
         const float new_ref = grow ? mx : m_ref;
         const float f = (grow && j > 0) ? fast_exp2(m_ref - new_ref) : 1.0f;
         if (j > 0) {
           // The accumulator may only be touched once the values of chunk j-1 have landed.
-          if (!mbar_wait(pv_done, (j - 1) & 1u, 0x602)) { ok = false; break; }
+          if (!bad) bad = !mbar_wait(pv_done, (j - 1) & 1u, 0x602);
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < 256; c += 32) {
+          for (int c = 0; c < 128; c += 32) {   // this part's 128 accumulator columns
             uint32_t o[32];
-            tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+            tmem_ld_32x32b_x32(lane_base + kColO + part * 128 + c, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st_32x32b_x32(lane_base + kColO + c, o);
+            tmem_st_32x32b_x32(lane_base + kColO + part * 128 + c, o);
           }
           tmem_st_wait();
           l *= f;
         }
         m_ref = new_ref;
       }
+      TRINITY_MLA_TICK(7)
       uint32_t pw[16];
       float sum = 0.0f;
 #pragma unroll
@@ -297,23 +509,34 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         pw[i] = pack_bf16x2(p0, p1);
       }
       l += sum;
-      tmem_st_32x32b_x16(s_addr, pw);   // probabilities overwrite the first 16 score columns
+      // probabilities overwrite the scores: positions [32 part, 32 part + 32) -> 16 columns
+      tmem_st_32x32b_x16(lane_base + kColS + buf * kKv + part * 16, pw);
       tmem_st_wait();
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(j & 1));
+      const bool warp_good = __all_sync(0xffffffffu, !bad);
+      if (lane == 0 && warp_good) mbar_arrive(p_full(buf));
+#pragma unroll
+      for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
+      TRINITY_MLA_TICK(8)
     }
+    TRINITY_MLA_TICK_FLUSH
 
-    if (num_chunks > 0 && ok && mbar_wait(pv_done, (num_chunks - 1) & 1u, 0x603)) {
+    bool ready = num_chunks > 0 && !bad;
+    if (ready) ready = mbar_wait(pv_done, (num_chunks - 1) & 1u, 0x603);
+    // the two parts of a row add their sums of probabilities
+    row_max[(part * 3 + 2) * 128 + row] = l;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    l += row_max[((part ^ 1) * 3 + 2) * 128 + row];
+    if (__all_sync(0xffffffffu, ready)) {
       tc_fence_after();
       const float inv_l = 1.0f / l;
       if (p.splits == 1) {
         __nv_bfloat16* orow =
-            p.out + (static_cast<long long>(b) * p.heads + row) * kDv + half * 256;
+            p.out + (static_cast<long long>(b) * p.heads + row) * kDv + half * 256 + part * 128;
 #pragma unroll 1
-        for (int c = 0; c < 256; c += 32) {
+        for (int c = 0; c < 128; c += 32) {
           uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+          tmem_ld_32x32b_x32(lane_base + kColO + part * 128 + c, o);
           tmem_ld_wait();
           if (live) {
 #pragma unroll
@@ -329,11 +552,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       } else {
         const long long slot = (static_cast<long long>(b) * p.splits + split) * p.heads + row;
-        float* prow = p.partial_o + slot * kDv + half * 256;
+        float* prow = p.partial_o + slot * kDv + half * 256 + part * 128;
 #pragma unroll 1
-        for (int c = 0; c < 256; c += 32) {
+        for (int c = 0; c < 128; c += 32) {
           uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+          tmem_ld_32x32b_x32(lane_base + kColO + part * 128 + c, o);
           tmem_ld_wait();
           if (live) {
 #pragma unroll
@@ -344,13 +567,16 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
             }
           }
         }
-        if (live && half == 0) p.partial_lse[slot] = m_ref + log2f(l);
+        if (live && half == 0 && part == 0) p.partial_lse[slot] = m_ref + log2f(l);
       }
     }
   }
 
+  // Common exit.  Neither CTA of the pair may leave while the other can still write into its
+  // shared memory or arrive on its barriers, hence the cluster-wide barrier.
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();
   if (warp == 2) {
     if (g_device_status != 0)
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -401,7 +627,7 @@ extern "C" size_t trinity_sm100_mla_scratch_bytes(int32_t batch, int32_t heads, 
 }
 
 extern "C" int trinity_sm100_mla_default_splits(int32_t batch, int32_t seq) {
-  // Two CTAs (latent halves) per (batch, split); aim for about one CTA per SM without
+  // Two CTAs (feature halves) per (batch, split); aim for about one CTA per SM without
   // splitting a sequence more finely than 512 positions per split.
   int sms = 148;
   int device = 0;
@@ -476,8 +702,21 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   p.seq = a.seq;
   p.splits = splits;
   p.scale_log2 = a.scale * 1.4426950408889634f;
-  dim3 grid(2, splits, a.batch);
-  mla_decode_kernel<<<grid, kMlaThreads, kMlaSmem, stream>>>(map_q, map_cache, p);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(2, splits, a.batch);
+  config.blockDim = dim3(kMlaThreads);
+  config.dynamicSmemBytes = kMlaSmem;
+  config.stream = stream;
+  cudaLaunchAttribute cluster;
+  cluster.id = cudaLaunchAttributeClusterDimension;
+  cluster.val.clusterDim.x = 2;   // the two feature halves of one (batch, split)
+  cluster.val.clusterDim.y = 1;
+  cluster.val.clusterDim.z = 1;
+  config.attrs = &cluster;
+  config.numAttrs = 1;
+  cudaError_t launch_error = cudaLaunchKernelEx(&config, mla_decode_kernel, map_q, map_cache, p);
+  if (launch_error != cudaSuccess)
+    return fail(TRINITY_SM100_E_CUDA, "mla_decode launch: %s", cudaGetErrorString(launch_error));
   count_launch();
   if ((rc = check_launch("mla_decode"))) return rc;
   if (splits > 1) {

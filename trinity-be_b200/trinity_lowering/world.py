@@ -64,10 +64,12 @@ class World:
 
     # ------------------------------------------------------------------ control plane
     def _beat(self):
-        while not self._stop.wait(min(1.0, self.timeout / 4)):
+        while True:
             try:
                 self._store.set(f"beat{self.rank}", str(time.time()))
             except Exception:
+                return
+            if self._stop.wait(min(1.0, self.timeout / 4)):
                 return
 
     def check_peers(self):
@@ -79,9 +81,11 @@ class World:
             if peer == self.rank:
                 continue
             try:
+                if not self._store.check([f"beat{peer}"]):
+                    continue  # the peer has not published yet (a plain get would block)
                 seen = float(self._store.get(f"beat{peer}"))
             except Exception:
-                continue  # the peer has not published yet
+                continue
             if now - seen > self.timeout:
                 self._fail(f"rank {peer} stopped responding")
                 raise DistributedFailure(self._failed)
