@@ -263,6 +263,27 @@ TRINITY_SM100_API size_t trinity_sm100_allreduce_flag_words(void);
 TRINITY_SM100_API int trinity_sm100_allreduce_bf16(const trinity_sm100_allreduce* args, void* stream);
 
 /*
+ * Row-parallel GEMM with the sum all-reduce fused into its epilogue:
+ *   out (on every rank) = sum over ranks of A_rank[m,k] @ B_rank[k,n]        BF16, FP32 accumulate
+ * Every rank calls this with its own shard (`gemm`: no bias, no activation, BF16 out) and the
+ * same peer tables (`reduce`: peers[r] = rank r's [m,n] output buffer, peers[rank] == gemm->out;
+ * flags[r] = rank r's flag pad of at least trinity_sm100_gemm_allreduce_flag_words() zeroed
+ * words; epoch strictly increasing per call).  Inside one persistent kernel the epilogue warps
+ * store their partial tile, signal the tile's owner rank, and - one tile behind, so the wait
+ * is short and the NVLink traffic overlaps the next tile's MMAs - the owner adds the partials
+ * of its tiles in rank order in FP32 and pushes the rounded result into every rank's buffer
+ * over NVLink with 128-bit peer loads / stores.  All waits are bounded.  No NVSHMEM, no NCCL,
+ * no multicast.
+ *
+ * The reference has no all-reduce (its plan language only has all_gather,
+ * src/analysis/plan/expression.rs:227-231) and its multi-rank emission is unimplemented
+ * (src/emit/native/mod.rs:161-165); this entry point is what a tensor-parallel MLP needs.
+ */
+TRINITY_SM100_API size_t trinity_sm100_gemm_allreduce_flag_words(int64_t m, int64_t n, int32_t world);
+TRINITY_SM100_API int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* gemm,
+                                      const trinity_sm100_allreduce* reduce, void* stream);
+
+/*
  * Device status word: 0 while every bounded in-kernel wait has completed; otherwise the code
  * of the first wait that gave up (site id in the low 16 bits).  Reading synchronises the
  * device.  `clear` != 0 resets it afterwards.

@@ -23,10 +23,12 @@ def main():
     m, d_model, d_ff = 512, 1024, 2048
     x, wg, wu, wd = wl.mlp_inputs(m, d_model, d_ff, 1238)
     shards = [t.to(dev) for t in TensorParallelMLP.shard_weights(wg, wu, wd, world.rank, world.size)]
-    mlp = TensorParallelMLP(world, m, d_model, d_ff, *shards)
+    variants = [TensorParallelMLP(world, m, d_model, d_ff, *shards, fused=True),
+                TensorParallelMLP(world, m, d_model, d_ff, *shards, fused=False)]
     xd = x.to(dev)
     expected = None
-    for step in range(3):  # repeated steps reuse the flags with a growing epoch
+    for step in range(6):  # repeated steps reuse the flags with a growing epoch
+        mlp = variants[step % 2]
         out = mlp.forward(xd)
         torch.cuda.synchronize()
         assert k.device_status() == 0
@@ -40,6 +42,8 @@ def main():
         # two chained GEMMs with a BF16 hidden activation: the path's stated bar (rel-L2 <= 1e-2,
         # max-abs <= 2e-2); a one-ulp flip in H moves small outputs by more than one ulp
         assert_close_bf16(out.cpu(), expected, max_ulp=None, max_abs=2e-2)
+        if step == 1:   # fused and unfused add the same BF16 partials in the same order
+            assert torch.equal(variants[0].output, variants[1].output)
         world.barrier()
     # plain all-reduce of a ragged matrix against an FP32 sum
     buffer = world.allocate((301, 264), torch.bfloat16)

@@ -32,40 +32,6 @@ struct AllReduceParams {
   uint32_t epoch;
 };
 
-__device__ __forceinline__ void flag_store(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t flag_load(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-// Epoch comparison that tolerates wrap-around.
-__device__ __forceinline__ bool reached(uint32_t seen, uint32_t epoch) {
-  return static_cast<int32_t>(seen - epoch) >= 0;
-}
-__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t epoch, uint32_t site) {
-  if (reached(flag_load(p), epoch)) return true;
-  const long long start = clock64();
-  for (;;) {
-    for (int i = 0; i < 32; ++i) {
-      if (reached(flag_load(p), epoch)) return true;
-      __nanosleep(64);
-    }
-    if (clock64() - start > kWaitBudgetCycles) {
-      report_timeout(site);
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ uint4 peer_load(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
 __device__ __forceinline__ void slice_range(long long vectors, int world, int r, long long& lo,
                                             long long& hi) {
   const long long base = vectors / world, extra = vectors % world;

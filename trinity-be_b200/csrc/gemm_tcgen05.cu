@@ -27,6 +27,16 @@ constexpr int kStageBytesA = kBM * kBK * 2;
 constexpr int kStoreBufBytes = 32 * 128;  // 32 rows x 128 B per epilogue warp
 constexpr int kStagingBytes = 4 * 2 * kStoreBufBytes;
 
+// Peer-mapped output buffers and flag pads for the fused all-reduce epilogue.
+constexpr int kGemmMaxWorld = 8;
+struct GemmPeers {
+  uint4* buffers[kGemmMaxWorld];   // the [M,N] BF16 output on every rank (buffers[rank] is local)
+  uint32_t* flags[kGemmMaxWorld];  // flag pads: ready[tile][source rank], done[rank], counter
+  int world, rank;
+  uint32_t epoch;
+  long long ld_vectors;            // output row pitch in 16-byte vectors
+};
+
 struct GemmParams {
   const __nv_bfloat16* bias;
   long long ld_bias;
@@ -61,12 +71,68 @@ __device__ __forceinline__ float apply_activation(float x, int activation) {
   return x;
 }
 
-template <int kBN, int kStages, bool kGated, bool kOutF32>
+// Fused all-reduce duty of the epilogue warps (128 threads, `tid` in [0,128)): the rank that
+// owns tile `tile` waits until every rank has stored its partial of that tile, adds the
+// partials in rank order in FP32, rounds once and pushes the result into every rank's buffer.
+// Returns false if a wait gave up (uniform over the 128 threads).
+template <int kBN>
+__device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const GemmPeers& peers, int tile,
+                                                  int m0, int n0, int tid) {
+  uint32_t good = 1;
+  if (tid < peers.world)
+    good = wait_flag(peers.flags[peers.rank] + static_cast<long long>(tile) * peers.world + tid, peers.epoch,
+                     0x801) ? 1u : 0u;
+  uint32_t all_good;
+  asm volatile(
+      "{\n"
+      ".reg .pred a, b;\n"
+      "setp.ne.u32 a, %1, 0;\n"
+      "bar.red.and.pred b, 1, 128, a;\n"
+      "selp.u32 %0, 1, 0, b;\n"
+      "}\n"
+      : "=r"(all_good)
+      : "r"(good)
+      : "memory");
+  if (!all_good) return false;
+  constexpr int kVecPerRow = kBN / 8;
+#pragma unroll 1
+  for (int idx = tid; idx < kBM * kVecPerRow; idx += 128) {
+    const int row = m0 + idx / kVecPerRow;
+    const int col = n0 + (idx % kVecPerRow) * 8;
+    if (row >= p.m || col >= p.n) continue;
+    const long long v = static_cast<long long>(row) * peers.ld_vectors + (col >> 3);
+    uint4 part[kGemmMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kGemmMaxWorld; ++r)
+      if (r < peers.world) part[r] = peer_load(peers.buffers[r] + v);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int r = 0; r < kGemmMaxWorld; ++r) {
+      if (r < peers.world) {
+        const uint32_t w[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] += bf16_lo(w[e]);
+          acc[2 * e + 1] += bf16_hi(w[e]);
+        }
+      }
+    }
+    const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                               pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+#pragma unroll
+    for (int r = 0; r < kGemmMaxWorld; ++r)
+      if (r < peers.world) peer_store(peers.buffers[r] + v, o);
+  }
+  return true;
+}
+
+template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_b2,
-                         const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
+                         const __grid_constant__ CUtensorMap map_out, const GemmParams p,
+                         const GemmPeers peers) {
   constexpr int kOutN = kGated ? kBN / 2 : kBN;      // output columns per tile
   constexpr int kStage = stage_bytes<kBN>();
   constexpr int kChunksB = kBN / 64;                 // 64-column TMA boxes per stage
@@ -186,6 +252,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t local_tile = 0;
     uint32_t store_buf = 0;
     bool ok = true;
+    const int etid = threadIdx.x - 64;      // 0..127 within the epilogue group
+    int owed_tile = -1, owed_m0 = 0, owed_n0 = 0;   // fused all-reduce: duty carried one tile behind
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
@@ -193,7 +261,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const int n0 = n_blk * kOutN;
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_phase = (local_tile >> 1) & 1u;
-      if (!mbar_wait(tmem_full_bar(acc), acc_phase, 0x301)) { ok = false; break; }
+      if (kFused) {
+        // a give-up must be uniform over the group because the fused path uses group barriers
+        uint32_t good = mbar_wait(tmem_full_bar(acc), acc_phase, 0x301) ? 1u : 0u, all_good;
+        asm volatile(
+            "{\n"
+            ".reg .pred a, b;\n"
+            "setp.ne.u32 a, %1, 0;\n"
+            "bar.red.and.pred b, 1, 128, a;\n"
+            "selp.u32 %0, 1, 0, b;\n"
+            "}\n"
+            : "=r"(all_good)
+            : "r"(good)
+            : "memory");
+        if (!all_good) { ok = false; break; }
+      } else if (!mbar_wait(tmem_full_bar(acc), acc_phase, 0x301)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
@@ -311,8 +393,46 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+      if (kFused) {
+        // This rank's partial of the tile is complete in memory -> tell the tile's owner, then do
+        // the reduction this CTA still owes for its previous tile (peers have had a whole tile
+        // time to finish theirs, so the wait inside is short).
+        if (lane == 0) {
+          tma_store_wait_all();
+          __threadfence_system();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (etid == 0)
+          flag_store(peers.flags[tile % peers.world] + static_cast<long long>(tile) * peers.world + peers.rank,
+                     peers.epoch);
+        if (owed_tile >= 0 && owed_tile % peers.world == peers.rank)
+          ok = reduce_owned_tile<kBN>(p, peers, owed_tile, owed_m0, owed_n0, etid);
+        owed_tile = tile;
+        owed_m0 = m0;
+        owed_n0 = n0;
+      }
     }
     if (lane == 0) tma_store_wait_all();
+    if (kFused) {
+      if (ok && owed_tile >= 0 && owed_tile % peers.world == peers.rank)
+        ok = reduce_owned_tile<kBN>(p, peers, owed_tile, owed_m0, owed_n0, etid);
+      // Retire: once every CTA of this rank has pushed its tiles, tell the peers; the last CTA
+      // stays until every peer has said the same, so the output is complete when the kernel ends.
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (etid == 0) {
+        uint32_t* mine = peers.flags[peers.rank] + static_cast<long long>(p.num_tiles) * peers.world;
+        const unsigned prev = atomicAdd(mine + kGemmMaxWorld, 1u);
+        if (prev == gridDim.x - 1) {
+          mine[kGemmMaxWorld] = 0;
+          __threadfence_system();
+          for (int r = 0; r < peers.world; ++r)
+            flag_store(peers.flags[r] + static_cast<long long>(p.num_tiles) * peers.world + peers.rank, peers.epoch);
+          for (int r = 0; r < peers.world; ++r)
+            if (!wait_flag(mine + r, peers.epoch, 0x802)) break;
+        }
+      }
+    }
   }
 
   // Common exit: every role leaves its loop (normally or after a wait gave up) and meets here.
@@ -328,12 +448,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
-template <int kBN, int kStages, bool kGated, bool kOutF32>
-int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream) {
+template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false>
+int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, const GemmPeers* fused = nullptr) {
   constexpr int kOutN = kGated ? kBN / 2 : kBN;
   constexpr int kSmem = gemm_smem_bytes<kBN, kStages>();
   static_assert(kSmem <= 232448, "exceeds the 227 KB shared-memory limit");
-  auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32>;
+  auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused>;
   static bool configured[64] = {};
   int device = 0;
   cudaGetDevice(&device);
@@ -368,7 +488,9 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream) 
   p.num_tiles = p.tiles_m * p.tiles_n;
   p.num_kb = int((g.k + kBK - 1) / kBK);
   const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
-  kernel<<<grid, kGemmThreads, kSmem, stream>>>(map_a, map_b, map_b2, map_out, p);
+  GemmPeers peers = {};
+  if (fused) peers = *fused;
+  kernel<<<grid, kGemmThreads, kSmem, stream>>>(map_a, map_b, map_b2, map_out, p, peers);
   count_launch();
   return check_launch("gemm_bf16_tcgen05");
 }
@@ -426,4 +548,48 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
   }
   return f32 ? launch_gemm<128, 6, false, true>(g, sm_count, stream)
              : launch_gemm<128, 6, false, false>(g, sm_count, stream);
+}
+
+extern "C" size_t trinity_sm100_gemm_allreduce_flag_words(int64_t m, int64_t n, int32_t world) {
+  if (m <= 0 || n <= 0 || world <= 0) return 0;
+  const size_t tiles = size_t((m + kBM - 1) / kBM) * size_t((n + 255) / 256);
+  return tiles * size_t(world) + kGemmMaxWorld + 8;
+}
+
+extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
+                                                 const trinity_sm100_allreduce* reduce, void* stream_handle) {
+  if (!args || !reduce) return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: null argument block");
+  const trinity_sm100_gemm& g = *args;
+  const trinity_sm100_allreduce& r = *reduce;
+  if (!g.a || !g.b || !g.out) return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: null operand");
+  if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.m > INT32_MAX || g.n > INT32_MAX || g.k > INT32_MAX)
+    return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: extents must be in [1, 2^31)");
+  if (g.activation != TRINITY_SM100_ACT_NONE || g.bias_mode != TRINITY_SM100_BIAS_NONE ||
+      g.out_dtype != TRINITY_SM100_BF16)
+    return fail(TRINITY_SM100_E_UNSUPPORTED,
+                "gemm_allreduce: the partial products are summed across ranks, so no bias or activation, BF16 out");
+  if (g.lda % 8 || g.ldb % 8 || g.ldo % 8 || g.n % 8 || g.lda < g.k || g.ldb < g.n || g.ldo < g.n)
+    return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: pitches and n must be multiples of 8 elements");
+  if (!r.peers || !r.flags || r.world < 1 || r.world > kGemmMaxWorld || r.rank < 0 || r.rank >= r.world)
+    return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: world %d / rank %d or pointer tables invalid", r.world, r.rank);
+  if (r.rows != g.m || r.cols != g.n)
+    return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: reduce extents differ from the output");
+  GemmPeers peers = {};
+  for (int i = 0; i < r.world; ++i) {
+    if (!r.peers[i] || !r.flags[i] || !aligned16(r.peers[i]) || !aligned16(r.flags[i]))
+      return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: peer %d pointer null or misaligned", i);
+    peers.buffers[i] = static_cast<uint4*>(r.peers[i]);
+    peers.flags[i] = static_cast<uint32_t*>(r.flags[i]);
+  }
+  if (r.peers[r.rank] != g.out)
+    return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: out must be this rank's entry of the peer table");
+  if (!aligned16(g.a) || !aligned16(g.b)) return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: operands must be 16-byte aligned");
+  peers.world = r.world;
+  peers.rank = r.rank;
+  peers.epoch = r.epoch;
+  peers.ld_vectors = g.ldo / 8;
+  int sm_count = 0;
+  if (int rc = require_sm100(&sm_count)) return rc;
+  // every CTA of the persistent grid is resident (one per SM), which the flag waits rely on
+  return launch_gemm<256, 4, false, false, true>(g, sm_count, static_cast<cudaStream_t>(stream_handle), &peers);
 }

@@ -26,6 +26,13 @@ EXPORTS = (
     "trinity_sm100_mla_decode_bf16_noalloc",
     "trinity_sm100_allreduce_flag_words",
     "trinity_sm100_allreduce_bf16",
+    "trinity_sm100_gemm_allreduce_flag_words",
+    "trinity_sm100_gemm_allreduce_bf16",
+    "trinity_sm100_pointwise",
+    "trinity_sm100_row_reduce_sum",
+    "trinity_sm100_prepare_device",
+    "trinity_sm100_current_device",
+    "trinity_sm100_stream_synchronize",
     "trinity_sm100_device_status",
     "trinity_sm100_abi_version",
     "trinity_sm100_last_error",
@@ -105,6 +112,10 @@ def library():
             lib.trinity_sm100_allreduce_flag_words.restype = ctypes.c_size_t
             lib.trinity_sm100_allreduce_bf16.argtypes = [
                 ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
+            lib.trinity_sm100_gemm_allreduce_flag_words.argtypes = [ctypes.c_int64, ctypes.c_int64, ctypes.c_int32]
+            lib.trinity_sm100_gemm_allreduce_flag_words.restype = ctypes.c_size_t
+            lib.trinity_sm100_gemm_allreduce_bf16.argtypes = [
+                ctypes.POINTER(GemmArgs), ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
             lib.trinity_sm100_device_status.argtypes = [
                 ctypes.POINTER(ctypes.c_uint32), ctypes.c_int]
             lib.trinity_sm100_last_error.restype = ctypes.c_char_p
@@ -288,3 +299,33 @@ def allreduce(peer_ptrs, flag_ptrs, rows, cols, rank, epoch, stream=None):
     args.flags = ctypes.cast(flags, ctypes.POINTER(ctypes.c_void_p))
     args.rows, args.cols, args.world, args.rank, args.epoch = rows, cols, world, rank, epoch
     _check(library().trinity_sm100_allreduce_bf16(ctypes.byref(args), _stream(stream)))
+
+
+def gemm_allreduce_flag_words(m, n, world):
+    return int(library().trinity_sm100_gemm_allreduce_flag_words(m, n, world))
+
+
+def gemm_allreduce(a, b, out, peer_ptrs, flag_ptrs, rank, epoch, stream=None):
+    """out (on every rank) = sum over ranks of a_rank @ b_rank, reduced inside the GEMM's
+    epilogue over peer-mapped memory (see ``trinity_sm100_gemm_allreduce_bf16``).  ``out`` is this
+    rank's symmetric buffer, ``peer_ptrs[rank] == out.data_ptr()``."""
+    _require(a, torch.bfloat16, "a")
+    _require(b, torch.bfloat16, "b")
+    _require(out, torch.bfloat16, "out")
+    m, kk = a.shape
+    n = b.shape[1]
+    args = GemmArgs()
+    args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.m, args.n, args.k = m, n, kk
+    args.lda, args.ldb, args.ldo = a.stride(0), b.stride(0), out.stride(0)
+    world = len(peer_ptrs)
+    peers = (ctypes.c_void_p * world)(*peer_ptrs)
+    flags = (ctypes.c_void_p * world)(*flag_ptrs)
+    red = AllReduceArgs()
+    red.peers = ctypes.cast(peers, ctypes.POINTER(ctypes.c_void_p))
+    red.flags = ctypes.cast(flags, ctypes.POINTER(ctypes.c_void_p))
+    red.rows, red.cols, red.world, red.rank, red.epoch = m, n, world, rank, epoch
+    with torch.cuda.device(a.device):
+        _check(library().trinity_sm100_gemm_allreduce_bf16(ctypes.byref(args), ctypes.byref(red),
+                                                           _stream(stream)))
+    return out

@@ -5,7 +5,9 @@ of W_down ([d_ff / n, d_model]); X is replicated.  Per step a rank launches
   1. the gated GEMM (two accumulators, SiLU-gate epilogue) -> H[M, d_ff / n] in BF16,
   2. the row-parallel down GEMM -> its partial Y[M, d_model] into a symmetric buffer,
   3. the peer-memory sum all-reduce of Y (skipped when the world has one rank),
-all on one stream, with no host synchronisation in between.
+all on one stream, with no host synchronisation in between.  With ``fused=True`` (the default)
+steps 2 and 3 are one kernel: the down GEMM's epilogue warps exchange and add the partial tiles
+over NVLink while the tensor cores work on the following tiles.
 The plan-level spelling of the same computation is `plans.gated_gemm` followed by a GEMM and
 `(all_reduce ...)`; this class is the launch sequence the provider emits for it.
 """
@@ -15,7 +17,7 @@ from . import kernels as k
 
 
 class TensorParallelMLP:
-    def __init__(self, world, m, d_model, d_ff, w_gate, w_up, w_down, device=None):
+    def __init__(self, world, m, d_model, d_ff, w_gate, w_up, w_down, device=None, fused=True):
         self.world = world
         self.size = world.size if world is not None else 1
         self.rank = world.rank if world is not None else 0
@@ -30,8 +32,10 @@ class TensorParallelMLP:
         self.w_gate, self.w_up, self.w_down = w_gate, w_up, w_down
         device = device or w_gate.device
         self.hidden = torch.empty((m, shard), dtype=torch.bfloat16, device=device)
+        self.fused = fused
         if world is not None and self.size > 1:
-            self.buffer = world.allocate((m, d_model), torch.bfloat16)
+            self.buffer = world.allocate((m, d_model), torch.bfloat16,
+                                         flag_words=k.gemm_allreduce_flag_words(m, d_model, self.size))
             self.output = self.buffer.tensor
         else:
             self.buffer = None
@@ -41,6 +45,9 @@ class TensorParallelMLP:
         """Launches the step on `stream` (default: current); returns the output tensor, which
         holds the all-reduced result once the stream has run."""
         k.gemm(x, self.w_up, b2=self.w_gate, activation=k.ACT_SILU_GATE, out=self.hidden, stream=stream)
+        if self.buffer is not None and self.fused:
+            self.world.gemm_all_reduce(self.hidden, self.w_down, self.buffer, stream=stream)
+            return self.output
         k.gemm(self.hidden, self.w_down, out=self.output, stream=stream)
         if self.buffer is not None:
             self.world.all_reduce(self.buffer, stream=stream)

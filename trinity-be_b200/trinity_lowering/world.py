@@ -136,8 +136,9 @@ class World:
         self._stage("barrier", lambda: None)
 
     # ------------------------------------------------------------------ data plane
-    def allocate(self, shape, dtype=None):
-        """A symmetric buffer: same shape on every rank, every rank's copy mapped everywhere."""
+    def allocate(self, shape, dtype=None, flag_words=None):
+        """A symmetric buffer: same shape on every rank, every rank's copy mapped everywhere.
+        ``flag_words`` sizes the flag pad that travels with it (default: the all-reduce kernel's)."""
         import torch
         import torch.distributed._symmetric_memory as symm
         from . import kernels
@@ -145,13 +146,14 @@ class World:
         def make():
             tensor = symm.empty(*shape, dtype=dtype or torch.bfloat16, device=self.device)
             handle = symm.rendezvous(tensor, group=torch.distributed.group.WORLD)
-            flags = symm.empty(kernels.allreduce_flag_words(), dtype=torch.int32, device=self.device)
+            flags = symm.empty(max(flag_words or 0, kernels.allreduce_flag_words()), dtype=torch.int32,
+                               device=self.device)
             flags.zero_()
             flag_handle = symm.rendezvous(flags, group=torch.distributed.group.WORLD)
             torch.cuda.synchronize(self.device)
             return SymmetricBuffer(self, tensor, list(handle.buffer_ptrs), flags, list(flag_handle.buffer_ptrs))
 
-        buffer = self._stage("allocate", make, [list(shape), str(dtype)])
+        buffer = self._stage("allocate", make, [list(shape), str(dtype), flag_words])
         self._stage("allocate.ready", lambda: None)
         self._buffers.append(buffer)
         return buffer
@@ -164,6 +166,15 @@ class World:
         rows = buffer.tensor.shape[0] if buffer.tensor.dim() > 1 else 1
         cols = buffer.tensor.numel() // rows
         kernels.allreduce(buffer.peer_ptrs, buffer.flag_ptrs, rows, cols, self.rank, self._epoch, stream=stream)
+        return buffer.tensor
+
+    def gemm_all_reduce(self, a, b, buffer, stream=None):
+        """buffer.tensor (on every rank) = sum over ranks of a @ b, reduced in the GEMM epilogue."""
+        from . import kernels
+        self._check()
+        self._epoch += 1
+        kernels.gemm_allreduce(a, b, buffer.tensor, buffer.peer_ptrs, buffer.flag_ptrs, self.rank,
+                               self._epoch, stream=stream)
         return buffer.tensor
 
     def close(self):
