@@ -37,6 +37,9 @@ NCU_TRAFFIC_BYTES = {
     "rmsnorm": 4.889e8,
     "softmax": 4.866e8,
     "mla": 3.154e8,
+    "tp_mlp": None,
+    "tp_mlp_unfused": None,
+    "tp_mlp_noreduce": None,
 }
 
 
@@ -112,12 +115,15 @@ class Workload:
     """name, metric, unit, bound, work per step, device step, end-to-end step, CPU sample."""
 
 
-def make_workload(name, device):
+def make_workload(name, device, world=None):
     from oracle import workloads as wl  # seeded input generators only (no oracle math here)
     from trinity_lowering import kernels as k
 
     w = Workload()
     w.name = name
+    w.world = world
+    w.strong = False
+    w.no_graph = False
     on_gpu = device.type == "cuda"
 
     def pin(t):
@@ -258,6 +264,69 @@ def make_workload(name, device):
             wl.mla_oracle(q, cache, scale, d_v, batches=[0, 1])
             dt = time.perf_counter() - t0
             return (w.alg_bytes * 2 / batch) / 1e9 / dt, "2 of 64 sequences, CPU oracle", dt
+    elif name in ("tp_mlp", "tp_mlp_unfused", "tp_mlp_noreduce"):
+        # Tensor-parallel SwiGLU MLP: total work fixed, sharded over the ranks (strong scaling).
+        m, d_model, d_ff = 16384, 8192, 28672
+        w.label = ("tp_swiglu_mlp X[16384,8192], W_gate/W_up[8192,28672] column-sharded, "
+                   "W_down[28672,8192] row-sharded" + {
+                       "tp_mlp": ", all-reduce fused into the down GEMM",
+                       "tp_mlp_unfused": ", separate all-reduce kernel",
+                       "tp_mlp_noreduce": ", NO all-reduce (timing baseline, result incomplete)"}[name])
+        w.metric, w.unit, w.bound, w.dtype = "tp_mlp_tflops", "TFLOP/s", "tensor", "bf16"
+        w.total_work = 3 * 2.0 * m * d_model * d_ff / 1e12
+        w.alg_bytes = (m * d_model * 2 + 3 * d_model * d_ff + m * d_ff * 2) * 2
+        w.flush, w.l2_note = False, "inputs larger than L2"
+        w.strong = True
+        w.no_graph = True     # the all-reduce epoch is a launch argument
+        if on_gpu:
+            from trinity_lowering.tp_mlp import TensorParallelMLP
+            world = w.world
+            size = world.size if world is not None else 1
+            rank = world.rank if world is not None else 0
+            shard = d_ff // size
+            g = torch.Generator(device=device)
+            g.manual_seed(1238 + rank)
+            def normal(shape, std):
+                return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std).bfloat16()
+            gx = torch.Generator(device=device)
+            gx.manual_seed(1238)
+            xd = (torch.randn((m, d_model), generator=gx, device=device)).bfloat16()
+            wg = normal((d_model, shard), 1.0 / math.sqrt(d_model))
+            wu = normal((d_model, shard), 1.0 / math.sqrt(d_model))
+            wd = normal((shard, d_model), 1.0 / math.sqrt(d_ff))
+            mlp = TensorParallelMLP(world, m, d_model, d_ff, wg, wu, wd,
+                                    fused={"tp_mlp": True, "tp_mlp_unfused": False}.get(name))
+            host_x = xd.cpu().pin_memory()
+            host_y = torch.empty((m, d_model), dtype=torch.bfloat16).pin_memory()
+            w.work = w.total_work / size
+            w.kernels_per_step = 2 if (size == 1 or name == "tp_mlp") else 3
+
+            def device_step():
+                mlp.forward(xd)
+
+            def e2e_step():
+                xd.copy_(host_x, non_blocking=True)
+                mlp.forward(xd)
+                host_y.copy_(mlp.output, non_blocking=True)
+
+            w.h2d, w.d2h = xd.numel() * 2, m * d_model * 2
+        else:
+            device_step = e2e_step = None
+
+        def cpu_sample(threads, budget_s):
+            torch.set_num_threads(threads)
+            rows = 128
+            gcpu = torch.Generator().manual_seed(7)
+            xs = torch.randn((rows, d_model), generator=gcpu)
+            a = torch.randn((d_model, d_ff), generator=gcpu) / math.sqrt(d_model)
+            bm = torch.randn((d_model, d_ff), generator=gcpu) / math.sqrt(d_model)
+            c = torch.randn((d_ff, d_model), generator=gcpu) / math.sqrt(d_ff)
+            t0 = time.perf_counter()
+            gate = xs @ a
+            h = (xs @ bm) * (gate * torch.sigmoid(gate))
+            (h.bfloat16().float() @ c).bfloat16()
+            dt = time.perf_counter() - t0
+            return 3 * 2.0 * rows * d_model * d_ff / 1e12 / dt, f"{rows} of {m} rows, torch CPU FP32", dt
     else:
         raise SystemExit(f"unknown workload {name}")
     w.device_step, w.e2e_step, w.cpu_sample = device_step, e2e_step, cpu_sample
@@ -353,7 +422,14 @@ def main():
 
     from trinity_lowering import kernels as k
     k.library()
-    w = make_workload(args.workload, device)
+    world_obj = None
+    if distributed and args.workload.startswith("tp_mlp"):
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        from trinity_lowering.world import World
+        world_obj = World.from_torchrun(timeout=120.0)
+    w = make_workload(args.workload, device, world_obj)
+    if w.no_graph:
+        args.no_graph = True
     stream = torch.cuda.Stream(device=device)
     flush_buffer = (torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device) if w.flush else None)
 
@@ -411,6 +487,7 @@ def main():
     per_step_ms = ms / args.steps
     value = world * w.work * args.steps / (ms / 1e3)
     e2e_value = world * w.work * e2e_steps / (e2e_ms / 1e3)
+    scaling = "strong" if w.strong else "weak"
     achieved = w.work / (per_step_ms / 1e3)            # per GPU, dominant kernel
     if w.bound == "tensor":
         long_run = ms > 1000.0
@@ -422,9 +499,10 @@ def main():
     line = {
         "metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": per_step_ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "scaling": scaling, "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
         "config": {"workload": w.label, "l2": w.l2_note,
-                   "parallelism": "replicas only" if world > 1 else "single GPU",
+                   "parallelism": ("single GPU" if world == 1 else
+                                   f"tp{world} over NVLink peer memory" if w.strong else "replicas only"),
                    "launch": "direct" if args.no_graph else "CUDA Graph replay"},
         "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": roof_unit,
                      "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name),

@@ -268,12 +268,12 @@ TRINITY_SM100_API int trinity_sm100_allreduce_bf16(const trinity_sm100_allreduce
  * Every rank calls this with its own shard (`gemm`: no bias, no activation, BF16 out) and the
  * same peer tables (`reduce`: peers[r] = rank r's [m,n] output buffer, peers[rank] == gemm->out;
  * flags[r] = rank r's flag pad of at least trinity_sm100_gemm_allreduce_flag_words() zeroed
- * words; epoch strictly increasing per call).  Inside one persistent kernel the epilogue warps
- * store their partial tile, signal the tile's owner rank, and - one tile behind, so the wait
- * is short and the NVLink traffic overlaps the next tile's MMAs - the owner adds the partials
- * of its tiles in rank order in FP32 and pushes the rounded result into every rank's buffer
- * over NVLink with 128-bit peer loads / stores.  All waits are bounded.  No NVSHMEM, no NCCL,
- * no multicast.
+ * words; epoch strictly increasing per call; world is 1, 2, 4 or 8).  Inside one persistent
+ * kernel the epilogue warps store their partial tile, tell every rank, and - one tile behind,
+ * so the wait is short and the NVLink traffic overlaps the next tile's MMAs - each rank adds
+ * the partials of its own 128/world rows of that tile in rank order in FP32 and pushes the
+ * rounded rows into every rank's buffer over NVLink with 128-bit peer loads / stores.  All
+ * waits are bounded.  No NVSHMEM, no NCCL, no multicast.
  *
  * The reference has no all-reduce (its plan language only has all_gather,
  * src/analysis/plan/expression.rs:227-231) and its multi-rank emission is unimplemented

@@ -71,9 +71,11 @@ __device__ __forceinline__ float apply_activation(float x, int activation) {
   return x;
 }
 
-// Fused all-reduce duty of the epilogue warps (128 threads, `tid` in [0,128)): the rank that
-// owns tile `tile` waits until every rank has stored its partial of that tile, adds the
-// partials in rank order in FP32, rounds once and pushes the result into every rank's buffer.
+// Fused all-reduce duty of the epilogue warps (128 threads, `tid` in [0,128)).  Every rank owns
+// the same 128/world rows of *every* tile: it waits until all ranks have stored their partial of
+// the tile, adds the partials of its rows in rank order in FP32, rounds once and pushes the
+// result into every rank's buffer.  Small equal duties after every tile keep NVLink busy all the
+// time and cost each CTA about one round trip per tile.
 // Returns false if a wait gave up (uniform over the 128 threads).
 template <int kBN>
 __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const GemmPeers& peers, int tile,
@@ -94,34 +96,57 @@ __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const Gem
       : "r"(good)
       : "memory");
   if (!all_good) return false;
+  // Four vectors per thread and step, all loads issued before the first add: with NVLink round
+  // trips of a few microseconds the duty is latency-bound, so memory-level parallelism decides
+  // how long an owned tile takes.  The sum is always taken in rank order.
   constexpr int kVecPerRow = kBN / 8;
+  constexpr int kBatch = 4;
+  const int slice_rows = kBM / peers.world;
+  m0 += peers.rank * slice_rows;
 #pragma unroll 1
-  for (int idx = tid; idx < kBM * kVecPerRow; idx += 128) {
-    const int row = m0 + idx / kVecPerRow;
-    const int col = n0 + (idx % kVecPerRow) * 8;
-    if (row >= p.m || col >= p.n) continue;
-    const long long v = static_cast<long long>(row) * peers.ld_vectors + (col >> 3);
-    uint4 part[kGemmMaxWorld];
+  for (int base = 0; base < slice_rows * kVecPerRow; base += 128 * kBatch) {
+    long long v[kBatch];
+    bool live[kBatch];
+    uint4 part[kBatch][kGemmMaxWorld];
 #pragma unroll
-    for (int r = 0; r < kGemmMaxWorld; ++r)
-      if (r < peers.world) part[r] = peer_load(peers.buffers[r] + v);
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int u = 0; u < kBatch; ++u) {
+      const int idx = base + u * 128 + tid;
+      const int row = m0 + idx / kVecPerRow;
+      const int col = n0 + (idx % kVecPerRow) * 8;
+      live[u] = idx < slice_rows * kVecPerRow && row < p.m && col < p.n;
+      v[u] = static_cast<long long>(row) * peers.ld_vectors + (col >> 3);
+    }
+    // (register arrays are indexed statically on purpose: a dynamically indexed destination would
+    // consume each load at once and serialise the round trips)
 #pragma unroll
     for (int r = 0; r < kGemmMaxWorld; ++r) {
       if (r < peers.world) {
-        const uint32_t w[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          acc[2 * e] += bf16_lo(w[e]);
-          acc[2 * e + 1] += bf16_hi(w[e]);
-        }
+        for (int u = 0; u < kBatch; ++u)
+          if (live[u]) part[u][r] = peer_load(peers.buffers[r] + v[u]);
       }
     }
-    const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
-                               pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
 #pragma unroll
-    for (int r = 0; r < kGemmMaxWorld; ++r)
-      if (r < peers.world) peer_store(peers.buffers[r] + v, o);
+    for (int u = 0; u < kBatch; ++u) {
+      if (!live[u]) continue;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int r = 0; r < kGemmMaxWorld; ++r) {
+        if (r < peers.world) {
+          const uint32_t w[4] = {part[u][r].x, part[u][r].y, part[u][r].z, part[u][r].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] += bf16_lo(w[e]);
+            acc[2 * e + 1] += bf16_hi(w[e]);
+          }
+        }
+      }
+      const uint4 o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                 pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+#pragma unroll
+      for (int r = 0; r < kGemmMaxWorld; ++r)
+        if (r < peers.world) peer_store(peers.buffers[r] + v[u], o);
+    }
   }
   return true;
 }
@@ -402,11 +427,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           __threadfence_system();
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (etid == 0)
-          flag_store(peers.flags[tile % peers.world] + static_cast<long long>(tile) * peers.world + peers.rank,
-                     peers.epoch);
-        if (owed_tile >= 0 && owed_tile % peers.world == peers.rank)
-          ok = reduce_owned_tile<kBN>(p, peers, owed_tile, owed_m0, owed_n0, etid);
+        if (etid < peers.world)
+          flag_store(peers.flags[etid] + static_cast<long long>(tile) * peers.world + peers.rank, peers.epoch);
+        if (owed_tile >= 0) ok = reduce_owned_tile<kBN>(p, peers, owed_tile, owed_m0, owed_n0, etid);
         owed_tile = tile;
         owed_m0 = m0;
         owed_n0 = n0;
@@ -414,8 +437,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     if (lane == 0) tma_store_wait_all();
     if (kFused) {
-      if (ok && owed_tile >= 0 && owed_tile % peers.world == peers.rank)
-        ok = reduce_owned_tile<kBN>(p, peers, owed_tile, owed_m0, owed_n0, etid);
+      if (ok && owed_tile >= 0) ok = reduce_owned_tile<kBN>(p, peers, owed_tile, owed_m0, owed_n0, etid);
       // Retire: once every CTA of this rank has pushed its tiles, tell the peers; the last CTA
       // stays until every peer has said the same, so the output is complete when the kernel ends.
       __threadfence_system();
@@ -570,6 +592,8 @@ extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
                 "gemm_allreduce: the partial products are summed across ranks, so no bias or activation, BF16 out");
   if (g.lda % 8 || g.ldb % 8 || g.ldo % 8 || g.n % 8 || g.lda < g.k || g.ldb < g.n || g.ldo < g.n)
     return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: pitches and n must be multiples of 8 elements");
+  if (r.world != 1 && r.world != 2 && r.world != 4 && r.world != 8)
+    return fail(TRINITY_SM100_E_UNSUPPORTED, "gemm_allreduce: world must be 1, 2, 4 or 8 (row slices of a 128-row tile)");
   if (!r.peers || !r.flags || r.world < 1 || r.world > kGemmMaxWorld || r.rank < 0 || r.rank >= r.world)
     return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: world %d / rank %d or pointer tables invalid", r.world, r.rank);
   if (r.rows != g.m || r.cols != g.n)

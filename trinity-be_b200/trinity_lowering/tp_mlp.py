@@ -45,6 +45,9 @@ class TensorParallelMLP:
         """Launches the step on `stream` (default: current); returns the output tensor, which
         holds the all-reduced result once the stream has run."""
         k.gemm(x, self.w_up, b2=self.w_gate, activation=k.ACT_SILU_GATE, out=self.hidden, stream=stream)
+        if self.fused is None:   # timing baseline only: per-rank partial, no exchange
+            k.gemm(self.hidden, self.w_down, out=self.output, stream=stream)
+            return self.output
         if self.buffer is not None and self.fused:
             self.world.gemm_all_reduce(self.hidden, self.w_down, self.buffer, stream=stream)
             return self.output
