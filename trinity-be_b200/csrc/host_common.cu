@@ -107,7 +107,7 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint6
 int make_tensor_map_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
                        uint64_t mid, uint64_t outer, uint64_t mid_pitch_bytes,
                        uint64_t outer_pitch_bytes, uint32_t box_inner, uint32_t box_mid,
-                       uint32_t box_outer, bool swizzle128) {
+                       uint32_t box_outer, int swizzle_bytes) {
   EncodeTiled fn = encode_tiled();
   if (!fn) return fail(TRINITY_SM100_E_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
   cuuint64_t dims[3] = {inner, mid, outer};
@@ -116,7 +116,9 @@ int make_tensor_map_3d(CUtensorMap* map, const void* base, int elem_bytes, uint6
   cuuint32_t elem_strides[3] = {1, 1, 1};
   CUresult r = fn(map, map_dtype(elem_bytes), 3, const_cast<void*>(base), dims, strides, box,
                   elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  swizzle_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                  : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                        : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(TRINITY_SM100_E_CUDA, "cuTensorMapEncodeTiled(3d) -> %d", int(r));

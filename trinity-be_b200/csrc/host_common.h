@@ -30,10 +30,11 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint6
                        uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner,
                        uint32_t box_outer, bool swizzle128);
 
-// 3-D variant: dims (inner, mid, outer) with byte pitches for mid and outer.
+// 3-D variant: dims (inner, mid, outer) with byte pitches for mid and outer; swizzle_bytes is
+// 0, 64 or 128 (the box's inner extent in bytes must equal a non-zero swizzle width).
 int make_tensor_map_3d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
                        uint64_t mid, uint64_t outer, uint64_t mid_pitch_bytes,
                        uint64_t outer_pitch_bytes, uint32_t box_inner, uint32_t box_mid,
-                       uint32_t box_outer, bool swizzle128);
+                       uint32_t box_outer, int swizzle_bytes);
 
 }  // namespace trinity_sm100

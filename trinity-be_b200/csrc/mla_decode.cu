@@ -19,18 +19,20 @@
 //   values:  each CTA multiplies the (identical) probabilities with its own 256 latent
 //            columns, which are exactly the cache bytes it already loaded for the scores
 //
-// So every cache byte is loaded once per cluster (plus the 64-feature rope box, which both
-// CTAs load), no score FLOP is duplicated, and the query half (256 latent features) lives in
-// TMEM as the A operand.  TMEM: accumulator 256 columns, two 64-column score buffers, query
-// 128 columns.  Shared memory: three 40 KB cache stages, the query's rope box, two receive and
-// two send tiles of 16 KB.
+// So every cache byte is loaded exactly once per cluster, no score FLOP is duplicated, and the
+// query half (256 latent + 32 rope features) lives in TMEM as the A operand of every score MMA.
+// TMEM: accumulator 256 columns, one 64-column score buffer, one 32-column probability buffer,
+// query 144 columns.  Shared memory: four 36 KB cache stages (four 128-byte-swizzled latent boxes
+// and one 64-byte-swizzled rope box of 32 features), two receive and two send tiles of 16 KB.
 //
-//   warp 0    TMA producer (query rope box, then the cache chunk ring: 4 latent boxes + rope)
-//   warp 1    MMA issuer: QK(j) = 16 TMEM-A + 2 SMEM-A MMAs (N=64), PV(j-1) = 4 TMEM-A MMAs
-//             (N=256); scores of chunk j are issued before the values of chunk j-1
+//   warp 0    TMA producer (the cache chunk ring: 4 latent boxes + rope box per chunk)
+//   warp 1    MMA issuer: QK(j) = 18 TMEM-A MMAs (N=64), PV(j) = 4 TMEM-A MMAs (N=256).  The
+//             scores of chunk j+2 are issued as soon as the softmax group has copied the scores
+//             of chunk j+1 out of TMEM, which it does before it turns to chunk j; so the score
+//             MMAs run two chunks ahead of the value MMAs and never queue behind a softmax.
 //   warps 2-9 softmax group, two threads per head (32 positions of each chunk apiece):
 //             partial-score load, exchange with the peer CTA, running max / sum, conditional
-//             rescale of the accumulator, BF16 probabilities written over the score buffer,
+//             rescale of the accumulator, BF16 probabilities into their own TMEM buffer,
 //             final epilogue
 //   warp 10   courier: acknowledges consumed exchange tiles to the peer CTA
 //
@@ -51,16 +53,15 @@ constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
 constexpr int kMlaThreads = 64 + kSoftmaxThreads + 32;  // producer, MMA issuer, softmax group, courier
 constexpr int kKv = 64;                        // cache positions per chunk
 constexpr int kDqk = 576, kDv = 512;
-constexpr int kKvStages = 3;
+constexpr int kKvStages = 4;
 constexpr int kBoxBytes = kKv * 128;           // 8192: one [64 positions x 64 features] box
-constexpr int kStageBoxes = 5;                 // 4 latent boxes of this CTA's half + rope box
-constexpr int kStageBytes = kStageBoxes * kBoxBytes;  // 40960
-constexpr int kQRopeBytes = 128 * 128;         // [128 heads x 64 rope features]
+constexpr int kRopeBoxBytes = kKv * 64;        // 4096: [64 positions x 32 rope features]
+constexpr int kStageBytes = 4 * kBoxBytes + kRopeBoxBytes;  // 36864
 constexpr int kXchgBytes = 128 * kKv * 2;      // one partial score tile in FP16: 16384
 // two receive tiles + two send tiles: the exchange of chunk j+1 overlaps the softmax of chunk j
-constexpr int kMlaSmem = 1024 + kQRopeBytes + kKvStages * kStageBytes + 4 * kXchgBytes + 256;
-// TMEM columns
-constexpr uint32_t kColO = 0, kColS = 256, kColQ = 384, kTmemCols = 512;
+constexpr int kMlaSmem = 1024 + kKvStages * kStageBytes + 4 * kXchgBytes + 256;
+// TMEM columns: accumulator, scores, probabilities, query (128 latent + 16 rope word columns)
+constexpr uint32_t kColO = 0, kColS = 256, kColP = 320, kColQ = 352, kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;      // in log2 units: probabilities stay below 2^8
 
 struct MlaParams {
@@ -187,34 +188,34 @@ __host__ __device__ inline void split_range(int chunks, int splits, int s, int& 
 }
 
 __global__ void __launch_bounds__(kMlaThreads, 1)
-mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
-                  const __grid_constant__ CUtensorMap map_cache, const MlaParams p) {
+mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
+                  const __grid_constant__ CUtensorMap map_rope, const MlaParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ float row_max[2 * 3 * 128];        // [part][chunk parity | 2 = final sums][head]
   __shared__ unsigned read_count_storage;       // softmax warps that have read their receive tile
   volatile unsigned* read_count = &read_count_storage;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t q_smem = smem_base;                                  // query rope box
-  const uint32_t kv_smem = q_smem + kQRopeBytes;                      // cache stage ring
+  const uint32_t kv_smem = smem_base;                                 // cache stage ring
   const uint32_t xchg_smem = kv_smem + kKvStages * kStageBytes;       // peer's partial scores land here
   const uint32_t send_smem = xchg_smem + 2 * kXchgBytes;               // my partial scores, staged for the copy
   const uint32_t bar_base = xchg_smem + 4 * kXchgBytes;
-  uint8_t* xchg = smem + kQRopeBytes + kKvStages * kStageBytes;
+  uint8_t* xchg = smem + kKvStages * kStageBytes;
   uint8_t* send = xchg + 2 * kXchgBytes;
-  // barriers: kv_full[3], kv_empty[3], s_full[2], p_full[2], x_full[2], x_empty[2], q_full,
-  //           q_tmem, pv_done
+  // barriers: kv_full[stages], kv_empty[stages], x_full[2], x_empty[2], s_full, s_free, p_full,
+  //           pv_done, q_tmem.  The four single barriers complete once per chunk, so chunk j is
+  //           phase j & 1 on each of them.
   auto kv_full = [&](int s) { return bar_base + 8u * s; };
   auto kv_empty = [&](int s) { return bar_base + 8u * (kKvStages + s); };
-  auto s_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + b); };
-  auto p_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + 2 + b); };
-  auto x_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + 4 + b); };
-  auto x_empty = [&](int b) { return bar_base + 8u * (2 * kKvStages + 6 + b); };
-  const uint32_t q_full = bar_base + 8u * (2 * kKvStages + 8);
-  const uint32_t q_tmem = bar_base + 8u * (2 * kKvStages + 9);
-  const uint32_t pv_done = bar_base + 8u * (2 * kKvStages + 10);
+  auto x_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + b); };
+  auto x_empty = [&](int b) { return bar_base + 8u * (2 * kKvStages + 2 + b); };
+  const uint32_t s_full = bar_base + 8u * (2 * kKvStages + 4);    // scores of a chunk are in TMEM
+  const uint32_t s_free = bar_base + 8u * (2 * kKvStages + 5);    // ... and have been copied out
+  const uint32_t p_full = bar_base + 8u * (2 * kKvStages + 6);    // probabilities are in TMEM
+  const uint32_t pv_done = bar_base + 8u * (2 * kKvStages + 7);   // ... and have been consumed
+  const uint32_t q_tmem = bar_base + 8u * (2 * kKvStages + 8);
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(
-      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 11));
+      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 9));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -234,17 +235,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(kv_empty(s), 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(s_full(i), 1);
-      mbar_init(p_full(i), kSoftmaxWarps);
       mbar_init(x_full(i), 1);     // local arm (expect_tx) + the peer's bulk copy bytes
       mbar_init(x_empty(i), 1);    // one arrival from the peer once all its threads have read
     }
-    mbar_init(q_full, 1);
-    mbar_init(q_tmem, kSoftmaxWarps);
+    mbar_init(s_full, 1);
+    mbar_init(s_free, kSoftmaxWarps);
+    mbar_init(p_full, kSoftmaxWarps);
     mbar_init(pv_done, 1);
+    mbar_init(q_tmem, kSoftmaxWarps);
     mbar_fence_init();
-    tma_prefetch_desc(&map_q);
     tma_prefetch_desc(&map_cache);
+    tma_prefetch_desc(&map_rope);
   }
   if (warp == 2) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
@@ -259,8 +260,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0 && num_chunks > 0) {
-      mbar_arrive_expect_tx(q_full, kQRopeBytes);
-      tma_load_3d(q_smem, &map_q, q_full, kDv, 0, b);
       for (int j = 0; j < num_chunks; ++j) {
         const int s = j % kKvStages;
         const uint32_t phase = (j / kKvStages) & 1u;
@@ -271,7 +270,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
         for (int f = 0; f < 4; ++f)
           tma_load_3d(dst + f * kBoxBytes, &map_cache, kv_full(s), int(half) * 256 + f * 64, kv0, b);
-        tma_load_3d(dst + 4 * kBoxBytes, &map_cache, kv_full(s), kDv, kv0, b);
+        tma_load_3d(dst + 4 * kBoxBytes, &map_rope, kv_full(s), kDv + int(half) * 32, kv0, b);
       }
     }
   } else if (warp == 1) {
@@ -279,48 +278,51 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     if (lane == 0 && num_chunks > 0) {
       constexpr uint32_t kIdescQK = umma_idesc_bf16(128, kKv, 0, 0);
       constexpr uint32_t kIdescPV = umma_idesc_bf16(128, 256, 0, 1);
-      bool ok = mbar_wait(q_full, 0, 0x501) && mbar_wait(q_tmem, 0, 0x502);
+      // Scores of one chunk: 16 K-steps over the latent boxes and 2 over the rope box, the query
+      // always from TMEM.
+      auto issue_scores = [&](int c) -> bool {
+        const int s = c % kKvStages;
+        if (!mbar_wait(kv_full(s), (c / kKvStages) & 1u, 0x503)) return false;
+        tc_fence_after();
+        const uint32_t stage = kv_smem + s * kStageBytes;
+#pragma unroll
+        for (int ks = 0; ks < 16; ++ks) {
+          const uint64_t b_desc =
+              umma_smem_desc(stage + (ks / 4) * kBoxBytes + (ks % 4) * 32, 16, 1024);
+          umma_bf16_ts(tmem_base + kColS, tmem_base + kColQ + ks * 8, b_desc, kIdescQK, ks != 0);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const uint64_t b_desc = umma_smem_desc_sw64(stage + 4 * kBoxBytes + r * 32, 512);
+          umma_bf16_ts(tmem_base + kColS, tmem_base + kColQ + 128 + r * 8, b_desc, kIdescQK, 1u);
+        }
+        umma_commit(s_full);
+        return true;
+      };
+      bool ok = mbar_wait(q_tmem, 0, 0x502);
       tc_fence_after();
-      for (int j = 0; j <= num_chunks && ok; ++j) {
-        if (j < num_chunks) {
-          const int s = j % kKvStages;
-          if (!mbar_wait(kv_full(s), (j / kKvStages) & 1u, 0x503)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t stage = kv_smem + s * kStageBytes;
-          const uint32_t d_s = tmem_base + kColS + (j & 1) * kKv;
-          // partial scores over this CTA's 256 latent features: query from TMEM
-#pragma unroll
-          for (int ks = 0; ks < 16; ++ks) {
-            const uint64_t b_desc =
-                umma_smem_desc(stage + (ks / 4) * kBoxBytes + (ks % 4) * 32, 16, 1024);
-            umma_bf16_ts(d_s, tmem_base + kColQ + ks * 8, b_desc, kIdescQK, ks != 0);
-          }
-          // ... and over its 32 rope features: query from shared memory
-#pragma unroll
-          for (int r = 0; r < 2; ++r) {
-            const uint32_t off = (half * 2 + r) * 32;
-            const uint64_t a_desc = umma_smem_desc(q_smem + off, 16, 1024);
-            const uint64_t b_desc = umma_smem_desc(stage + 4 * kBoxBytes + off, 16, 1024);
-            umma_bf16_ss(d_s, a_desc, b_desc, kIdescQK, 1u);
-          }
-          umma_commit(s_full(j & 1));
+      // The score buffer is free as soon as the softmax group holds a chunk in registers, which for
+      // chunk c happens at the start of its step c-1; so the scores run two chunks ahead of the
+      // values and are complete when the softmax group asks for them.
+      ok = ok && issue_scores(0);
+      if (ok && num_chunks > 1) ok = mbar_wait(s_free, 0, 0x505) && issue_scores(1);
+      for (int j = 0; j < num_chunks && ok; ++j) {
+        if (j + 2 < num_chunks) {
+          if (!mbar_wait(s_free, (j + 1) & 1u, 0x505)) break;
+          if (!issue_scores(j + 2)) break;
         }
-        if (j >= 1) {
-          const int jj = j - 1;
-          const int s = jj % kKvStages;
-          if (!mbar_wait(p_full(jj & 1), (jj >> 1) & 1u, 0x504)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t stage = kv_smem + s * kStageBytes;
-          const uint32_t a_p = tmem_base + kColS + (jj & 1) * kKv;
+        const int s = j % kKvStages;
+        if (!mbar_wait(p_full, j & 1u, 0x504)) break;
+        tc_fence_after();
+        const uint32_t stage = kv_smem + s * kStageBytes;
 #pragma unroll
-          for (int ks = 0; ks < kKv / 16; ++ks) {
-            // values: N-major, 64-latent boxes 8192 B apart, 8-position groups 1024 B apart
-            const uint64_t b_desc = umma_smem_desc(stage + ks * 2048, kBoxBytes, 1024);
-            umma_bf16_ts(tmem_base + kColO, a_p + ks * 8, b_desc, kIdescPV, (jj | ks) != 0);
-          }
-          umma_commit(kv_empty(s));
-          umma_commit(pv_done);
+        for (int ks = 0; ks < kKv / 16; ++ks) {
+          // values: N-major, 64-latent boxes 8192 B apart, 8-position groups 1024 B apart
+          const uint64_t b_desc = umma_smem_desc(stage + ks * 2048, kBoxBytes, 1024);
+          umma_bf16_ts(tmem_base + kColO, tmem_base + kColP + ks * 8, b_desc, kIdescPV, (j | ks) != 0);
         }
+        umma_commit(kv_empty(s));
+        umma_commit(pv_done);
       }
     }
   } else if (warp == 2 + kSoftmaxWarps) {
@@ -356,7 +358,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const bool live = row < p.heads;
     if (num_chunks > 0) {
-      // This CTA's 256 latent query features -> TMEM as packed BF16 pairs (128 per thread).
+      // This CTA's query features -> TMEM as packed BF16 pairs: 128 latent features per thread,
+      // and the 32 rope features from the threads of part 0.
       const uint4* qrow = reinterpret_cast<const uint4*>(
           p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk + half * 256 + part * 128);
 #pragma unroll 1
@@ -368,6 +371,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
           w[v * 4 + 0] = x.x; w[v * 4 + 1] = x.y; w[v * 4 + 2] = x.z; w[v * 4 + 3] = x.w;
         }
         tmem_st_32x32b_x32(lane_base + kColQ + part * 64 + c * 32, w);
+      }
+      if (part == 0) {
+        const uint4* qrope = reinterpret_cast<const uint4*>(
+            p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk + kDv + half * 32);
+        uint32_t w[16];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 x = live ? __ldg(qrope + v) : make_uint4(0, 0, 0, 0);
+          w[v * 4 + 0] = x.x; w[v * 4 + 1] = x.y; w[v * 4 + 2] = x.z; w[v * 4 + 3] = x.w;
+        }
+        tmem_st_32x32b_x16(lane_base + kColQ + 128, w);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -391,12 +405,15 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
       const int buf = c & 1;
       const uint32_t phase = (c >> 1) & 1u;
       TRINITY_MLA_TICK(0)
-      if (!bad) bad = !mbar_wait(s_full(buf), phase, 0x601);
+      if (!bad) bad = !mbar_wait(s_full, c & 1u, 0x601);
       TRINITY_MLA_TICK(1)
       tc_fence_after();
       uint32_t sv[32];
-      tmem_ld_32x32b_x32(lane_base + kColS + buf * kKv + part * 32, sv);
+      tmem_ld_32x32b_x32(lane_base + kColS + part * 32, sv);
       tmem_ld_wait();
+      // the scores are in registers: the next chunk's score MMAs may overwrite the buffer
+      tc_fence_before();
+      if (__all_sync(0xffffffffu, !bad) && lane == 0) mbar_arrive(s_free);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const __half2 h = __floats2half2_rn(__uint_as_float(sv[2 * i]) * p.scale_log2,
@@ -476,14 +493,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
       mx = fmaxf(mx, row_max[((part ^ 1) * 3 + buf) * 128 + row]);
       TRINITY_MLA_TICK(6)
 
+      // Neither the probability buffer nor the accumulator may be touched before the value MMAs
+      // of chunk j-1 have finished with them.
+      if (j > 0) {
+        if (!bad) bad = !mbar_wait(pv_done, (j - 1) & 1u, 0x602);
+        tc_fence_after();
+      }
       const bool grow = mx > m_ref + kRescaleThreshold;   // always true for the first chunk
       if (__any_sync(0xffffffffu, grow)) {
         const float new_ref = grow ? mx : m_ref;
         const float f = (grow && j > 0) ? fast_exp2(m_ref - new_ref) : 1.0f;
         if (j > 0) {
-          // The accumulator may only be touched once the values of chunk j-1 have landed.
-          if (!bad) bad = !mbar_wait(pv_done, (j - 1) & 1u, 0x602);
-          tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < 128; c += 32) {   // this part's 128 accumulator columns
             uint32_t o[32];
@@ -509,12 +529,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         pw[i] = pack_bf16x2(p0, p1);
       }
       l += sum;
-      // probabilities overwrite the scores: positions [32 part, 32 part + 32) -> 16 columns
-      tmem_st_32x32b_x16(lane_base + kColS + buf * kKv + part * 16, pw);
+      // positions [32 part, 32 part + 32) -> 16 columns of packed pairs
+      tmem_st_32x32b_x16(lane_base + kColP + part * 16, pw);
       tmem_st_wait();
       tc_fence_before();
       const bool warp_good = __all_sync(0xffffffffu, !bad);
-      if (lane == 0 && warp_good) mbar_arrive(p_full(buf));
+      if (lane == 0 && warp_good) mbar_arrive(p_full);
 #pragma unroll
       for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
       TRINITY_MLA_TICK(8)
@@ -678,13 +698,15 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
       return fail(TRINITY_SM100_E_CUDA, "mla: shared memory opt-in: %s", cudaGetErrorString(e));
     configured[device & 63] = true;
   }
-  CUtensorMap map_q, map_cache;
+  // Two views of the cache: 64-feature boxes (128-byte swizzle) for the latent part and
+  // 32-feature boxes (64-byte swizzle) for each CTA's half of the rope part.
+  CUtensorMap map_cache, map_rope;
   int rc;
-  if ((rc = make_tensor_map_3d(&map_q, a.q, 2, kDqk, a.heads, a.batch, kDqk * 2ull,
-                               uint64_t(a.heads) * kDqk * 2, 64, 128, 1, true)))
-    return rc;
   if ((rc = make_tensor_map_3d(&map_cache, a.cache, 2, kDqk, a.seq, a.batch, kDqk * 2ull,
-                               uint64_t(a.seq) * kDqk * 2, 64, kKv, 1, true)))
+                               uint64_t(a.seq) * kDqk * 2, 64, kKv, 1, 128)))
+    return rc;
+  if ((rc = make_tensor_map_3d(&map_rope, a.cache, 2, kDqk, a.seq, a.batch, kDqk * 2ull,
+                               uint64_t(a.seq) * kDqk * 2, 32, kKv, 1, 64)))
     return rc;
   MlaParams p;
   p.q = static_cast<const __nv_bfloat16*>(a.q);
@@ -714,7 +736,7 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   cluster.val.clusterDim.z = 1;
   config.attrs = &cluster;
   config.numAttrs = 1;
-  cudaError_t launch_error = cudaLaunchKernelEx(&config, mla_decode_kernel, map_q, map_cache, p);
+  cudaError_t launch_error = cudaLaunchKernelEx(&config, mla_decode_kernel, map_cache, map_rope, p);
   if (launch_error != cudaSuccess)
     return fail(TRINITY_SM100_E_CUDA, "mla_decode launch: %s", cudaGetErrorString(launch_error));
   count_launch();

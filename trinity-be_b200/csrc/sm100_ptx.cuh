@@ -182,6 +182,18 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
+// Same for operands laid out with the 64-byte swizzle (32 BF16 per row, rows 64 B apart,
+// 8-row groups `stride_bytes` apart): swizzle mode 4.
+__device__ __forceinline__ uint64_t umma_smem_desc_sw64(uint32_t smem_addr, uint32_t stride_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>((stride_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= 4ull << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16 with BF16 operands and an FP32 accumulator.
 //   a_mn_major / b_mn_major: 0 = operand is K-major in shared memory, 1 = MN-major.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(uint32_t m, uint32_t n, uint32_t a_mn_major,
