@@ -10,14 +10,15 @@
 //
 //   CTA c owns latent columns [256c, 256c+256) and rope features [32c, 32c+32).
 //   scores:  each CTA contracts only its 288 features (18 K-steps, N = 64 positions) into a
-//            partial score tile.  The partial tiles are scaled into the log2 domain, rounded
-//            to FP16 and exchanged through distributed shared memory with a bulk asynchronous
-//            copy (16 KB per chunk and direction; the copy of chunk j+1 overlaps the softmax of
-//            chunk j); both CTAs add the same two rounded tiles, so they hold identical scores.
+//            partial score tile.  The partial tiles are rounded to FP16 and exchanged through
+//            distributed shared memory with a bulk asynchronous copy (16 KB per chunk and
+//            direction); each CTA adds the peer's rounded tile to its own exact FP32 tile.
 //            FP16 halves the exchange, which measures ~18 B/clk per SM and would otherwise
-//            bound the kernel; it costs 2^-11 relative precision on each partial logit.
-//   values:  each CTA multiplies the (identical) probabilities with its own 256 latent
-//            columns, which are exactly the cache bytes it already loaded for the scores
+//            bound the kernel; it costs 2^-11 relative precision on the peer's half of a logit.
+//            The two CTAs therefore hold logits that differ in the last bits; each normalises
+//            its own columns with its own sums, so every output column is a consistent softmax.
+//   values:  each CTA multiplies its probabilities with its own 256 latent columns, which
+//            are exactly the cache bytes it already loaded for the scores
 //
 // So every cache byte is loaded exactly once per cluster, no score FLOP is duplicated, and the
 // query half (256 latent + 32 rope features) lives in TMEM as the A operand of every score MMA.
@@ -30,16 +31,19 @@
 //             scores of chunk j+2 are issued as soon as the softmax group has copied the scores
 //             of chunk j+1 out of TMEM, which it does before it turns to chunk j; so the score
 //             MMAs run two chunks ahead of the value MMAs and never queue behind a softmax.
-//   warps 2-9 softmax group, two threads per head (32 positions of each chunk apiece):
-//             partial-score load, exchange with the peer CTA, running max / sum, conditional
-//             rescale of the accumulator, BF16 probabilities into their own TMEM buffer,
-//             final epilogue
+//   warps 2-9 two softmax groups of four warps; group g takes the chunks with j % 2 == g and
+//             one thread handles a head's whole 64-position row of a chunk: partial-score load,
+//             exchange with the peer CTA, row maximum, exponentials, BF16 probabilities into
+//             their TMEM buffer.  While one group waits for the peer's tile the other computes.
+//             The running reference maximum of a head passes from group to group through
+//             shared memory (one mbarrier per TMEM lane quadrant orders the hand-over); the
+//             accumulator is rescaled only when the maximum grows by more than 2^8.
 //   warp 10   courier: acknowledges consumed exchange tiles to the peer CTA
 //
 // With kv_splits == 1 the CTA writes BF16 output directly.  Otherwise it writes a normalised
-// FP32 partial and its log-sum-exp to scratch and a small kernel merges the splits.
-// Algorithmic traffic: q + cache + out bytes; the scratch adds 2 * splits * batch * heads *
-// 513 * 4 bytes when splits > 1.
+// FP32 partial and its log-sum-exp (one per feature half) to scratch and a small kernel merges
+// the splits.  Algorithmic traffic: q + cache + out bytes; the scratch adds 2 * splits * batch *
+// heads * 514 * 4 bytes when splits > 1.
 #include "host_common.h"
 #include <cuda_fp16.h>
 
@@ -48,7 +52,7 @@
 namespace trinity_sm100 {
 namespace {
 
-constexpr int kSoftmaxWarps = 8;                 // two warps per TMEM lane quadrant: 32 positions each
+constexpr int kSoftmaxWarps = 8;                 // two groups of four warps (one per TMEM lane quadrant)
 constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
 constexpr int kMlaThreads = 64 + kSoftmaxThreads + 32;  // producer, MMA issuer, softmax group, courier
 constexpr int kKv = 64;                        // cache positions per chunk
@@ -68,9 +72,10 @@ struct MlaParams {
   const __nv_bfloat16* q;
   __nv_bfloat16* out;
   float* partial_o;   // [batch][splits][heads][512]
-  float* partial_lse; // [batch][splits][heads]
+  float* partial_lse; // [batch][splits][heads][2 feature halves]
   int batch, heads, seq, splits;
-  float scale_log2;
+  float scale_log2;   // |scale| * log2(e)
+  int negate;         // scale < 0: the query's sign is flipped on its way into TMEM
 };
 
 // Optional per-phase cycle counters of the softmax loop: a tuning harness that defines
@@ -191,9 +196,10 @@ __global__ void __launch_bounds__(kMlaThreads, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
                   const __grid_constant__ CUtensorMap map_rope, const MlaParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ float row_max[2 * 3 * 128];        // [part][chunk parity | 2 = final sums][head]
-  __shared__ unsigned read_count_storage;       // softmax warps that have read their receive tile
-  volatile unsigned* read_count = &read_count_storage;
+  __shared__ float m_shared[128];               // reference maximum of each head (log2 domain)
+  __shared__ float l_part[2 * 128];             // [group][head] sums of probabilities at the end
+  __shared__ unsigned read_count_storage[2];    // per receive tile: warps that have read it
+  volatile unsigned* read_count = read_count_storage;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t kv_smem = smem_base;                                 // cache stage ring
@@ -202,20 +208,25 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   const uint32_t bar_base = xchg_smem + 4 * kXchgBytes;
   uint8_t* xchg = smem + kKvStages * kStageBytes;
   uint8_t* send = xchg + 2 * kXchgBytes;
-  // barriers: kv_full[stages], kv_empty[stages], x_full[2], x_empty[2], s_full, s_free, p_full,
-  //           pv_done, q_tmem.  The four single barriers complete once per chunk, so chunk j is
-  //           phase j & 1 on each of them.
+  // barriers: kv_full[stages], kv_empty[stages], x_full[2], x_empty[2], s_full[2], pv_done[2],
+  //           s_free, p_full, q_tmem, m_ready[4].  s_free and p_full complete once per chunk and
+  //           are waited on by one thread, chunk after chunk (chunk j is phase j & 1).  s_full
+  //           and pv_done are waited on by the softmax groups, which skip every other chunk; a
+  //           parity wait is only meaningful on consecutive phases, so these two exist once per
+  //           chunk parity (chunk j is phase (j >> 1) & 1 of barrier j & 1).
   auto kv_full = [&](int s) { return bar_base + 8u * s; };
   auto kv_empty = [&](int s) { return bar_base + 8u * (kKvStages + s); };
   auto x_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + b); };
   auto x_empty = [&](int b) { return bar_base + 8u * (2 * kKvStages + 2 + b); };
-  const uint32_t s_full = bar_base + 8u * (2 * kKvStages + 4);    // scores of a chunk are in TMEM
-  const uint32_t s_free = bar_base + 8u * (2 * kKvStages + 5);    // ... and have been copied out
-  const uint32_t p_full = bar_base + 8u * (2 * kKvStages + 6);    // probabilities are in TMEM
-  const uint32_t pv_done = bar_base + 8u * (2 * kKvStages + 7);   // ... and have been consumed
-  const uint32_t q_tmem = bar_base + 8u * (2 * kKvStages + 8);
+  auto s_full = [&](int c) { return bar_base + 8u * (2 * kKvStages + 4 + (c & 1)); };   // scores of chunk c are in TMEM
+  auto pv_done = [&](int c) { return bar_base + 8u * (2 * kKvStages + 6 + (c & 1)); };  // values of chunk c are accumulated
+  const uint32_t s_free = bar_base + 8u * (2 * kKvStages + 8);    // the scores have been copied out
+  const uint32_t p_full = bar_base + 8u * (2 * kKvStages + 9);    // probabilities are in TMEM
+  const uint32_t q_tmem = bar_base + 8u * (2 * kKvStages + 10);
+  // m_ready[quadrant]: the reference maxima after a chunk are in m_shared (one arrival a chunk)
+  auto m_ready = [&](int q) { return bar_base + 8u * (2 * kKvStages + 11 + q); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(
-      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 9));
+      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 15));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -229,7 +240,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   split_range(total_chunks, p.splits, split, first_chunk, num_chunks);
 
   if (threadIdx.x == 0) {
-    read_count_storage = 0;
+    read_count_storage[0] = 0;
+    read_count_storage[1] = 0;
     for (int s = 0; s < kKvStages; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
@@ -238,11 +250,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       mbar_init(x_full(i), 1);     // local arm (expect_tx) + the peer's bulk copy bytes
       mbar_init(x_empty(i), 1);    // one arrival from the peer once all its threads have read
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_free, kSoftmaxWarps);
-    mbar_init(p_full, kSoftmaxWarps);
-    mbar_init(pv_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(s_full(i), 1);
+      mbar_init(pv_done(i), 1);
+    }
+    mbar_init(s_free, 4);        // the four warps of the group that owns the chunk
+    mbar_init(p_full, 4);
     mbar_init(q_tmem, kSoftmaxWarps);
+    for (int q = 0; q < 4; ++q) mbar_init(m_ready(q), 1);
     mbar_fence_init();
     tma_prefetch_desc(&map_cache);
     tma_prefetch_desc(&map_rope);
@@ -296,7 +311,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           const uint64_t b_desc = umma_smem_desc_sw64(stage + 4 * kBoxBytes + r * 32, 512);
           umma_bf16_ts(tmem_base + kColS, tmem_base + kColQ + 128 + r * 8, b_desc, kIdescQK, 1u);
         }
-        umma_commit(s_full);
+        umma_commit(s_full(c));
         return true;
       };
       bool ok = mbar_wait(q_tmem, 0, 0x502);
@@ -322,20 +337,20 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           umma_bf16_ts(tmem_base + kColO, tmem_base + kColP + ks * 8, b_desc, kIdescPV, (j | ks) != 0);
         }
         umma_commit(kv_empty(s));
-        umma_commit(pv_done);
+        umma_commit(pv_done(j));
       }
     }
   } else if (warp == 2 + kSoftmaxWarps) {
     // ------------------------------------------------------------ courier
-    // Tells the peer that its tile in my receive buffer has been read by all softmax warps.
+    // Tells the peer that its tile in my receive buffer has been read by the group's four warps.
     // A separate warp does it because a release at cluster scope costs close to a thousand
     // cycles, which the softmax warps cannot afford on their critical path.
     if (lane == 0) {
       for (int j = 0; j < num_chunks; ++j) {
-        const unsigned target = unsigned(kSoftmaxWarps) * unsigned(j + 1);
+        const unsigned target = 4u * unsigned((j >> 1) + 1);
         const long long start = clock64();
         bool seen = true;
-        while (*read_count < target) {
+        while (read_count[j & 1] < target) {
           __nanosleep(32);
           if (clock64() - start > kWaitBudgetCycles) {
             report_timeout(0x701);
@@ -350,36 +365,39 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     }
   } else {
     // ------------------------------------------------------------ softmax / epilogue warps
-    // Warps 2..9.  Warp w reads TMEM lanes of quadrant (w & 3); warps w and w+4 share the
-    // quadrant's 32 heads and take positions [0,32) and [32,64) of every chunk.
+    // Warps 2..9.  Warp w reads the TMEM lanes of quadrant (w & 3); warps w and w+4 serve the same
+    // 32 heads, the first for even chunks and the second for odd ones.
     const int quad = warp & 3;
-    const int part = (warp - 2) >> 2;              // which 32 positions of a chunk
+    const int group = (warp - 2) >> 2;
     const int row = quad * 32 + lane;              // head index
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const bool live = row < p.heads;
     if (num_chunks > 0) {
       // This CTA's query features -> TMEM as packed BF16 pairs: 128 latent features per thread,
-      // and the 32 rope features from the threads of part 0.
+      // and the 32 rope features from the threads of group 0.
+      const uint32_t flip = p.negate ? 0x80008000u : 0u;
       const uint4* qrow = reinterpret_cast<const uint4*>(
-          p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk + half * 256 + part * 128);
+          p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk + half * 256 + group * 128);
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t w[32];
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
           uint4 x = live ? __ldg(qrow + c * 8 + v) : make_uint4(0, 0, 0, 0);
-          w[v * 4 + 0] = x.x; w[v * 4 + 1] = x.y; w[v * 4 + 2] = x.z; w[v * 4 + 3] = x.w;
+          w[v * 4 + 0] = x.x ^ flip; w[v * 4 + 1] = x.y ^ flip;
+          w[v * 4 + 2] = x.z ^ flip; w[v * 4 + 3] = x.w ^ flip;
         }
-        tmem_st_32x32b_x32(lane_base + kColQ + part * 64 + c * 32, w);
+        tmem_st_32x32b_x32(lane_base + kColQ + group * 64 + c * 32, w);
       }
-      if (part == 0) {
+      if (group == 0) {
         const uint4* qrope = reinterpret_cast<const uint4*>(
             p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk + kDv + half * 32);
         uint32_t w[16];
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           uint4 x = live ? __ldg(qrope + v) : make_uint4(0, 0, 0, 0);
-          w[v * 4 + 0] = x.x; w[v * 4 + 1] = x.y; w[v * 4 + 2] = x.z; w[v * 4 + 3] = x.w;
+          w[v * 4 + 0] = x.x ^ flip; w[v * 4 + 1] = x.y ^ flip;
+          w[v * 4 + 2] = x.z ^ flip; w[v * 4 + 3] = x.w ^ flip;
         }
         tmem_st_32x32b_x16(lane_base + kColQ + 128, w);
       }
@@ -389,45 +407,54 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       if (lane == 0) mbar_arrive(q_tmem);
     }
 
-    float m_ref = -INFINITY;   // reference maximum (log2 domain, scaled); identical in both parts
-    float l = 0.0f;            // running sum over this thread's positions, relative to m_ref
+    float m_l = -INFINITY;     // reference maximum that `l` is relative to
+    float l = 0.0f;            // sum of this thread's probabilities
     // A wait that gives up only sets `bad`: the thread keeps executing the warp- and
-    // group-collective instructions (on meaningless data) and all softmax threads leave together
-    // at the next vote, so no barrier or collective is ever left half-attended.
+    // group-collective instructions (on meaningless data) and the threads of a group leave
+    // together at the next vote, so no barrier or collective is ever left half-attended.
     bool bad = false;
     TRINITY_MLA_TICK_DECL
+    uint4* staged = reinterpret_cast<uint4*>(send + group * kXchgBytes);
+    const uint4* received = reinterpret_cast<const uint4*>(xchg + group * kXchgBytes);
 
-    // Reads this thread's 32 partial scores of chunk c from TMEM, scales them into the log2
-    // domain, rounds to FP16 pairs (both CTAs use the rounded value, so they add identical
-    // numbers), stages them in shared memory ([8 groups of 8 positions][128 rows], conflict-free)
-    // and has one thread start the bulk asynchronous copy into the peer's receive tile.
-    auto stage_and_send = [&](int c, uint32_t (&own)[16]) -> bool {
-      const int buf = c & 1;
-      const uint32_t phase = (c >> 1) & 1u;
+    for (int j = group; j < num_chunks; j += 2) {
+      const uint32_t phase = (j >> 1) & 1u;
+      // ---- partial scores of this CTA's feature half: TMEM -> registers
       TRINITY_MLA_TICK(0)
-      if (!bad) bad = !mbar_wait(s_full, c & 1u, 0x601);
+      if (!bad) bad = !mbar_wait(s_full(j), phase, 0x601);
       TRINITY_MLA_TICK(1)
       tc_fence_after();
-      uint32_t sv[32];
-      tmem_ld_32x32b_x32(lane_base + kColS + part * 32, sv);
-      tmem_ld_wait();
-      // the scores are in registers: the next chunk's score MMAs may overwrite the buffer
+      float t[64];
+      {
+        uint32_t lo[32], hi[32];
+        tmem_ld_32x32b_x32(lane_base + kColS, lo);
+        tmem_ld_32x32b_x32(lane_base + kColS + 32, hi);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          t[i] = __uint_as_float(lo[i]);
+          t[32 + i] = __uint_as_float(hi[i]);
+        }
+      }
+      // the scores are in registers: later score MMAs may overwrite the buffer
       tc_fence_before();
       if (__all_sync(0xffffffffu, !bad) && lane == 0) mbar_arrive(s_free);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const __half2 h = __floats2half2_rn(__uint_as_float(sv[2 * i]) * p.scale_log2,
-                                            __uint_as_float(sv[2 * i + 1]) * p.scale_log2);
-        own[i] = *reinterpret_cast<const uint32_t*>(&h);
-      }
       TRINITY_MLA_TICK(2)
-      if (!bad) bad = !mbar_wait_cluster(x_empty(buf), phase ^ 1u, 0x604);
+      // ---- FP16 copy for the peer: [8 groups of 8 positions][128 rows] (conflict-free), then one
+      //      thread starts the bulk asynchronous copy into the peer's receive tile
+      if (!bad) bad = !mbar_wait_cluster(x_empty(group), phase ^ 1u, 0x604);
       TRINITY_MLA_TICK(3)
-      uint4* staged = reinterpret_cast<uint4*>(send + buf * kXchgBytes);
       if (!bad) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
-          staged[(part * 4 + g) * 128 + row] = make_uint4(own[4 * g], own[4 * g + 1], own[4 * g + 2], own[4 * g + 3]);
+        for (int g = 0; g < 8; ++g) {
+          uint32_t h[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const __half2 v = __floats2half2_rn(t[g * 8 + 2 * e], t[g * 8 + 2 * e + 1]);
+            h[e] = *reinterpret_cast<const uint32_t*>(&v);
+          }
+          staged[g * 128 + row] = make_uint4(h[0], h[1], h[2], h[3]);
+        }
       }
       fence_async_smem();
       uint32_t all_good;
@@ -435,128 +462,144 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           "{\n"
           ".reg .pred p, q;\n"
           "setp.eq.u32 p, %1, 0;\n"
-          "bar.red.and.pred q, 1, 256, p;\n"   // CTA barrier 1 over the softmax threads + vote
+          "bar.red.and.pred q, %2, 128, p;\n"   // barrier over the group's threads + vote
           "selp.u32 %0, 1, 0, q;\n"
           "}\n"
           : "=r"(all_good)
-          : "r"(bad ? 1u : 0u)
+          : "r"(bad ? 1u : 0u), "r"(1 + group)
           : "memory");
-      if (all_good && warp == 2 && lane == 0) {
-        mbar_arrive_expect_tx(x_full(buf), kXchgBytes);
-        asm volatile(
-            "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-            ::"r"(map_to_peer(xchg_smem + buf * kXchgBytes, peer)), "r"(send_smem + buf * kXchgBytes),
-              "r"(kXchgBytes), "r"(map_to_peer(x_full(buf), peer))
-            : "memory");
-      }
-      TRINITY_MLA_TICK(4)
-      return all_good != 0;
-    };
-
-    uint32_t cur[16], nxt[16];
-    bool running = num_chunks > 0 && stage_and_send(0, cur);
-    if (num_chunks > 0 && !running) bad = true;
-    for (int j = 0; running && j < num_chunks; ++j) {
-      const int buf = j & 1;
-      const uint32_t use_phase = (j >> 1) & 1u;
-      if (j + 1 < num_chunks && !stage_and_send(j + 1, nxt)) {
+      if (!all_good) {
         bad = true;
         break;
       }
-      if (!bad) bad = !mbar_wait_cluster(x_full(buf), use_phase, 0x605);
+      if ((warp & 3) == 2 && lane == 0) {
+        mbar_arrive_expect_tx(x_full(group), kXchgBytes);
+        asm volatile(
+            "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+            ::"r"(map_to_peer(xchg_smem + group * kXchgBytes, peer)), "r"(send_smem + group * kXchgBytes),
+              "r"(kXchgBytes), "r"(map_to_peer(x_full(group), peer))
+            : "memory");
+      }
+      TRINITY_MLA_TICK(4)
+      // ---- the peer's half of the scores
+      if (!bad) bad = !mbar_wait_cluster(x_full(group), phase, 0x605);
       TRINITY_MLA_TICK(5)
-      const uint4* mine = reinterpret_cast<const uint4*>(xchg + buf * kXchgBytes);
-      const int valid = p.seq - (first_chunk + j) * kKv - part * 32;  // my positions inside seq
-      float t[32];
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const uint4 other = mine[(part * 4 + g) * 128 + row];
+      for (int g = 0; g < 8; ++g) {
+        const uint4 other = received[g * 128 + row];
         const uint32_t theirs[4] = {other.x, other.y, other.z, other.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&cur[4 * g + e]));
           const float2 c2 = __half22float2(*reinterpret_cast<const __half2*>(&theirs[e]));
-          const int i = g * 8 + e * 2;
-          t[i] = i < valid ? a.x + c2.x : -INFINITY;
-          t[i + 1] = i + 1 < valid ? a.y + c2.y : -INFINITY;
-          mx4[e] = fmaxf(mx4[e], fmaxf(t[i], t[i + 1]));
+          t[g * 8 + 2 * e] += c2.x;
+          t[g * 8 + 2 * e + 1] += c2.y;
         }
       }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // this warp has read the receive tile; the courier acknowledges once all eight have
+      // this warp has read the receive tile; the courier acknowledges once all four have
       __syncwarp();
-      if (lane == 0) atomicAdd(const_cast<unsigned*>(read_count), 1u);
-      // the row maximum spans both parts
-      row_max[(part * 3 + buf) * 128 + row] = mx;
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      mx = fmaxf(mx, row_max[((part ^ 1) * 3 + buf) * 128 + row]);
+      if (lane == 0) atomicAdd(const_cast<unsigned*>(read_count) + group, 1u);
+      const int valid = p.seq - (first_chunk + j) * kKv;   // positions of this chunk inside seq
+      if (valid < kKv) {
+#pragma unroll
+        for (int i = 0; i < kKv; ++i)
+          if (i >= valid) t[i] = -INFINITY;
+      }
+      float mx4[4] = {t[0], t[1], t[2], t[3]};
+#pragma unroll
+      for (int i = 4; i < kKv; i += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], t[i + e]);
+      }
+      // position 0 of a chunk is always inside seq, so the maximum is finite
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       TRINITY_MLA_TICK(6)
-
+      // ---- reference maximum: take it over from the group that had chunk j-1, pass it on
+      float m_prev = -INFINITY;
+      if (j > 0) {
+        if (!bad) bad = !mbar_wait(m_ready(quad), (j - 1) & 1u, 0x606);
+        m_prev = m_shared[row];
+      }
+      const bool grow = mx > m_prev + kRescaleThreshold;   // always true for the first chunk
+      const float m_new = grow ? mx : m_prev;
+      m_shared[row] = m_new;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(m_ready(quad));
       // Neither the probability buffer nor the accumulator may be touched before the value MMAs
       // of chunk j-1 have finished with them.
-      if (j > 0) {
-        if (!bad) bad = !mbar_wait(pv_done, (j - 1) & 1u, 0x602);
-        tc_fence_after();
-      }
-      const bool grow = mx > m_ref + kRescaleThreshold;   // always true for the first chunk
-      if (__any_sync(0xffffffffu, grow)) {
-        const float new_ref = grow ? mx : m_ref;
-        const float f = (grow && j > 0) ? fast_exp2(m_ref - new_ref) : 1.0f;
-        if (j > 0) {
+      if (j > 0 && !bad) bad = !mbar_wait(pv_done(j - 1), ((j - 1) >> 1) & 1u, 0x602);
+      tc_fence_after();
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        const float f = grow ? fast_exp2(m_prev - m_new) : 1.0f;
 #pragma unroll 1
-          for (int c = 0; c < 128; c += 32) {   // this part's 128 accumulator columns
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(lane_base + kColO + part * 128 + c, o);
-            tmem_ld_wait();
+        for (int c = 0; c < 256; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st_32x32b_x32(lane_base + kColO + part * 128 + c, o);
-          }
-          tmem_st_wait();
-          l *= f;
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tmem_st_32x32b_x32(lane_base + kColO + c, o);
         }
-        m_ref = new_ref;
+        tmem_st_wait();
+      }
+      if (m_new != m_l) {
+        l *= fast_exp2(m_l - m_new);   // the first time: 0 * 2^-inf
+        m_l = m_new;
       }
       TRINITY_MLA_TICK(7)
-      uint32_t pw[16];
-      float sum = 0.0f;
+      // ---- probabilities
+      uint32_t pw[32];
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 = fast_exp2(t[2 * i] - m_ref);
-        const float p1 = fast_exp2(t[2 * i + 1] - m_ref);
-        sum += p0 + p1;
+      for (int i = 0; i < 32; ++i) {
+        const float p0 = fast_exp2(fmaf(t[2 * i], p.scale_log2, -m_new));
+        const float p1 = fast_exp2(fmaf(t[2 * i + 1], p.scale_log2, -m_new));
+        sum4[i & 3] += p0 + p1;
         pw[i] = pack_bf16x2(p0, p1);
       }
-      l += sum;
-      // positions [32 part, 32 part + 32) -> 16 columns of packed pairs
-      tmem_st_32x32b_x16(lane_base + kColP + part * 16, pw);
+      if (valid < kKv) {
+        // positions outside seq: exact zeros whatever the scale (0 * -inf would be a NaN)
+        float tail = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool in0 = 2 * i < valid, in1 = 2 * i + 1 < valid;
+          const float p0 = in0 ? fast_exp2(fmaf(t[2 * i], p.scale_log2, -m_new)) : 0.0f;
+          const float p1 = in1 ? fast_exp2(fmaf(t[2 * i + 1], p.scale_log2, -m_new)) : 0.0f;
+          tail += p0 + p1;
+          pw[i] = pack_bf16x2(p0, p1);
+        }
+        sum4[0] = tail; sum4[1] = 0.0f; sum4[2] = 0.0f; sum4[3] = 0.0f;
+      }
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_st_32x32b_x32(lane_base + kColP, pw);
       tmem_st_wait();
       tc_fence_before();
       const bool warp_good = __all_sync(0xffffffffu, !bad);
       if (lane == 0 && warp_good) mbar_arrive(p_full);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
       TRINITY_MLA_TICK(8)
     }
     TRINITY_MLA_TICK_FLUSH
 
+    // Every softmax thread comes here, also after a failure.  The final reference maximum of a
+    // head was written by the group that had the last chunk.
+    asm volatile("bar.sync 3, 256;" ::: "memory");
     bool ready = num_chunks > 0 && !bad;
-    if (ready) ready = mbar_wait(pv_done, (num_chunks - 1) & 1u, 0x603);
-    // the two parts of a row add their sums of probabilities
-    row_max[(part * 3 + 2) * 128 + row] = l;
-    asm volatile("bar.sync 2, 256;" ::: "memory");
-    l += row_max[((part ^ 1) * 3 + 2) * 128 + row];
+    const float m_final = num_chunks > 0 ? m_shared[row] : 0.0f;
+    if (m_l != m_final) l *= fast_exp2(m_l - m_final);   // a group without chunks holds l = 0
+    l_part[group * 128 + row] = l;
+    if (ready) ready = mbar_wait(pv_done(num_chunks - 1), ((num_chunks - 1) >> 1) & 1u, 0x603);
+    asm volatile("bar.sync 3, 256;" ::: "memory");
+    l += l_part[(group ^ 1) * 128 + row];
     if (__all_sync(0xffffffffu, ready)) {
       tc_fence_after();
       const float inv_l = 1.0f / l;
+      // group g writes accumulator columns [128 g, 128 g + 128)
       if (p.splits == 1) {
         __nv_bfloat16* orow =
-            p.out + (static_cast<long long>(b) * p.heads + row) * kDv + half * 256 + part * 128;
+            p.out + (static_cast<long long>(b) * p.heads + row) * kDv + half * 256 + group * 128;
 #pragma unroll 1
         for (int c = 0; c < 128; c += 32) {
           uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + part * 128 + c, o);
+          tmem_ld_32x32b_x32(lane_base + kColO + group * 128 + c, o);
           tmem_ld_wait();
           if (live) {
 #pragma unroll
@@ -572,11 +615,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         }
       } else {
         const long long slot = (static_cast<long long>(b) * p.splits + split) * p.heads + row;
-        float* prow = p.partial_o + slot * kDv + half * 256 + part * 128;
+        float* prow = p.partial_o + slot * kDv + half * 256 + group * 128;
 #pragma unroll 1
         for (int c = 0; c < 128; c += 32) {
           uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + part * 128 + c, o);
+          tmem_ld_32x32b_x32(lane_base + kColO + group * 128 + c, o);
           tmem_ld_wait();
           if (live) {
 #pragma unroll
@@ -587,7 +630,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
             }
           }
         }
-        if (live && half == 0 && part == 0) p.partial_lse[slot] = m_ref + log2f(l);
+        // each feature half was normalised with its own sums, so each records its own log-sum-exp
+        if (live && group == 0) p.partial_lse[slot * 2 + half] = m_final + log2f(l);
       }
     }
   }
@@ -604,25 +648,30 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   }
 }
 
-// out[b,h,:] = sum_s w_s * partial[b,s,h,:],  w_s = 2^(lse_s - max) / sum_s 2^(lse_s - max).
-// Splits that held no positions have lse = -inf and weight zero.
+// out[b,h,c] = sum_s w_s * partial[b,s,h,c],  w_s = 2^(lse_s - max) / sum_s 2^(lse_s - max), with
+// the log-sum-exp of the feature half that column c belongs to.  Splits that held no positions
+// have lse = -inf and weight zero.
 __global__ void mla_combine_kernel(const float* __restrict__ partial_o,
                                    const float* __restrict__ partial_lse,
                                    __nv_bfloat16* __restrict__ out, int heads, int splits) {
   const int bh = blockIdx.x;  // b * heads + h
   const int b = bh / heads, h = bh % heads;
-  float mx = -INFINITY;
+  float mx[2] = {-INFINITY, -INFINITY}, inv[2];
   for (int s = 0; s < splits; ++s)
-    mx = fmaxf(mx, partial_lse[(static_cast<long long>(b) * splits + s) * heads + h]);
-  float denom = 0.0f;
-  for (int s = 0; s < splits; ++s)
-    denom += exp2f(partial_lse[(static_cast<long long>(b) * splits + s) * heads + h] - mx);
-  const float inv = 1.0f / denom;
+    for (int f = 0; f < 2; ++f)
+      mx[f] = fmaxf(mx[f], partial_lse[((static_cast<long long>(b) * splits + s) * heads + h) * 2 + f]);
+  for (int f = 0; f < 2; ++f) {
+    float denom = 0.0f;
+    for (int s = 0; s < splits; ++s)
+      denom += exp2f(partial_lse[((static_cast<long long>(b) * splits + s) * heads + h) * 2 + f] - mx[f]);
+    inv[f] = 1.0f / denom;
+  }
   for (int c = threadIdx.x; c < kDv; c += blockDim.x) {
+    const int f = c >> 8;
     float acc = 0.0f;
     for (int s = 0; s < splits; ++s) {
       const long long slot = (static_cast<long long>(b) * splits + s) * heads + h;
-      const float w = exp2f(partial_lse[slot] - mx) * inv;
+      const float w = exp2f(partial_lse[slot * 2 + f] - mx[f]) * inv[f];
       if (w != 0.0f) acc += w * partial_o[slot * kDv + c];
     }
     out[static_cast<long long>(bh) * kDv + c] = __float2bfloat16(acc);
@@ -632,7 +681,7 @@ __global__ void mla_combine_kernel(const float* __restrict__ partial_o,
 size_t scratch_bytes(int batch, int heads, int d_v, int splits) {
   if (splits <= 1) return 0;
   const size_t slots = size_t(batch) * splits * heads;
-  return ((slots * d_v * 4 + 255) / 256) * 256 + ((slots * 4 + 255) / 256) * 256;
+  return ((slots * d_v * 4 + 255) / 256) * 256 + ((slots * 2 * 4 + 255) / 256) * 256;
 }
 
 }  // namespace
@@ -723,7 +772,8 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   p.heads = a.heads;
   p.seq = a.seq;
   p.splits = splits;
-  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.scale_log2 = fabsf(a.scale) * 1.4426950408889634f;
+  p.negate = a.scale < 0.0f ? 1 : 0;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(2, splits, a.batch);
   config.blockDim = dim3(kMlaThreads);
