@@ -27,18 +27,19 @@
 // and one 64-byte-swizzled rope box of 32 features), two receive and two send tiles of 16 KB.
 //
 //   warp 0    TMA producer (the cache chunk ring: 4 latent boxes + rope box per chunk)
-//   warp 1    MMA issuer: QK(j) = 18 TMEM-A MMAs (N=64), PV(j) = 4 TMEM-A MMAs (N=256).  The
-//             scores of chunk j+2 are issued as soon as the softmax group has copied the scores
-//             of chunk j+1 out of TMEM, which it does before it turns to chunk j; so the score
-//             MMAs run two chunks ahead of the value MMAs and never queue behind a softmax.
-//   warps 2-9 two softmax groups of four warps; group g takes the chunks with j % 2 == g and
+//   warp 1    score MMA issuer: QK(j) = 18 TMEM-A MMAs (N=64), issued as soon as the softmax
+//             group has copied the scores of chunk j-1 out of TMEM and the chunk's cache stage
+//             has landed, so the scores run ahead of the values by up to the depth of the ring
+//   warp 15   value MMA issuer: PV(j) = 4 TMEM-A MMAs (N=256), issued when the chunk's
+//             probabilities are in TMEM
+//   warps 2-13 three softmax groups of four warps; group g takes the chunks with j % 3 == g and
 //             one thread handles a head's whole 64-position row of a chunk: partial-score load,
 //             exchange with the peer CTA, row maximum, exponentials, BF16 probabilities into
-//             their TMEM buffer.  While one group waits for the peer's tile the other computes.
+//             their TMEM buffer.  While one group waits for the peer's tile the others compute.
 //             The running reference maximum of a head passes from group to group through
 //             shared memory (one mbarrier per TMEM lane quadrant orders the hand-over); the
 //             accumulator is rescaled only when the maximum grows by more than 2^8.
-//   warp 10   courier: acknowledges consumed exchange tiles to the peer CTA
+//   warp 14   courier: acknowledges consumed exchange tiles to the peer CTA
 //
 // With kv_splits == 1 the CTA writes BF16 output directly.  Otherwise it writes a normalised
 // FP32 partial and its log-sum-exp (one per feature half) to scratch and a small kernel merges
@@ -52,18 +53,21 @@
 namespace trinity_sm100 {
 namespace {
 
-constexpr int kSoftmaxWarps = 8;                 // two groups of four warps (one per TMEM lane quadrant)
+constexpr int kGroups = 3;                       // softmax groups; group g owns chunks j % kGroups == g
+constexpr int kSoftmaxWarps = 4 * kGroups;       // four warps (one per TMEM lane quadrant) per group
 constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
-constexpr int kMlaThreads = 64 + kSoftmaxThreads + 32;  // producer, MMA issuer, softmax group, courier
+// producer, score MMA issuer, softmax groups, courier, value MMA issuer
+constexpr int kMlaThreads = 64 + kSoftmaxThreads + 64;
 constexpr int kKv = 64;                        // cache positions per chunk
 constexpr int kDqk = 576, kDv = 512;
 constexpr int kKvStages = 4;
+constexpr int kPrefetchAhead = 4;              // chunks requested into L2 beyond the stage ring
 constexpr int kBoxBytes = kKv * 128;           // 8192: one [64 positions x 64 features] box
 constexpr int kRopeBoxBytes = kKv * 64;        // 4096: [64 positions x 32 rope features]
 constexpr int kStageBytes = 4 * kBoxBytes + kRopeBoxBytes;  // 36864
 constexpr int kXchgBytes = 128 * kKv * 2;      // one partial score tile in FP16: 16384
 // two receive tiles + two send tiles: the exchange of chunk j+1 overlaps the softmax of chunk j
-constexpr int kMlaSmem = 1024 + kKvStages * kStageBytes + 4 * kXchgBytes + 256;
+constexpr int kMlaSmem = 1024 + kKvStages * kStageBytes + 4 * kXchgBytes + 512;
 // TMEM columns: accumulator, scores, probabilities, query (128 latent + 16 rope word columns)
 constexpr uint32_t kColO = 0, kColS = 256, kColP = 320, kColQ = 352, kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;      // in log2 units: probabilities stay below 2^8
@@ -81,11 +85,20 @@ struct MlaParams {
 // Optional per-phase cycle counters of the softmax loop: a tuning harness that defines
 // TRINITY_MLA_TIMING reads g_mla_ticks; the library build compiles the hooks away.
 #ifdef TRINITY_MLA_TIMING
-__device__ unsigned long long g_mla_ticks[16];
+__device__ unsigned long long g_mla_ticks[24];
+__device__ int g_mla_experiment;   // bit 0: no rope MMAs, bit 1: no exchange, bit 2: cache loaded only once per stage
+#define TRINITY_MLA_EXPERIMENT(bit) (g_mla_experiment & (bit))
 #define TRINITY_MLA_TICK_DECL long long tick_last = clock64(); unsigned long long tick_sum[12] = {};
 #define TRINITY_MLA_TICK(i) { const long long now = clock64(); tick_sum[i] += now - tick_last; tick_last = now; }
 #define TRINITY_MLA_TICK_FLUSH if (blockIdx.z == 0 && blockIdx.y == 0 && blockIdx.x == 0 && threadIdx.x == 64) { for (int i = 0; i < 12; ++i) g_mla_ticks[i] = tick_sum[i]; }
+#define TRINITY_MLA_ISSUER_DECL long long issuer_last = clock64(); unsigned long long issuer_sum[5] = {}; int why = 1;
+#define TRINITY_MLA_ISSUER_TICK(i) { const long long now = clock64(); issuer_sum[i] += now - issuer_last; issuer_last = now; }
+#define TRINITY_MLA_ISSUER_FLUSH if (blockIdx.z == 0 && blockIdx.y == 0 && blockIdx.x == 0) { for (int i = 0; i < 5; ++i) g_mla_ticks[16 + i] = issuer_sum[i]; }
 #else
+#define TRINITY_MLA_EXPERIMENT(bit) 0
+#define TRINITY_MLA_ISSUER_DECL
+#define TRINITY_MLA_ISSUER_TICK(i)
+#define TRINITY_MLA_ISSUER_FLUSH
 #define TRINITY_MLA_TICK_DECL
 #define TRINITY_MLA_TICK(i)
 #define TRINITY_MLA_TICK_FLUSH
@@ -197,7 +210,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
                   const __grid_constant__ CUtensorMap map_rope, const MlaParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ float m_shared[128];               // reference maximum of each head (log2 domain)
-  __shared__ float l_part[2 * 128];             // [group][head] sums of probabilities at the end
+  __shared__ float l_part[kGroups * 128];       // [group][head] sums of probabilities at the end
   __shared__ unsigned read_count_storage[2];    // per receive tile: warps that have read it
   volatile unsigned* read_count = read_count_storage;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -209,24 +222,26 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   uint8_t* xchg = smem + kKvStages * kStageBytes;
   uint8_t* send = xchg + 2 * kXchgBytes;
   // barriers: kv_full[stages], kv_empty[stages], x_full[2], x_empty[2], s_full[2], pv_done[2],
-  //           s_free, p_full, q_tmem, m_ready[4].  s_free and p_full complete once per chunk and
+  //           s_free, p_full, q_tmem, m_ready[3][4].  s_free and p_full complete once per chunk and
   //           are waited on by one thread, chunk after chunk (chunk j is phase j & 1).  s_full
-  //           and pv_done are waited on by the softmax groups, which skip every other chunk; a
-  //           parity wait is only meaningful on consecutive phases, so these two exist once per
-  //           chunk parity (chunk j is phase (j >> 1) & 1 of barrier j & 1).
+  //           and pv_done are waited on by the softmax groups, which see only every third chunk;
+  //           a parity wait is only meaningful on consecutive phases, so these two (and m_ready)
+  //           exist once per group (chunk j is phase (j / 3) & 1 of barrier j % 3).
   auto kv_full = [&](int s) { return bar_base + 8u * s; };
   auto kv_empty = [&](int s) { return bar_base + 8u * (kKvStages + s); };
   auto x_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + b); };
   auto x_empty = [&](int b) { return bar_base + 8u * (2 * kKvStages + 2 + b); };
-  auto s_full = [&](int c) { return bar_base + 8u * (2 * kKvStages + 4 + (c & 1)); };   // scores of chunk c are in TMEM
-  auto pv_done = [&](int c) { return bar_base + 8u * (2 * kKvStages + 6 + (c & 1)); };  // values of chunk c are accumulated
-  const uint32_t s_free = bar_base + 8u * (2 * kKvStages + 8);    // the scores have been copied out
-  const uint32_t p_full = bar_base + 8u * (2 * kKvStages + 9);    // probabilities are in TMEM
-  const uint32_t q_tmem = bar_base + 8u * (2 * kKvStages + 10);
-  // m_ready[quadrant]: the reference maxima after a chunk are in m_shared (one arrival a chunk)
-  auto m_ready = [&](int q) { return bar_base + 8u * (2 * kKvStages + 11 + q); };
+  auto s_full = [&](int c) { return bar_base + 8u * (2 * kKvStages + 4 + c % kGroups); };              // scores of chunk c are in TMEM
+  auto pv_done = [&](int c) { return bar_base + 8u * (2 * kKvStages + 4 + kGroups + c % kGroups); };   // values of chunk c are accumulated
+  auto group_phase = [](int c) { return static_cast<uint32_t>((c / kGroups) & 1); };
+  const uint32_t s_free = bar_base + 8u * (2 * kKvStages + 4 + 2 * kGroups);   // the scores have been copied out
+  const uint32_t p_full = s_free + 8u;                                         // probabilities are in TMEM
+  const uint32_t q_tmem = s_free + 16u;
+  // m_ready[group][quadrant]: the reference maxima after chunk c are in m_shared (one arrival a
+  // chunk, by the warp of group c % 3 that serves the quadrant)
+  auto m_ready = [&](int c, int q) { return s_free + 24u + 8u * ((c % kGroups) * 4 + q); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(
-      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 15));
+      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 4 + 2 * kGroups + 3 + 4 * kGroups));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -250,14 +265,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       mbar_init(x_full(i), 1);     // local arm (expect_tx) + the peer's bulk copy bytes
       mbar_init(x_empty(i), 1);    // one arrival from the peer once all its threads have read
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kGroups; ++i) {
       mbar_init(s_full(i), 1);
       mbar_init(pv_done(i), 1);
     }
     mbar_init(s_free, 4);        // the four warps of the group that owns the chunk
     mbar_init(p_full, 4);
     mbar_init(q_tmem, kSoftmaxWarps);
-    for (int q = 0; q < 4; ++q) mbar_init(m_ready(q), 1);
+    for (int q = 0; q < 4 * kGroups; ++q) mbar_init(m_ready(q >> 2, q & 3), 1);
     mbar_fence_init();
     tma_prefetch_desc(&map_cache);
     tma_prefetch_desc(&map_rope);
@@ -275,10 +290,27 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0 && num_chunks > 0) {
+      // A stage is held from its load until the chunk's values are accumulated, several
+      // thousand cycles, so the ring alone keeps too few bytes in flight to cover the memory
+      // latency.  Chunks further ahead are therefore requested into L2 first; the ring's own
+      // loads then find them there.
+      auto prefetch_chunk = [&](int c) {
+        if (c >= num_chunks) return;
+        const int kv0 = (first_chunk + c) * kKv;
+#pragma unroll
+        for (int f = 0; f < 4; ++f) tma_prefetch_l2_3d(&map_cache, int(half) * 256 + f * 64, kv0, b);
+        tma_prefetch_l2_3d(&map_rope, kDv + int(half) * 32, kv0, b);
+      };
+      for (int c = kKvStages; c < kKvStages + kPrefetchAhead; ++c) prefetch_chunk(c);
       for (int j = 0; j < num_chunks; ++j) {
         const int s = j % kKvStages;
         const uint32_t phase = (j / kKvStages) & 1u;
+        prefetch_chunk(j + kKvStages + kPrefetchAhead);
         if (!mbar_wait(kv_empty(s), phase ^ 1u, 0x401)) break;
+        if (TRINITY_MLA_EXPERIMENT(4) && j >= kKvStages) {
+          mbar_arrive(kv_full(s));
+          continue;
+        }
         mbar_arrive_expect_tx(kv_full(s), kStageBytes);
         const int kv0 = (first_chunk + j) * kKv;
         const uint32_t dst = kv_smem + s * kStageBytes;
@@ -289,55 +321,61 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ score MMA issuer
+    // Scores and values are issued by different threads so that neither waits for the other's
+    // inputs: the scores of a chunk need its cache stage and a score buffer that the softmax
+    // group has copied out (they run ahead of the values by as many chunks as there are stages
+    // to hold), the values need the chunk's probabilities.  An issuing thread shares its
+    // scheduler with three softmax warps and every instruction between two MMAs costs
+    // tensor-pipe time, so one descriptor per operand kind is built per chunk and the K-steps
+    // only add constants to its address field (units of 16 bytes; the field cannot overflow,
+    // shared memory ends below 256 KB).
     if (lane == 0 && num_chunks > 0) {
       constexpr uint32_t kIdescQK = umma_idesc_bf16(128, kKv, 0, 0);
-      constexpr uint32_t kIdescPV = umma_idesc_bf16(128, 256, 0, 1);
-      // Scores of one chunk: 16 K-steps over the latent boxes and 2 over the rope box, the query
-      // always from TMEM.
-      auto issue_scores = [&](int c) -> bool {
-        const int s = c % kKvStages;
-        if (!mbar_wait(kv_full(s), (c / kKvStages) & 1u, 0x503)) return false;
-        tc_fence_after();
-        const uint32_t stage = kv_smem + s * kStageBytes;
-#pragma unroll
-        for (int ks = 0; ks < 16; ++ks) {
-          const uint64_t b_desc =
-              umma_smem_desc(stage + (ks / 4) * kBoxBytes + (ks % 4) * 32, 16, 1024);
-          umma_bf16_ts(tmem_base + kColS, tmem_base + kColQ + ks * 8, b_desc, kIdescQK, ks != 0);
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const uint64_t b_desc = umma_smem_desc_sw64(stage + 4 * kBoxBytes + r * 32, 512);
-          umma_bf16_ts(tmem_base + kColS, tmem_base + kColQ + 128 + r * 8, b_desc, kIdescQK, 1u);
-        }
-        umma_commit(s_full(c));
-        return true;
-      };
+      const uint32_t d_scores = tmem_base + kColS, a_query = tmem_base + kColQ;
+      TRINITY_MLA_ISSUER_DECL
       bool ok = mbar_wait(q_tmem, 0, 0x502);
-      tc_fence_after();
-      // The score buffer is free as soon as the softmax group holds a chunk in registers, which for
-      // chunk c happens at the start of its step c-1; so the scores run two chunks ahead of the
-      // values and are complete when the softmax group asks for them.
-      ok = ok && issue_scores(0);
-      if (ok && num_chunks > 1) ok = mbar_wait(s_free, 0, 0x505) && issue_scores(1);
-      for (int j = 0; j < num_chunks && ok; ++j) {
-        if (j + 2 < num_chunks) {
-          if (!mbar_wait(s_free, (j + 1) & 1u, 0x505)) break;
-          if (!issue_scores(j + 2)) break;
-        }
-        const int s = j % kKvStages;
-        if (!mbar_wait(p_full, j & 1u, 0x504)) break;
+      for (int c = 0; c < num_chunks && ok; ++c) {
+        TRINITY_MLA_ISSUER_TICK(3)
+        if (c > 0 && !mbar_wait(s_free, (c - 1) & 1u, 0x505)) break;
+        TRINITY_MLA_ISSUER_TICK(0)
+        if (!mbar_wait(kv_full(c % kKvStages), (c / kKvStages) & 1u, 0x503)) break;
+        TRINITY_MLA_ISSUER_TICK(1)
         tc_fence_after();
-        const uint32_t stage = kv_smem + s * kStageBytes;
+        // 16 K-steps over the latent boxes and 2 over the rope box, the query always from TMEM
+        const uint32_t stage = kv_smem + (c % kKvStages) * kStageBytes;
+        const uint64_t latent = umma_smem_desc(stage, 16, 1024);
+        const uint64_t rope = umma_smem_desc_sw64(stage + 4 * kBoxBytes, 512);
 #pragma unroll
-        for (int ks = 0; ks < kKv / 16; ++ks) {
-          // values: N-major, 64-latent boxes 8192 B apart, 8-position groups 1024 B apart
-          const uint64_t b_desc = umma_smem_desc(stage + ks * 2048, kBoxBytes, 1024);
-          umma_bf16_ts(tmem_base + kColO, tmem_base + kColP + ks * 8, b_desc, kIdescPV, (j | ks) != 0);
-        }
+        for (int ks = 0; ks < 16; ++ks)
+          umma_bf16_ts(d_scores, a_query + ks * 8, latent + (((ks / 4) * kBoxBytes + (ks % 4) * 32) >> 4),
+                       kIdescQK, ks != 0);
+        if (!TRINITY_MLA_EXPERIMENT(1))
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+          umma_bf16_ts(d_scores, a_query + 128 + r * 8, rope + ((r * 32) >> 4), kIdescQK, 1u);
+        umma_commit(s_full(c));
+      }
+      TRINITY_MLA_ISSUER_TICK(3)
+      TRINITY_MLA_ISSUER_FLUSH
+    }
+  } else if (warp == 3 + kSoftmaxWarps) {
+    // ------------------------------------------------------------ value MMA issuer
+    // Probabilities from TMEM, the chunk's latent boxes N-major (64-latent boxes 8192 B apart,
+    // 8-position groups 1024 B apart).
+    if (lane == 0 && num_chunks > 0) {
+      constexpr uint32_t kIdescPV = umma_idesc_bf16(128, 256, 0, 1);
+      const uint32_t d_out = tmem_base + kColO, a_prob = tmem_base + kColP;
+      for (int c = 0; c < num_chunks; ++c) {
+        if (!mbar_wait(p_full, c & 1u, 0x504)) break;
+        tc_fence_after();
+        const int s = c % kKvStages;
+        const uint64_t values = umma_smem_desc(kv_smem + s * kStageBytes, kBoxBytes, 1024);
+#pragma unroll
+        for (int ks = 0; ks < kKv / 16; ++ks)
+          umma_bf16_ts(d_out, a_prob + ks * 8, values + ((ks * 2048) >> 4), kIdescPV, (c | ks) != 0);
         umma_commit(kv_empty(s));
-        umma_commit(pv_done(j));
+        umma_commit(pv_done(c));
       }
     }
   } else if (warp == 2 + kSoftmaxWarps) {
@@ -345,7 +383,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     // Tells the peer that its tile in my receive buffer has been read by the group's four warps.
     // A separate warp does it because a release at cluster scope costs close to a thousand
     // cycles, which the softmax warps cannot afford on their critical path.
-    if (lane == 0) {
+    if (lane == 0 && !TRINITY_MLA_EXPERIMENT(2)) {
       for (int j = 0; j < num_chunks; ++j) {
         const unsigned target = 4u * unsigned((j >> 1) + 1);
         const long long start = clock64();
@@ -365,41 +403,37 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     }
   } else {
     // ------------------------------------------------------------ softmax / epilogue warps
-    // Warps 2..9.  Warp w reads the TMEM lanes of quadrant (w & 3); warps w and w+4 serve the same
-    // 32 heads, the first for even chunks and the second for odd ones.
+    // Warp w reads the TMEM lanes of quadrant (w & 3); the warps w, w+4, w+8 of the three groups
+    // serve the same 32 heads in turn.
     const int quad = warp & 3;
     const int group = (warp - 2) >> 2;
     const int row = quad * 32 + lane;              // head index
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const bool live = row < p.heads;
     if (num_chunks > 0) {
-      // This CTA's query features -> TMEM as packed BF16 pairs: 128 latent features per thread,
-      // and the 32 rope features from the threads of group 0.
+      // This CTA's query features -> TMEM as packed BF16 pairs: four blocks of 64 latent
+      // features and one of 32 rope features, dealt out to the groups.
       const uint32_t flip = p.negate ? 0x80008000u : 0u;
-      const uint4* qrow = reinterpret_cast<const uint4*>(
-          p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk + half * 256 + group * 128);
+      const __nv_bfloat16* qhead = p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int blk = group; blk < 5; blk += kGroups) {
+        const uint4* src = reinterpret_cast<const uint4*>(blk < 4 ? qhead + half * 256 + blk * 64
+                                                                  : qhead + kDv + half * 32);
         uint32_t w[32];
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
-          uint4 x = live ? __ldg(qrow + c * 8 + v) : make_uint4(0, 0, 0, 0);
+          uint4 x = (live && (blk < 4 || v < 4)) ? __ldg(src + v) : make_uint4(0, 0, 0, 0);
           w[v * 4 + 0] = x.x ^ flip; w[v * 4 + 1] = x.y ^ flip;
           w[v * 4 + 2] = x.z ^ flip; w[v * 4 + 3] = x.w ^ flip;
         }
-        tmem_st_32x32b_x32(lane_base + kColQ + group * 64 + c * 32, w);
-      }
-      if (group == 0) {
-        const uint4* qrope = reinterpret_cast<const uint4*>(
-            p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk + kDv + half * 32);
-        uint32_t w[16];
+        if (blk < 4) {
+          tmem_st_32x32b_x32(lane_base + kColQ + blk * 32, w);
+        } else {
+          uint32_t r[16];
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 x = live ? __ldg(qrope + v) : make_uint4(0, 0, 0, 0);
-          w[v * 4 + 0] = x.x ^ flip; w[v * 4 + 1] = x.y ^ flip;
-          w[v * 4 + 2] = x.z ^ flip; w[v * 4 + 3] = x.w ^ flip;
+          for (int i = 0; i < 16; ++i) r[i] = w[i];
+          tmem_st_32x32b_x16(lane_base + kColQ + 128, r);
         }
-        tmem_st_32x32b_x16(lane_base + kColQ + 128, w);
       }
       tmem_st_wait();
       tc_fence_before();
@@ -414,14 +448,16 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     // together at the next vote, so no barrier or collective is ever left half-attended.
     bool bad = false;
     TRINITY_MLA_TICK_DECL
-    uint4* staged = reinterpret_cast<uint4*>(send + group * kXchgBytes);
-    const uint4* received = reinterpret_cast<const uint4*>(xchg + group * kXchgBytes);
 
-    for (int j = group; j < num_chunks; j += 2) {
+    for (int j = group; j < num_chunks; j += kGroups) {
+      // exchange tiles alternate between two buffers by chunk parity
+      const int buf = j & 1;
       const uint32_t phase = (j >> 1) & 1u;
+      uint4* staged = reinterpret_cast<uint4*>(send + buf * kXchgBytes);
+      const uint4* received = reinterpret_cast<const uint4*>(xchg + buf * kXchgBytes);
       // ---- partial scores of this CTA's feature half: TMEM -> registers
       TRINITY_MLA_TICK(0)
-      if (!bad) bad = !mbar_wait(s_full(j), phase, 0x601);
+      if (!bad) bad = !mbar_wait(s_full(j), group_phase(j), 0x601);
       TRINITY_MLA_TICK(1)
       tc_fence_after();
       float t[64];
@@ -442,9 +478,24 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       TRINITY_MLA_TICK(2)
       // ---- FP16 copy for the peer: [8 groups of 8 positions][128 rows] (conflict-free), then one
       //      thread starts the bulk asynchronous copy into the peer's receive tile
-      if (!bad) bad = !mbar_wait_cluster(x_empty(group), phase ^ 1u, 0x604);
+      // The buffers were last used for chunk j-2, by another group.  Once that group has read its
+      // receive tile, the exchange barriers of this buffer are in the phase this chunk expects.
+      if (!TRINITY_MLA_EXPERIMENT(2))
+      if (j >= 2 && !bad) {
+        const unsigned target = 4u * unsigned(j >> 1);
+        const long long start = clock64();
+        while (read_count[buf] < target) {
+          if (clock64() - start > kWaitBudgetCycles) {
+            report_timeout(0x607);
+            bad = true;
+            break;
+          }
+        }
+      }
+      if (!TRINITY_MLA_EXPERIMENT(2))
+      if (!bad) bad = !mbar_wait_cluster(x_empty(buf), phase ^ 1u, 0x604);
       TRINITY_MLA_TICK(3)
-      if (!bad) {
+      if (!bad && !TRINITY_MLA_EXPERIMENT(2)) {
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           uint32_t h[4];
@@ -472,20 +523,22 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         bad = true;
         break;
       }
-      if ((warp & 3) == 2 && lane == 0) {
-        mbar_arrive_expect_tx(x_full(group), kXchgBytes);
+      if ((warp & 3) == 2 && lane == 0 && !TRINITY_MLA_EXPERIMENT(2)) {
+        mbar_arrive_expect_tx(x_full(buf), kXchgBytes);
         asm volatile(
             "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-            ::"r"(map_to_peer(xchg_smem + group * kXchgBytes, peer)), "r"(send_smem + group * kXchgBytes),
-              "r"(kXchgBytes), "r"(map_to_peer(x_full(group), peer))
+            ::"r"(map_to_peer(xchg_smem + buf * kXchgBytes, peer)), "r"(send_smem + buf * kXchgBytes),
+              "r"(kXchgBytes), "r"(map_to_peer(x_full(buf), peer))
             : "memory");
       }
       TRINITY_MLA_TICK(4)
       // ---- the peer's half of the scores
-      if (!bad) bad = !mbar_wait_cluster(x_full(group), phase, 0x605);
+      if (!TRINITY_MLA_EXPERIMENT(2))
+      if (!bad) bad = !mbar_wait_cluster(x_full(buf), phase, 0x605);
       TRINITY_MLA_TICK(5)
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
+        if (TRINITY_MLA_EXPERIMENT(2)) break;
         const uint4 other = received[g * 128 + row];
         const uint32_t theirs[4] = {other.x, other.y, other.z, other.w};
 #pragma unroll
@@ -497,7 +550,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       }
       // this warp has read the receive tile; the courier acknowledges once all four have
       __syncwarp();
-      if (lane == 0) atomicAdd(const_cast<unsigned*>(read_count) + group, 1u);
+      if (lane == 0 && !TRINITY_MLA_EXPERIMENT(2)) atomicAdd(const_cast<unsigned*>(read_count) + buf, 1u);
       const int valid = p.seq - (first_chunk + j) * kKv;   // positions of this chunk inside seq
       if (valid < kKv) {
 #pragma unroll
@@ -516,36 +569,18 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       // ---- reference maximum: take it over from the group that had chunk j-1, pass it on
       float m_prev = -INFINITY;
       if (j > 0) {
-        if (!bad) bad = !mbar_wait(m_ready(quad), (j - 1) & 1u, 0x606);
+        if (!bad) bad = !mbar_wait(m_ready(j - 1, quad), group_phase(j - 1), 0x606);
         m_prev = m_shared[row];
       }
       const bool grow = mx > m_prev + kRescaleThreshold;   // always true for the first chunk
       const float m_new = grow ? mx : m_prev;
       m_shared[row] = m_new;
       __syncwarp();
-      if (lane == 0) mbar_arrive(m_ready(quad));
-      // Neither the probability buffer nor the accumulator may be touched before the value MMAs
-      // of chunk j-1 have finished with them.
-      if (j > 0 && !bad) bad = !mbar_wait(pv_done(j - 1), ((j - 1) >> 1) & 1u, 0x602);
-      tc_fence_after();
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        const float f = grow ? fast_exp2(m_prev - m_new) : 1.0f;
-#pragma unroll 1
-        for (int c = 0; c < 256; c += 32) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-          tmem_st_32x32b_x32(lane_base + kColO + c, o);
-        }
-        tmem_st_wait();
-      }
+      if (lane == 0) mbar_arrive(m_ready(j, quad));
       if (m_new != m_l) {
         l *= fast_exp2(m_l - m_new);   // the first time: 0 * 2^-inf
         m_l = m_new;
       }
-      TRINITY_MLA_TICK(7)
       // ---- probabilities
       uint32_t pw[32];
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -570,6 +605,24 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         sum4[0] = tail; sum4[1] = 0.0f; sum4[2] = 0.0f; sum4[3] = 0.0f;
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      TRINITY_MLA_TICK(7)
+      // Neither the probability buffer nor the accumulator may be touched before the value MMAs
+      // of chunk j-1 have finished with them.
+      if (j > 0 && !bad) bad = !mbar_wait(pv_done(j - 1), group_phase(j - 1), 0x602);
+      tc_fence_after();
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        const float f = grow ? fast_exp2(m_prev - m_new) : 1.0f;
+#pragma unroll 1
+        for (int c = 0; c < 256; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tmem_st_32x32b_x32(lane_base + kColO + c, o);
+        }
+        tmem_st_wait();
+      }
       tmem_st_32x32b_x32(lane_base + kColP, pw);
       tmem_st_wait();
       tc_fence_before();
@@ -581,25 +634,27 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
 
     // Every softmax thread comes here, also after a failure.  The final reference maximum of a
     // head was written by the group that had the last chunk.
-    asm volatile("bar.sync 3, 256;" ::: "memory");
+    asm volatile("bar.sync 4, %0;" ::"n"(kSoftmaxThreads) : "memory");
     bool ready = num_chunks > 0 && !bad;
     const float m_final = num_chunks > 0 ? m_shared[row] : 0.0f;
     if (m_l != m_final) l *= fast_exp2(m_l - m_final);   // a group without chunks holds l = 0
     l_part[group * 128 + row] = l;
-    if (ready) ready = mbar_wait(pv_done(num_chunks - 1), ((num_chunks - 1) >> 1) & 1u, 0x603);
-    asm volatile("bar.sync 3, 256;" ::: "memory");
-    l += l_part[(group ^ 1) * 128 + row];
+    if (ready) ready = mbar_wait(pv_done(num_chunks - 1), group_phase(num_chunks - 1), 0x603);
+    asm volatile("bar.sync 4, %0;" ::"n"(kSoftmaxThreads) : "memory");
+    l = 0.0f;
+#pragma unroll
+    for (int g = 0; g < kGroups; ++g) l += l_part[g * 128 + row];
     if (__all_sync(0xffffffffu, ready)) {
       tc_fence_after();
       const float inv_l = 1.0f / l;
-      // group g writes accumulator columns [128 g, 128 g + 128)
+      // the eight 32-column blocks of the accumulator are dealt out to the groups
       if (p.splits == 1) {
         __nv_bfloat16* orow =
-            p.out + (static_cast<long long>(b) * p.heads + row) * kDv + half * 256 + group * 128;
+            p.out + (static_cast<long long>(b) * p.heads + row) * kDv + half * 256;
 #pragma unroll 1
-        for (int c = 0; c < 128; c += 32) {
+        for (int c = group * 32; c < 256; c += kGroups * 32) {
           uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + group * 128 + c, o);
+          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
           tmem_ld_wait();
           if (live) {
 #pragma unroll
@@ -615,11 +670,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         }
       } else {
         const long long slot = (static_cast<long long>(b) * p.splits + split) * p.heads + row;
-        float* prow = p.partial_o + slot * kDv + half * 256 + group * 128;
+        float* prow = p.partial_o + slot * kDv + half * 256;
 #pragma unroll 1
-        for (int c = 0; c < 128; c += 32) {
+        for (int c = group * 32; c < 256; c += kGroups * 32) {
           uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + group * 128 + c, o);
+          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
           tmem_ld_wait();
           if (live) {
 #pragma unroll

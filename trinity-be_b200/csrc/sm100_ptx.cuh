@@ -54,6 +54,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+// Non-blocking test of a phase parity, for a thread that polls several barriers in turn.
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
 // Bounded wait on a phase parity.  Returns false (and records `site`) if the budget runs out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t site) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -88,6 +102,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+// Brings one box of a 3-D tensor into L2 without a shared-memory destination.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int32_t x, int32_t y,
+                                                   int32_t z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z)
+               : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int32_t x,
                                              int32_t y) {
