@@ -248,7 +248,7 @@ def make_workload(name, device, world=None):
         w.l2_note, w.flush = "inputs larger than L2", False
 
         def device_step():
-            k.mla_decode(qd, cd, scale, kv_splits=splits, out=od, scratch=scratch)
+            k.mla_decode(qd, cd, scale, kv_splits=0, out=od, scratch=scratch)
 
         def e2e_step():
             qd.copy_(host_q, non_blocking=True)

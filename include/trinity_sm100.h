@@ -202,7 +202,10 @@ typedef struct trinity_sm100_mla {
   void* scratch;
   size_t scratch_bytes;
   int32_t batch, heads, seq, d_qk, d_v;
-  int32_t kv_splits; /* 0 = choose from the SM count */
+  int32_t kv_splits; /* > 0: that many equal splits of every sequence; 0: chosen by the library
+                        (scratch for trinity_sm100_mla_default_splits() slots per sequence);
+                        < 0: the balanced schedule (equal runs of KV chunks over all sequences,
+                        scratch for trinity_sm100_mla_balanced_slots() slots per sequence) */
   float scale;
   int32_t reserved;
 } trinity_sm100_mla;
@@ -210,6 +213,7 @@ typedef struct trinity_sm100_mla {
 TRINITY_SM100_API size_t trinity_sm100_mla_scratch_bytes(int32_t batch, int32_t heads, int32_t d_v,
                                        int32_t kv_splits);
 TRINITY_SM100_API int trinity_sm100_mla_default_splits(int32_t batch, int32_t seq);
+TRINITY_SM100_API int trinity_sm100_mla_balanced_slots(int32_t batch, int32_t seq);
 TRINITY_SM100_API int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void* stream);
 
 /*

@@ -44,6 +44,35 @@ def test_against_oracle(kernels, batch, heads, seq, splits):
     assert_close_bf16(out, expected, max_ulp=None, max_abs=2e-2)
 
 
+@pytest.mark.parametrize("batch,heads,seq", [
+    (5, 128, 1000),     # clusters own parts of two sequences; ragged last chunk
+    (9, 128, 1536),     # three-chunk pieces, most sequences cut twice
+    (100, 32, 320),     # more sequences than SM pairs: several whole sequences per cluster
+    (1, 128, 8192),     # one sequence over many clusters
+])
+@pytest.mark.parametrize("mode", [-1, 0])
+def test_balanced_and_automatic_schedule(kernels, batch, heads, seq, mode):
+    """kv_splits = -1: the (sequence, chunk) grid is cut into equal runs, one per cluster; a
+    cluster then works through pieces of several sequences with one set of barriers.
+    kv_splits = 0: the library chooses between that and equal splits."""
+    q, cache = wl.mla_inputs(batch, heads, seq, 576, 99 + seq)
+    out = kernels.mla_decode(q.to(DEV), cache.to(DEV), SCALE, kv_splits=mode).cpu()
+    picks = sorted({0, batch // 2, batch - 1})
+    expected = wl.mla_oracle(q, cache, SCALE, 512, batches=picks)
+    assert_close_bf16(out[picks], expected, max_ulp=None, max_abs=2e-2)
+    # every sequence, not only the picked ones, against the one-cluster-per-sequence path
+    single = kernels.mla_decode(q.to(DEV), cache.to(DEV), SCALE, kv_splits=1).cpu()
+    assert_close_bf16(out, single, max_ulp=None, max_abs=2e-2)
+
+
+def test_negative_scale(kernels):
+    """A negative scale is applied by flipping the query's sign on its way into tensor memory."""
+    q, cache = wl.mla_inputs(2, 128, 256, 576, 777)
+    out = kernels.mla_decode(q.to(DEV), cache.to(DEV), -SCALE, kv_splits=1).cpu()
+    expected = wl.mla_oracle(q, cache, -SCALE, 512)
+    assert_close_bf16(out, expected, max_ulp=None, max_abs=2e-2)
+
+
 def test_rescale_path_with_growing_scores(kernels):
     """Scores that grow along the sequence force the accumulator rescale again and again."""
     q, cache = wl.mla_inputs(1, 128, 1024, 576, 4242)

@@ -30,7 +30,7 @@
 //   warp 1    score MMA issuer: QK(j) = 18 TMEM-A MMAs (N=64), issued as soon as the softmax
 //             group has copied the scores of chunk j-1 out of TMEM and the chunk's cache stage
 //             has landed, so the scores run ahead of the values by up to the depth of the ring
-//   warp 15   value MMA issuer: PV(j) = 4 TMEM-A MMAs (N=256), issued when the chunk's
+//   warp 14   value MMA issuer: PV(j) = 4 TMEM-A MMAs (N=256), issued when the chunk's
 //             probabilities are in TMEM
 //   warps 2-13 three softmax groups of four warps; group g takes the chunks with j % 3 == g and
 //             one thread handles a head's whole 64-position row of a chunk: partial-score load,
@@ -39,7 +39,6 @@
 //             The running reference maximum of a head passes from group to group through
 //             shared memory (one mbarrier per TMEM lane quadrant orders the hand-over); the
 //             accumulator is rescaled only when the maximum grows by more than 2^8.
-//   warp 14   courier: acknowledges consumed exchange tiles to the peer CTA
 //
 // With kv_splits == 1 the CTA writes BF16 output directly.  Otherwise it writes a normalised
 // FP32 partial and its log-sum-exp (one per feature half) to scratch and a small kernel merges
@@ -56,8 +55,8 @@ namespace {
 constexpr int kGroups = 3;                       // softmax groups; group g owns chunks j % kGroups == g
 constexpr int kSoftmaxWarps = 4 * kGroups;       // four warps (one per TMEM lane quadrant) per group
 constexpr int kSoftmaxThreads = kSoftmaxWarps * 32;
-// producer, score MMA issuer, softmax groups, courier, value MMA issuer
-constexpr int kMlaThreads = 64 + kSoftmaxThreads + 64;
+// producer, score MMA issuer, softmax groups, value MMA issuer
+constexpr int kMlaThreads = 64 + kSoftmaxThreads + 32;
 constexpr int kKv = 64;                        // cache positions per chunk
 constexpr int kDqk = 576, kDv = 512;
 constexpr int kKvStages = 4;
@@ -76,8 +75,13 @@ struct MlaParams {
   const __nv_bfloat16* q;
   __nv_bfloat16* out;
   float* partial_o;   // [batch][splits][heads][512]
-  float* partial_lse; // [batch][splits][heads][2 feature halves]
-  int batch, heads, seq, splits;
+  float* partial_lse; // [batch][pieces][heads][2 feature halves]
+  int batch, heads, seq;
+  int chunks_per_seq;
+  int pieces;         // partial slots per sequence: the KV splits, or the most pieces a sequence is cut into
+  int balanced;       // 0: grid (2, splits, batch), one segment per cluster; 1: grid (2, clusters), see unit_begin
+  int clusters;
+  long long units;    // batch * chunks_per_seq
   float scale_log2;   // |scale| * log2(e)
   int negate;         // scale < 0: the query's sign is flipped on its way into TMEM
 };
@@ -86,8 +90,6 @@ struct MlaParams {
 // TRINITY_MLA_TIMING reads g_mla_ticks; the library build compiles the hooks away.
 #ifdef TRINITY_MLA_TIMING
 __device__ unsigned long long g_mla_ticks[24];
-__device__ int g_mla_experiment;   // bit 0: no rope MMAs, bit 1: no exchange, bit 2: cache loaded only once per stage
-#define TRINITY_MLA_EXPERIMENT(bit) (g_mla_experiment & (bit))
 #define TRINITY_MLA_TICK_DECL long long tick_last = clock64(); unsigned long long tick_sum[12] = {};
 #define TRINITY_MLA_TICK(i) { const long long now = clock64(); tick_sum[i] += now - tick_last; tick_last = now; }
 #define TRINITY_MLA_TICK_FLUSH if (blockIdx.z == 0 && blockIdx.y == 0 && blockIdx.x == 0 && threadIdx.x == 64) { for (int i = 0; i < 12; ++i) g_mla_ticks[i] = tick_sum[i]; }
@@ -95,7 +97,6 @@ __device__ int g_mla_experiment;   // bit 0: no rope MMAs, bit 1: no exchange, b
 #define TRINITY_MLA_ISSUER_TICK(i) { const long long now = clock64(); issuer_sum[i] += now - issuer_last; issuer_last = now; }
 #define TRINITY_MLA_ISSUER_FLUSH if (blockIdx.z == 0 && blockIdx.y == 0 && blockIdx.x == 0) { for (int i = 0; i < 5; ++i) g_mla_ticks[16 + i] = issuer_sum[i]; }
 #else
-#define TRINITY_MLA_EXPERIMENT(bit) 0
 #define TRINITY_MLA_ISSUER_DECL
 #define TRINITY_MLA_ISSUER_TICK(i)
 #define TRINITY_MLA_ISSUER_FLUSH
@@ -118,6 +119,22 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, u
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
       "}\n"
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same with the shared-memory descriptor given as two words: within a stage only the low word
+// (the address field) changes from MMA to MMA, so the issuing thread adds 32-bit constants.
+__device__ __forceinline__ void umma_bf16_ts_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t desc_lo,
+                                                   uint32_t desc_hi, uint32_t idesc,
+                                                   uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 desc;\n"
+      "mov.b64 desc, {%2, %3};\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], desc, %4, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -162,9 +179,11 @@ __device__ __forceinline__ void st_peer_v4(uint32_t remote_addr, float a, float 
                ::"r"(remote_addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
-// Arrive on a barrier in the peer CTA; releases this thread's earlier peer stores.
-__device__ __forceinline__ void mbar_arrive_peer(uint32_t remote_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+// Arrive on a barrier in the peer CTA without ordering earlier memory operations.  The callers
+// acknowledge shared-memory reads whose values they have already used, so there is nothing to
+// release; the releasing form stalls the issuing thread for about a thousand cycles.
+__device__ __forceinline__ void mbar_arrive_peer_relaxed(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
 }
 __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -205,6 +224,50 @@ __host__ __device__ inline void split_range(int chunks, int splits, int s, int& 
   count = base + (s < extra ? 1 : 0);
 }
 
+// Balanced schedule: the (batch x chunks-per-sequence) chunks of the whole call, numbered row by
+// row, are cut into `clusters` contiguous runs of equal length (to within one chunk).  Cluster k
+// owns units [unit_begin(k), unit_begin(k + 1)).
+__host__ __device__ inline long long unit_begin(long long units, int clusters, int k) {
+  return units * k / clusters;
+}
+// The cluster whose run contains unit u: the largest k with unit_begin(k) <= u.
+__host__ __device__ inline int cluster_of_unit(long long units, int clusters, long long u) {
+  return int(((u + 1) * clusters + units - 1) / units) - 1;
+}
+
+// One piece of work of a cluster: `num_chunks` chunks of sequence `b` starting at `first_chunk`.
+// `whole` pieces cover their sequence alone and write BF16 output; the others write a partial
+// into `slot`.
+struct Segment {
+  int b, first_chunk, num_chunks;
+  long long slot;
+  bool whole;
+};
+// The i-th segment of this cluster; false when the cluster has no such segment.
+__device__ __forceinline__ bool get_segment(const MlaParams& p, int i, Segment& s) {
+  if (p.balanced == 0) {
+    if (i != 0) return false;
+    s.b = blockIdx.z;
+    split_range(p.chunks_per_seq, p.pieces, blockIdx.y, s.first_chunk, s.num_chunks);
+    s.slot = static_cast<long long>(s.b) * p.pieces + blockIdx.y;
+    s.whole = p.pieces == 1;
+    return s.num_chunks > 0;
+  }
+  const int k = blockIdx.y;
+  const long long u0 = unit_begin(p.units, p.clusters, k), u1 = unit_begin(p.units, p.clusters, k + 1);
+  const long long cps = p.chunks_per_seq;
+  const long long b = u0 / cps + i;
+  const long long lo = b * cps > u0 ? b * cps : u0;
+  const long long hi = (b + 1) * cps < u1 ? (b + 1) * cps : u1;
+  if (lo >= hi) return false;
+  s.b = int(b);
+  s.first_chunk = int(lo - b * cps);
+  s.num_chunks = int(hi - lo);
+  s.slot = b * p.pieces + (k - cluster_of_unit(p.units, p.clusters, b * cps));
+  s.whole = s.num_chunks == p.chunks_per_seq;
+  return true;
+}
+
 __global__ void __launch_bounds__(kMlaThreads, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
                   const __grid_constant__ CUtensorMap map_rope, const MlaParams p) {
@@ -221,12 +284,16 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   const uint32_t bar_base = xchg_smem + 4 * kXchgBytes;
   uint8_t* xchg = smem + kKvStages * kStageBytes;
   uint8_t* send = xchg + 2 * kXchgBytes;
-  // barriers: kv_full[stages], kv_empty[stages], x_full[2], x_empty[2], s_full[2], pv_done[2],
-  //           s_free, p_full, q_tmem, m_ready[3][4].  s_free and p_full complete once per chunk and
-  //           are waited on by one thread, chunk after chunk (chunk j is phase j & 1).  s_full
-  //           and pv_done are waited on by the softmax groups, which see only every third chunk;
-  //           a parity wait is only meaningful on consecutive phases, so these two (and m_ready)
-  //           exist once per group (chunk j is phase (j / 3) & 1 of barrier j % 3).
+  // A cluster works through its segments one after the other; chunks are counted across
+  // segments (g below), and every barrier's phase follows from that count, so all roles agree on
+  // the phases without resetting anything between segments.
+  // barriers: kv_full[stages], kv_empty[stages], x_full[2], x_empty[2], s_full[3], pv_done[3],
+  //           s_free, p_full, q_tmem, o_free, m_ready[3][4].  s_free and p_full complete once per
+  //           chunk and are waited on by one thread, chunk after chunk (chunk g is phase g & 1).
+  //           s_full and pv_done are waited on by the softmax groups, which see only every third
+  //           chunk; a parity wait is only meaningful on consecutive phases, so these two (and
+  //           m_ready) exist once per group (chunk g is phase (g / 3) & 1 of barrier g % 3).
+  //           q_tmem and o_free complete once per segment.
   auto kv_full = [&](int s) { return bar_base + 8u * s; };
   auto kv_empty = [&](int s) { return bar_base + 8u * (kKvStages + s); };
   auto x_full = [&](int b) { return bar_base + 8u * (2 * kKvStages + b); };
@@ -236,23 +303,18 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   auto group_phase = [](int c) { return static_cast<uint32_t>((c / kGroups) & 1); };
   const uint32_t s_free = bar_base + 8u * (2 * kKvStages + 4 + 2 * kGroups);   // the scores have been copied out
   const uint32_t p_full = s_free + 8u;                                         // probabilities are in TMEM
-  const uint32_t q_tmem = s_free + 16u;
+  const uint32_t q_tmem = s_free + 16u;                                        // the segment's query is in TMEM
+  const uint32_t o_free = s_free + 24u;                                        // the segment's accumulator has been read
   // m_ready[group][quadrant]: the reference maxima after chunk c are in m_shared (one arrival a
   // chunk, by the warp of group c % 3 that serves the quadrant)
-  auto m_ready = [&](int c, int q) { return s_free + 24u + 8u * ((c % kGroups) * 4 + q); };
+  auto m_ready = [&](int c, int q) { return s_free + 32u + 8u * ((c % kGroups) * 4 + q); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(
-      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 4 + 2 * kGroups + 3 + 4 * kGroups));
+      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 4 + 2 * kGroups + 4 + 4 * kGroups));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t half = cluster_rank();   // latent half and rope half owned by this CTA
   const uint32_t peer = half ^ 1u;
-  const int split = blockIdx.y;
-  const int b = blockIdx.z;
-
-  const int total_chunks = (p.seq + kKv - 1) / kKv;
-  int first_chunk, num_chunks;
-  split_range(total_chunks, p.splits, split, first_chunk, num_chunks);
 
   if (threadIdx.x == 0) {
     read_count_storage[0] = 0;
@@ -263,7 +325,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(x_full(i), 1);     // local arm (expect_tx) + the peer's bulk copy bytes
-      mbar_init(x_empty(i), 1);    // one arrival from the peer once all its threads have read
+      mbar_init(x_empty(i), 4);    // the peer's four warps that have read the tile
     }
     for (int i = 0; i < kGroups; ++i) {
       mbar_init(s_full(i), 1);
@@ -272,6 +334,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     mbar_init(s_free, 4);        // the four warps of the group that owns the chunk
     mbar_init(p_full, 4);
     mbar_init(q_tmem, kSoftmaxWarps);
+    mbar_init(o_free, kSoftmaxWarps);
     for (int q = 0; q < 4 * kGroups; ++q) mbar_init(m_ready(q >> 2, q & 3), 1);
     mbar_fence_init();
     tma_prefetch_desc(&map_cache);
@@ -286,38 +349,40 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  Segment seg;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0 && num_chunks > 0) {
+    if (lane == 0) {
       // A stage is held from its load until the chunk's values are accumulated, several
       // thousand cycles, so the ring alone keeps too few bytes in flight to cover the memory
       // latency.  Chunks further ahead are therefore requested into L2 first; the ring's own
       // loads then find them there.
-      auto prefetch_chunk = [&](int c) {
-        if (c >= num_chunks) return;
-        const int kv0 = (first_chunk + c) * kKv;
+      int g = 0;
+      bool ok = true;
+      for (int si = 0; ok && get_segment(p, si, seg); ++si) {
+        auto prefetch_chunk = [&](int c) {
+          if (c >= seg.num_chunks) return;
+          const int kv0 = (seg.first_chunk + c) * kKv;
 #pragma unroll
-        for (int f = 0; f < 4; ++f) tma_prefetch_l2_3d(&map_cache, int(half) * 256 + f * 64, kv0, b);
-        tma_prefetch_l2_3d(&map_rope, kDv + int(half) * 32, kv0, b);
-      };
-      for (int c = kKvStages; c < kKvStages + kPrefetchAhead; ++c) prefetch_chunk(c);
-      for (int j = 0; j < num_chunks; ++j) {
-        const int s = j % kKvStages;
-        const uint32_t phase = (j / kKvStages) & 1u;
-        prefetch_chunk(j + kKvStages + kPrefetchAhead);
-        if (!mbar_wait(kv_empty(s), phase ^ 1u, 0x401)) break;
-        if (TRINITY_MLA_EXPERIMENT(4) && j >= kKvStages) {
-          mbar_arrive(kv_full(s));
-          continue;
+          for (int f = 0; f < 4; ++f)
+            tma_prefetch_l2_3d(&map_cache, int(half) * 256 + f * 64, kv0, seg.b);
+          tma_prefetch_l2_3d(&map_rope, kDv + int(half) * 32, kv0, seg.b);
+        };
+        for (int c = 0; c < kKvStages + kPrefetchAhead; ++c) prefetch_chunk(c);
+        for (int j = 0; j < seg.num_chunks; ++j, ++g) {
+          const int s = g % kKvStages;
+          const uint32_t phase = (g / kKvStages) & 1u;
+          prefetch_chunk(j + kKvStages + kPrefetchAhead);
+          if (!mbar_wait(kv_empty(s), phase ^ 1u, 0x401)) { ok = false; break; }
+          mbar_arrive_expect_tx(kv_full(s), kStageBytes);
+          const int kv0 = (seg.first_chunk + j) * kKv;
+          const uint32_t dst = kv_smem + s * kStageBytes;
+#pragma unroll
+          for (int f = 0; f < 4; ++f)
+            tma_load_3d(dst + f * kBoxBytes, &map_cache, kv_full(s), int(half) * 256 + f * 64, kv0, seg.b);
+          tma_load_3d(dst + 4 * kBoxBytes, &map_rope, kv_full(s), kDv + int(half) * 32, kv0, seg.b);
         }
-        mbar_arrive_expect_tx(kv_full(s), kStageBytes);
-        const int kv0 = (first_chunk + j) * kKv;
-        const uint32_t dst = kv_smem + s * kStageBytes;
-#pragma unroll
-        for (int f = 0; f < 4; ++f)
-          tma_load_3d(dst + f * kBoxBytes, &map_cache, kv_full(s), int(half) * 256 + f * 64, kv0, b);
-        tma_load_3d(dst + 4 * kBoxBytes, &map_rope, kv_full(s), kDv + int(half) * 32, kv0, b);
       }
     }
   } else if (warp == 1) {
@@ -330,75 +395,65 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     // tensor-pipe time, so one descriptor per operand kind is built per chunk and the K-steps
     // only add constants to its address field (units of 16 bytes; the field cannot overflow,
     // shared memory ends below 256 KB).
-    if (lane == 0 && num_chunks > 0) {
+    if (lane == 0) {
       constexpr uint32_t kIdescQK = umma_idesc_bf16(128, kKv, 0, 0);
       const uint32_t d_scores = tmem_base + kColS, a_query = tmem_base + kColQ;
       TRINITY_MLA_ISSUER_DECL
-      bool ok = mbar_wait(q_tmem, 0, 0x502);
-      for (int c = 0; c < num_chunks && ok; ++c) {
-        TRINITY_MLA_ISSUER_TICK(3)
-        if (c > 0 && !mbar_wait(s_free, (c - 1) & 1u, 0x505)) break;
-        TRINITY_MLA_ISSUER_TICK(0)
-        if (!mbar_wait(kv_full(c % kKvStages), (c / kKvStages) & 1u, 0x503)) break;
-        TRINITY_MLA_ISSUER_TICK(1)
-        tc_fence_after();
-        // 16 K-steps over the latent boxes and 2 over the rope box, the query always from TMEM
-        const uint32_t stage = kv_smem + (c % kKvStages) * kStageBytes;
-        const uint64_t latent = umma_smem_desc(stage, 16, 1024);
-        const uint64_t rope = umma_smem_desc_sw64(stage + 4 * kBoxBytes, 512);
+      int g = 0;
+      bool ok = true;
+      for (int si = 0; ok && get_segment(p, si, seg); ++si) {
+        ok = mbar_wait(q_tmem, si & 1u, 0x502);
+        for (int j = 0; ok && j < seg.num_chunks; ++j, ++g) {
+          TRINITY_MLA_ISSUER_TICK(3)
+          if (g > 0 && !mbar_wait(s_free, (g - 1) & 1u, 0x505)) { ok = false; break; }
+          TRINITY_MLA_ISSUER_TICK(0)
+          if (!mbar_wait(kv_full(g % kKvStages), (g / kKvStages) & 1u, 0x503)) { ok = false; break; }
+          TRINITY_MLA_ISSUER_TICK(1)
+          tc_fence_after();
+          // 16 K-steps over the latent boxes and 2 over the rope box, the query always from TMEM
+          const uint32_t stage = kv_smem + (g % kKvStages) * kStageBytes;
+          const uint64_t latent = umma_smem_desc(stage, 16, 1024);
+          const uint64_t rope = umma_smem_desc_sw64(stage + 4 * kBoxBytes, 512);
+          const uint32_t latent_lo = uint32_t(latent), latent_hi = uint32_t(latent >> 32);
+          const uint32_t rope_lo = uint32_t(rope), rope_hi = uint32_t(rope >> 32);
 #pragma unroll
-        for (int ks = 0; ks < 16; ++ks)
-          umma_bf16_ts(d_scores, a_query + ks * 8, latent + (((ks / 4) * kBoxBytes + (ks % 4) * 32) >> 4),
-                       kIdescQK, ks != 0);
-        if (!TRINITY_MLA_EXPERIMENT(1))
+          for (int ks = 0; ks < 16; ++ks)
+            umma_bf16_ts_split(d_scores, a_query + ks * 8,
+                               latent_lo + (((ks / 4) * kBoxBytes + (ks % 4) * 32) >> 4), latent_hi,
+                               kIdescQK, ks != 0);
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
-          umma_bf16_ts(d_scores, a_query + 128 + r * 8, rope + ((r * 32) >> 4), kIdescQK, 1u);
-        umma_commit(s_full(c));
+          for (int r = 0; r < 2; ++r)
+            umma_bf16_ts_split(d_scores, a_query + 128 + r * 8, rope_lo + ((r * 32) >> 4), rope_hi,
+                               kIdescQK, 1u);
+          umma_commit(s_full(g));
+        }
       }
       TRINITY_MLA_ISSUER_TICK(3)
       TRINITY_MLA_ISSUER_FLUSH
     }
-  } else if (warp == 3 + kSoftmaxWarps) {
+  } else if (warp == 2 + kSoftmaxWarps) {
     // ------------------------------------------------------------ value MMA issuer
     // Probabilities from TMEM, the chunk's latent boxes N-major (64-latent boxes 8192 B apart,
     // 8-position groups 1024 B apart).
-    if (lane == 0 && num_chunks > 0) {
+    if (lane == 0) {
       constexpr uint32_t kIdescPV = umma_idesc_bf16(128, 256, 0, 1);
       const uint32_t d_out = tmem_base + kColO, a_prob = tmem_base + kColP;
-      for (int c = 0; c < num_chunks; ++c) {
-        if (!mbar_wait(p_full, c & 1u, 0x504)) break;
-        tc_fence_after();
-        const int s = c % kKvStages;
-        const uint64_t values = umma_smem_desc(kv_smem + s * kStageBytes, kBoxBytes, 1024);
+      int g = 0;
+      bool ok = true;
+      for (int si = 0; ok && get_segment(p, si, seg); ++si) {
+        // the previous segment's accumulator must have been read before it is overwritten
+        if (si > 0) ok = mbar_wait(o_free, (si - 1) & 1u, 0x506);
+        for (int j = 0; ok && j < seg.num_chunks; ++j, ++g) {
+          if (!mbar_wait(p_full, g & 1u, 0x504)) { ok = false; break; }
+          tc_fence_after();
+          const int s = g % kKvStages;
+          const uint64_t values = umma_smem_desc(kv_smem + s * kStageBytes, kBoxBytes, 1024);
 #pragma unroll
-        for (int ks = 0; ks < kKv / 16; ++ks)
-          umma_bf16_ts(d_out, a_prob + ks * 8, values + ((ks * 2048) >> 4), kIdescPV, (c | ks) != 0);
-        umma_commit(kv_empty(s));
-        umma_commit(pv_done(c));
-      }
-    }
-  } else if (warp == 2 + kSoftmaxWarps) {
-    // ------------------------------------------------------------ courier
-    // Tells the peer that its tile in my receive buffer has been read by the group's four warps.
-    // A separate warp does it because a release at cluster scope costs close to a thousand
-    // cycles, which the softmax warps cannot afford on their critical path.
-    if (lane == 0 && !TRINITY_MLA_EXPERIMENT(2)) {
-      for (int j = 0; j < num_chunks; ++j) {
-        const unsigned target = 4u * unsigned((j >> 1) + 1);
-        const long long start = clock64();
-        bool seen = true;
-        while (read_count[j & 1] < target) {
-          __nanosleep(32);
-          if (clock64() - start > kWaitBudgetCycles) {
-            report_timeout(0x701);
-            seen = false;
-            break;
-          }
+          for (int ks = 0; ks < kKv / 16; ++ks)
+            umma_bf16_ts(d_out, a_prob + ks * 8, values + ((ks * 2048) >> 4), kIdescPV, (j | ks) != 0);
+          umma_commit(kv_empty(s));
+          umma_commit(pv_done(g));
         }
-        if (!seen) break;
-        __threadfence_block();
-        mbar_arrive_peer(map_to_peer(x_empty(j & 1), peer));
       }
     }
   } else {
@@ -410,284 +465,303 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     const int row = quad * 32 + lane;              // head index
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const bool live = row < p.heads;
-    if (num_chunks > 0) {
-      // This CTA's query features -> TMEM as packed BF16 pairs: four blocks of 64 latent
-      // features and one of 32 rope features, dealt out to the groups.
-      const uint32_t flip = p.negate ? 0x80008000u : 0u;
-      const __nv_bfloat16* qhead = p.q + (static_cast<long long>(b) * p.heads + (live ? row : 0)) * kDqk;
-#pragma unroll 1
-      for (int blk = group; blk < 5; blk += kGroups) {
-        const uint4* src = reinterpret_cast<const uint4*>(blk < 4 ? qhead + half * 256 + blk * 64
-                                                                  : qhead + kDv + half * 32);
-        uint32_t w[32];
-#pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          uint4 x = (live && (blk < 4 || v < 4)) ? __ldg(src + v) : make_uint4(0, 0, 0, 0);
-          w[v * 4 + 0] = x.x ^ flip; w[v * 4 + 1] = x.y ^ flip;
-          w[v * 4 + 2] = x.z ^ flip; w[v * 4 + 3] = x.w ^ flip;
-        }
-        if (blk < 4) {
-          tmem_st_32x32b_x32(lane_base + kColQ + blk * 32, w);
-        } else {
-          uint32_t r[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) r[i] = w[i];
-          tmem_st_32x32b_x16(lane_base + kColQ + 128, r);
-        }
-      }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(q_tmem);
-    }
-
-    float m_l = -INFINITY;     // reference maximum that `l` is relative to
-    float l = 0.0f;            // sum of this thread's probabilities
     // A wait that gives up only sets `bad`: the thread keeps executing the warp- and
     // group-collective instructions (on meaningless data) and the threads of a group leave
     // together at the next vote, so no barrier or collective is ever left half-attended.
     bool bad = false;
+    int gbase = 0;   // chunks of earlier segments
     TRINITY_MLA_TICK_DECL
 
-    for (int j = group; j < num_chunks; j += kGroups) {
-      // exchange tiles alternate between two buffers by chunk parity
-      const int buf = j & 1;
-      const uint32_t phase = (j >> 1) & 1u;
-      uint4* staged = reinterpret_cast<uint4*>(send + buf * kXchgBytes);
-      const uint4* received = reinterpret_cast<const uint4*>(xchg + buf * kXchgBytes);
-      // ---- partial scores of this CTA's feature half: TMEM -> registers
-      TRINITY_MLA_TICK(0)
-      if (!bad) bad = !mbar_wait(s_full(j), group_phase(j), 0x601);
-      TRINITY_MLA_TICK(1)
-      tc_fence_after();
-      float t[64];
+    for (int si = 0; get_segment(p, si, seg); ++si) {
+      const int num_chunks = seg.num_chunks;
       {
-        uint32_t lo[32], hi[32];
-        tmem_ld_32x32b_x32(lane_base + kColS, lo);
-        tmem_ld_32x32b_x32(lane_base + kColS + 32, hi);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          t[i] = __uint_as_float(lo[i]);
-          t[32 + i] = __uint_as_float(hi[i]);
-        }
-      }
-      // the scores are in registers: later score MMAs may overwrite the buffer
-      tc_fence_before();
-      if (__all_sync(0xffffffffu, !bad) && lane == 0) mbar_arrive(s_free);
-      TRINITY_MLA_TICK(2)
-      // ---- FP16 copy for the peer: [8 groups of 8 positions][128 rows] (conflict-free), then one
-      //      thread starts the bulk asynchronous copy into the peer's receive tile
-      // The buffers were last used for chunk j-2, by another group.  Once that group has read its
-      // receive tile, the exchange barriers of this buffer are in the phase this chunk expects.
-      if (!TRINITY_MLA_EXPERIMENT(2))
-      if (j >= 2 && !bad) {
-        const unsigned target = 4u * unsigned(j >> 1);
-        const long long start = clock64();
-        while (read_count[buf] < target) {
-          if (clock64() - start > kWaitBudgetCycles) {
-            report_timeout(0x607);
-            bad = true;
-            break;
-          }
-        }
-      }
-      if (!TRINITY_MLA_EXPERIMENT(2))
-      if (!bad) bad = !mbar_wait_cluster(x_empty(buf), phase ^ 1u, 0x604);
-      TRINITY_MLA_TICK(3)
-      if (!bad && !TRINITY_MLA_EXPERIMENT(2)) {
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          uint32_t h[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const __half2 v = __floats2half2_rn(t[g * 8 + 2 * e], t[g * 8 + 2 * e + 1]);
-            h[e] = *reinterpret_cast<const uint32_t*>(&v);
-          }
-          staged[g * 128 + row] = make_uint4(h[0], h[1], h[2], h[3]);
-        }
-      }
-      fence_async_smem();
-      uint32_t all_good;
-      asm volatile(
-          "{\n"
-          ".reg .pred p, q;\n"
-          "setp.eq.u32 p, %1, 0;\n"
-          "bar.red.and.pred q, %2, 128, p;\n"   // barrier over the group's threads + vote
-          "selp.u32 %0, 1, 0, q;\n"
-          "}\n"
-          : "=r"(all_good)
-          : "r"(bad ? 1u : 0u), "r"(1 + group)
-          : "memory");
-      if (!all_good) {
-        bad = true;
-        break;
-      }
-      if ((warp & 3) == 2 && lane == 0 && !TRINITY_MLA_EXPERIMENT(2)) {
-        mbar_arrive_expect_tx(x_full(buf), kXchgBytes);
-        asm volatile(
-            "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-            ::"r"(map_to_peer(xchg_smem + buf * kXchgBytes, peer)), "r"(send_smem + buf * kXchgBytes),
-              "r"(kXchgBytes), "r"(map_to_peer(x_full(buf), peer))
-            : "memory");
-      }
-      TRINITY_MLA_TICK(4)
-      // ---- the peer's half of the scores
-      if (!TRINITY_MLA_EXPERIMENT(2))
-      if (!bad) bad = !mbar_wait_cluster(x_full(buf), phase, 0x605);
-      TRINITY_MLA_TICK(5)
-#pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        if (TRINITY_MLA_EXPERIMENT(2)) break;
-        const uint4 other = received[g * 128 + row];
-        const uint32_t theirs[4] = {other.x, other.y, other.z, other.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 c2 = __half22float2(*reinterpret_cast<const __half2*>(&theirs[e]));
-          t[g * 8 + 2 * e] += c2.x;
-          t[g * 8 + 2 * e + 1] += c2.y;
-        }
-      }
-      // this warp has read the receive tile; the courier acknowledges once all four have
-      __syncwarp();
-      if (lane == 0 && !TRINITY_MLA_EXPERIMENT(2)) atomicAdd(const_cast<unsigned*>(read_count) + buf, 1u);
-      const int valid = p.seq - (first_chunk + j) * kKv;   // positions of this chunk inside seq
-      if (valid < kKv) {
-#pragma unroll
-        for (int i = 0; i < kKv; ++i)
-          if (i >= valid) t[i] = -INFINITY;
-      }
-      float mx4[4] = {t[0], t[1], t[2], t[3]};
-#pragma unroll
-      for (int i = 4; i < kKv; i += 4) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], t[i + e]);
-      }
-      // position 0 of a chunk is always inside seq, so the maximum is finite
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-      TRINITY_MLA_TICK(6)
-      // ---- reference maximum: take it over from the group that had chunk j-1, pass it on
-      float m_prev = -INFINITY;
-      if (j > 0) {
-        if (!bad) bad = !mbar_wait(m_ready(j - 1, quad), group_phase(j - 1), 0x606);
-        m_prev = m_shared[row];
-      }
-      const bool grow = mx > m_prev + kRescaleThreshold;   // always true for the first chunk
-      const float m_new = grow ? mx : m_prev;
-      m_shared[row] = m_new;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(m_ready(j, quad));
-      if (m_new != m_l) {
-        l *= fast_exp2(m_l - m_new);   // the first time: 0 * 2^-inf
-        m_l = m_new;
-      }
-      // ---- probabilities
-      uint32_t pw[32];
-      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float p0 = fast_exp2(fmaf(t[2 * i], p.scale_log2, -m_new));
-        const float p1 = fast_exp2(fmaf(t[2 * i + 1], p.scale_log2, -m_new));
-        sum4[i & 3] += p0 + p1;
-        pw[i] = pack_bf16x2(p0, p1);
-      }
-      if (valid < kKv) {
-        // positions outside seq: exact zeros whatever the scale (0 * -inf would be a NaN)
-        float tail = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const bool in0 = 2 * i < valid, in1 = 2 * i + 1 < valid;
-          const float p0 = in0 ? fast_exp2(fmaf(t[2 * i], p.scale_log2, -m_new)) : 0.0f;
-          const float p1 = in1 ? fast_exp2(fmaf(t[2 * i + 1], p.scale_log2, -m_new)) : 0.0f;
-          tail += p0 + p1;
-          pw[i] = pack_bf16x2(p0, p1);
-        }
-        sum4[0] = tail; sum4[1] = 0.0f; sum4[2] = 0.0f; sum4[3] = 0.0f;
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      TRINITY_MLA_TICK(7)
-      // Neither the probability buffer nor the accumulator may be touched before the value MMAs
-      // of chunk j-1 have finished with them.
-      if (j > 0 && !bad) bad = !mbar_wait(pv_done(j - 1), group_phase(j - 1), 0x602);
-      tc_fence_after();
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        const float f = grow ? fast_exp2(m_prev - m_new) : 1.0f;
+        // This CTA's query features -> TMEM as packed BF16 pairs: four blocks of 64 latent
+        // features and one of 32 rope features, dealt out to the groups.  (All MMAs of the
+        // previous segment have completed: its epilogue waited for the last of them.)
+        const uint32_t flip = p.negate ? 0x80008000u : 0u;
+        const __nv_bfloat16* qhead =
+            p.q + (static_cast<long long>(seg.b) * p.heads + (live ? row : 0)) * kDqk;
 #pragma unroll 1
-        for (int c = 0; c < 256; c += 32) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
-          tmem_ld_wait();
+        for (int blk = group; blk < 5; blk += kGroups) {
+          const uint4* src = reinterpret_cast<const uint4*>(blk < 4 ? qhead + half * 256 + blk * 64
+                                                                    : qhead + kDv + half * 32);
+          uint32_t w[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-          tmem_st_32x32b_x32(lane_base + kColO + c, o);
+          for (int v = 0; v < 8; ++v) {
+            uint4 x = (live && (blk < 4 || v < 4)) ? __ldg(src + v) : make_uint4(0, 0, 0, 0);
+            w[v * 4 + 0] = x.x ^ flip; w[v * 4 + 1] = x.y ^ flip;
+            w[v * 4 + 2] = x.z ^ flip; w[v * 4 + 3] = x.w ^ flip;
+          }
+          if (blk < 4) {
+            tmem_st_32x32b_x32(lane_base + kColQ + blk * 32, w);
+          } else {
+            uint32_t r[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = w[i];
+            tmem_st_32x32b_x16(lane_base + kColQ + 128, r);
+          }
         }
         tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(q_tmem);
       }
-      tmem_st_32x32b_x32(lane_base + kColP, pw);
-      tmem_st_wait();
-      tc_fence_before();
-      const bool warp_good = __all_sync(0xffffffffu, !bad);
-      if (lane == 0 && warp_good) mbar_arrive(p_full);
-      TRINITY_MLA_TICK(8)
-    }
-    TRINITY_MLA_TICK_FLUSH
 
-    // Every softmax thread comes here, also after a failure.  The final reference maximum of a
-    // head was written by the group that had the last chunk.
-    asm volatile("bar.sync 4, %0;" ::"n"(kSoftmaxThreads) : "memory");
-    bool ready = num_chunks > 0 && !bad;
-    const float m_final = num_chunks > 0 ? m_shared[row] : 0.0f;
-    if (m_l != m_final) l *= fast_exp2(m_l - m_final);   // a group without chunks holds l = 0
-    l_part[group * 128 + row] = l;
-    if (ready) ready = mbar_wait(pv_done(num_chunks - 1), group_phase(num_chunks - 1), 0x603);
-    asm volatile("bar.sync 4, %0;" ::"n"(kSoftmaxThreads) : "memory");
-    l = 0.0f;
-#pragma unroll
-    for (int g = 0; g < kGroups; ++g) l += l_part[g * 128 + row];
-    if (__all_sync(0xffffffffu, ready)) {
-      tc_fence_after();
-      const float inv_l = 1.0f / l;
-      // the eight 32-column blocks of the accumulator are dealt out to the groups
-      if (p.splits == 1) {
-        __nv_bfloat16* orow =
-            p.out + (static_cast<long long>(b) * p.heads + row) * kDv + half * 256;
-#pragma unroll 1
-        for (int c = group * 32; c < 256; c += kGroups * 32) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+      float m_l = -INFINITY;     // reference maximum that `l` is relative to
+      float l = 0.0f;            // sum of this thread's probabilities
+      // this group's chunks of the segment: those whose running number is group (mod 3)
+      for (int j = (group + kGroups - gbase % kGroups) % kGroups; j < num_chunks; j += kGroups) {
+        const int g = gbase + j;
+        // exchange tiles alternate between two buffers by chunk parity
+        const int buf = g & 1;
+        const uint32_t phase = (g >> 1) & 1u;
+        uint4* staged = reinterpret_cast<uint4*>(send + buf * kXchgBytes);
+        const uint4* received = reinterpret_cast<const uint4*>(xchg + buf * kXchgBytes);
+        // ---- partial scores of this CTA's feature half: TMEM -> registers
+        TRINITY_MLA_TICK(0)
+        if (!bad) bad = !mbar_wait(s_full(g), group_phase(g), 0x601);
+        TRINITY_MLA_TICK(1)
+        tc_fence_after();
+        float t[64];
+        {
+          uint32_t lo[32], hi[32];
+          tmem_ld_32x32b_x32(lane_base + kColS, lo);
+          tmem_ld_32x32b_x32(lane_base + kColS + 32, hi);
           tmem_ld_wait();
-          if (live) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 w;
-              w.x = pack_bf16x2(__uint_as_float(o[v * 8 + 0]) * inv_l, __uint_as_float(o[v * 8 + 1]) * inv_l);
-              w.y = pack_bf16x2(__uint_as_float(o[v * 8 + 2]) * inv_l, __uint_as_float(o[v * 8 + 3]) * inv_l);
-              w.z = pack_bf16x2(__uint_as_float(o[v * 8 + 4]) * inv_l, __uint_as_float(o[v * 8 + 5]) * inv_l);
-              w.w = pack_bf16x2(__uint_as_float(o[v * 8 + 6]) * inv_l, __uint_as_float(o[v * 8 + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + c + v * 8) = w;
+          for (int i = 0; i < 32; ++i) {
+            t[i] = __uint_as_float(lo[i]);
+            t[32 + i] = __uint_as_float(hi[i]);
+          }
+        }
+        // the scores are in registers: later score MMAs may overwrite the buffer
+        tc_fence_before();
+        if (__all_sync(0xffffffffu, !bad) && lane == 0) mbar_arrive(s_free);
+        TRINITY_MLA_TICK(2)
+        // ---- FP16 copy for the peer: [8 groups of 8 positions][128 rows] (conflict-free), then
+        //      one thread starts the bulk asynchronous copy into the peer's receive tile.
+        // The buffers were last used for chunk g-2, by another group.  Once that group has read
+        // its receive tile, the exchange barriers of this buffer are in the phase this chunk
+        // expects.
+        if (g >= 2 && !bad) {
+          const unsigned target = 4u * unsigned(g >> 1);
+          const long long start = clock64();
+          while (read_count[buf] < target) {
+            if (clock64() - start > kWaitBudgetCycles) {
+              report_timeout(0x607);
+              bad = true;
+              break;
             }
           }
         }
-      } else {
-        const long long slot = (static_cast<long long>(b) * p.splits + split) * p.heads + row;
-        float* prow = p.partial_o + slot * kDv + half * 256;
-#pragma unroll 1
-        for (int c = group * 32; c < 256; c += kGroups * 32) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(lane_base + kColO + c, o);
-          tmem_ld_wait();
-          if (live) {
+        if (!bad) bad = !mbar_wait_cluster(x_empty(buf), phase ^ 1u, 0x604);
+        TRINITY_MLA_TICK(3)
+        if (!bad) {
 #pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              float4 w = make_float4(__uint_as_float(o[v * 4 + 0]) * inv_l, __uint_as_float(o[v * 4 + 1]) * inv_l,
-                                     __uint_as_float(o[v * 4 + 2]) * inv_l, __uint_as_float(o[v * 4 + 3]) * inv_l);
-              *reinterpret_cast<float4*>(prow + c + v * 4) = w;
+          for (int q8 = 0; q8 < 8; ++q8) {
+            uint32_t h[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __half2 v = __floats2half2_rn(t[q8 * 8 + 2 * e], t[q8 * 8 + 2 * e + 1]);
+              h[e] = *reinterpret_cast<const uint32_t*>(&v);
             }
+            staged[q8 * 128 + row] = make_uint4(h[0], h[1], h[2], h[3]);
           }
         }
-        // each feature half was normalised with its own sums, so each records its own log-sum-exp
-        if (live && group == 0) p.partial_lse[slot * 2 + half] = m_final + log2f(l);
+        fence_async_smem();
+        uint32_t all_good;
+        asm volatile(
+            "{\n"
+            ".reg .pred p, q;\n"
+            "setp.eq.u32 p, %1, 0;\n"
+            "bar.red.and.pred q, %2, 128, p;\n"   // barrier over the group's threads + vote
+            "selp.u32 %0, 1, 0, q;\n"
+            "}\n"
+            : "=r"(all_good)
+            : "r"(bad ? 1u : 0u), "r"(1 + group)
+            : "memory");
+        if (!all_good) {
+          bad = true;
+          break;
+        }
+        if ((warp & 3) == 2 && lane == 0) {
+          mbar_arrive_expect_tx(x_full(buf), kXchgBytes);
+          asm volatile(
+              "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+              ::"r"(map_to_peer(xchg_smem + buf * kXchgBytes, peer)), "r"(send_smem + buf * kXchgBytes),
+                "r"(kXchgBytes), "r"(map_to_peer(x_full(buf), peer))
+              : "memory");
+        }
+        TRINITY_MLA_TICK(4)
+        // ---- the peer's half of the scores
+        if (!bad) bad = !mbar_wait_cluster(x_full(buf), phase, 0x605);
+        TRINITY_MLA_TICK(5)
+#pragma unroll
+        for (int q8 = 0; q8 < 8; ++q8) {
+          const uint4 other = received[q8 * 128 + row];
+          const uint32_t theirs[4] = {other.x, other.y, other.z, other.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 c2 = __half22float2(*reinterpret_cast<const __half2*>(&theirs[e]));
+            t[q8 * 8 + 2 * e] += c2.x;
+            t[q8 * 8 + 2 * e + 1] += c2.y;
+          }
+        }
+        // This warp has read (and used) its part of the receive tile: tell the peer, whose next
+        // copy into this buffer waits for the four warps, and count it for the local group that
+        // uses the buffer next.
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_peer_relaxed(map_to_peer(x_empty(buf), peer));
+          atomicAdd(const_cast<unsigned*>(read_count) + buf, 1u);
+        }
+        const int valid = p.seq - (seg.first_chunk + j) * kKv;   // positions of this chunk inside seq
+        if (valid < kKv) {
+#pragma unroll
+          for (int i = 0; i < kKv; ++i)
+            if (i >= valid) t[i] = -INFINITY;
+        }
+        float mx4[4] = {t[0], t[1], t[2], t[3]};
+#pragma unroll
+        for (int i = 4; i < kKv; i += 4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], t[i + e]);
+        }
+        // position 0 of a chunk is always inside seq, so the maximum is finite
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+        TRINITY_MLA_TICK(6)
+        // ---- reference maximum: take it over from the group that had chunk j-1, pass it on
+        float m_prev = -INFINITY;
+        if (j > 0) {
+          if (!bad) bad = !mbar_wait(m_ready(g - 1, quad), group_phase(g - 1), 0x606);
+          m_prev = m_shared[row];
+        }
+        const bool grow = mx > m_prev + kRescaleThreshold;   // always true for a segment's first chunk
+        const float m_new = grow ? mx : m_prev;
+        m_shared[row] = m_new;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(m_ready(g, quad));
+        if (m_new != m_l) {
+          l *= fast_exp2(m_l - m_new);   // the first time: 0 * 2^-inf
+          m_l = m_new;
+        }
+        // ---- probabilities
+        uint32_t pw[32];
+        float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = fast_exp2(fmaf(t[2 * i], p.scale_log2, -m_new));
+          const float p1 = fast_exp2(fmaf(t[2 * i + 1], p.scale_log2, -m_new));
+          sum4[i & 3] += p0 + p1;
+          pw[i] = pack_bf16x2(p0, p1);
+        }
+        if (valid < kKv) {
+          // positions outside seq: exact zeros whatever the scale (0 * -inf would be a NaN)
+          float tail = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const bool in0 = 2 * i < valid, in1 = 2 * i + 1 < valid;
+            const float p0 = in0 ? fast_exp2(fmaf(t[2 * i], p.scale_log2, -m_new)) : 0.0f;
+            const float p1 = in1 ? fast_exp2(fmaf(t[2 * i + 1], p.scale_log2, -m_new)) : 0.0f;
+            tail += p0 + p1;
+            pw[i] = pack_bf16x2(p0, p1);
+          }
+          sum4[0] = tail; sum4[1] = 0.0f; sum4[2] = 0.0f; sum4[3] = 0.0f;
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        TRINITY_MLA_TICK(7)
+        // Neither the probability buffer nor the accumulator may be touched before the value MMAs
+        // of chunk j-1 have finished with them.  (For a segment's first chunk the previous
+        // segment's epilogue has waited for them.)
+        if (j > 0 && !bad) bad = !mbar_wait(pv_done(g - 1), group_phase(g - 1), 0x602);
+        tc_fence_after();
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          const float f = grow ? fast_exp2(m_prev - m_new) : 1.0f;
+#pragma unroll 1
+          for (int c = 0; c < 256; c += 32) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st_32x32b_x32(lane_base + kColO + c, o);
+          }
+          tmem_st_wait();
+        }
+        tmem_st_32x32b_x32(lane_base + kColP, pw);
+        tmem_st_wait();
+        tc_fence_before();
+        const bool warp_good = __all_sync(0xffffffffu, !bad);
+        if (lane == 0 && warp_good) mbar_arrive(p_full);
+        TRINITY_MLA_TICK(8)
       }
+      if (si == 0) { TRINITY_MLA_TICK_FLUSH }
+
+      // Every softmax thread comes here, also after a failure.  The final reference maximum of
+      // a head was written by the group that had the segment's last chunk.
+      const int g_last = gbase + num_chunks - 1;
+      asm volatile("bar.sync 4, %0;" ::"n"(kSoftmaxThreads) : "memory");
+      bool ready = !bad;
+      const float m_final = m_shared[row];
+      if (m_l != m_final) l *= fast_exp2(m_l - m_final);   // a group without chunks holds l = 0
+      l_part[group * 128 + row] = l;
+      if (ready) ready = mbar_wait(pv_done(g_last), group_phase(g_last), 0x603);
+      asm volatile("bar.sync 4, %0;" ::"n"(kSoftmaxThreads) : "memory");
+      l = 0.0f;
+#pragma unroll
+      for (int gi = 0; gi < kGroups; ++gi) l += l_part[gi * 128 + row];
+      const bool all_ready = __all_sync(0xffffffffu, ready);
+      if (all_ready) {
+        tc_fence_after();
+        const float inv_l = 1.0f / l;
+        // the eight 32-column blocks of the accumulator are dealt out to the groups
+        if (seg.whole) {
+          __nv_bfloat16* orow =
+              p.out + (static_cast<long long>(seg.b) * p.heads + row) * kDv + half * 256;
+#pragma unroll 1
+          for (int c = group * 32; c < 256; c += kGroups * 32) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+            tmem_ld_wait();
+            if (live) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 w;
+                w.x = pack_bf16x2(__uint_as_float(o[v * 8 + 0]) * inv_l, __uint_as_float(o[v * 8 + 1]) * inv_l);
+                w.y = pack_bf16x2(__uint_as_float(o[v * 8 + 2]) * inv_l, __uint_as_float(o[v * 8 + 3]) * inv_l);
+                w.z = pack_bf16x2(__uint_as_float(o[v * 8 + 4]) * inv_l, __uint_as_float(o[v * 8 + 5]) * inv_l);
+                w.w = pack_bf16x2(__uint_as_float(o[v * 8 + 6]) * inv_l, __uint_as_float(o[v * 8 + 7]) * inv_l);
+                *reinterpret_cast<uint4*>(orow + c + v * 8) = w;
+              }
+            }
+          }
+        } else {
+          const long long slot = seg.slot * p.heads + row;
+          float* prow = p.partial_o + slot * kDv + half * 256;
+#pragma unroll 1
+          for (int c = group * 32; c < 256; c += kGroups * 32) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(lane_base + kColO + c, o);
+            tmem_ld_wait();
+            if (live) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 w = make_float4(__uint_as_float(o[v * 4 + 0]) * inv_l, __uint_as_float(o[v * 4 + 1]) * inv_l,
+                                       __uint_as_float(o[v * 4 + 2]) * inv_l, __uint_as_float(o[v * 4 + 3]) * inv_l);
+                *reinterpret_cast<float4*>(prow + c + v * 4) = w;
+              }
+            }
+          }
+          // each feature half was normalised with its own sums, so each records its own log-sum-exp
+          if (live && group == 0) p.partial_lse[slot * 2 + half] = m_final + log2f(l);
+        }
+      }
+      // the accumulator has been read: the next segment's values may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0 && all_ready) mbar_arrive(o_free);
+      gbase += num_chunks;
+      if (!all_ready) break;   // after a failure the remaining segments are not attempted
     }
   }
 
@@ -704,39 +778,141 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
 }
 
 // out[b,h,c] = sum_s w_s * partial[b,s,h,c],  w_s = 2^(lse_s - max) / sum_s 2^(lse_s - max), with
-// the log-sum-exp of the feature half that column c belongs to.  Splits that held no positions
-// have lse = -inf and weight zero.
-__global__ void mla_combine_kernel(const float* __restrict__ partial_o,
-                                   const float* __restrict__ partial_lse,
-                                   __nv_bfloat16* __restrict__ out, int heads, int splits) {
-  const int bh = blockIdx.x;  // b * heads + h
+// the log-sum-exp of the feature half that column c belongs to.  Under the balanced schedule a
+// sequence has as many pieces as clusters touch it; a sequence with one piece was written
+// directly and is skipped.
+__global__ void __launch_bounds__(128)
+mla_combine_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_lse,
+                   __nv_bfloat16* __restrict__ out, int rows, int heads, int pieces, int balanced,
+                   int chunks_per_seq, int clusters, long long units) {
+  // one warp per (sequence, head): lane l owns columns [4 l, 4 l + 4) of each 128-column quarter
+  const int bh = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (bh >= rows) return;
   const int b = bh / heads, h = bh % heads;
+  int n = pieces;
+  if (balanced) {
+    const long long u = static_cast<long long>(b) * chunks_per_seq;
+    n = cluster_of_unit(units, clusters, u + chunks_per_seq - 1) - cluster_of_unit(units, clusters, u) + 1;
+    if (n == 1) return;
+  }
+  const long long slot0 = static_cast<long long>(b) * pieces * heads + h;   // piece s: slot0 + s * heads
   float mx[2] = {-INFINITY, -INFINITY}, inv[2];
-  for (int s = 0; s < splits; ++s)
-    for (int f = 0; f < 2; ++f)
-      mx[f] = fmaxf(mx[f], partial_lse[((static_cast<long long>(b) * splits + s) * heads + h) * 2 + f]);
-  for (int f = 0; f < 2; ++f) {
-    float denom = 0.0f;
-    for (int s = 0; s < splits; ++s)
-      denom += exp2f(partial_lse[((static_cast<long long>(b) * splits + s) * heads + h) * 2 + f] - mx[f]);
-    inv[f] = 1.0f / denom;
+  for (int s = lane; s < n; s += 32) {
+    const float2 v = *reinterpret_cast<const float2*>(partial_lse + (slot0 + static_cast<long long>(s) * heads) * 2);
+    mx[0] = fmaxf(mx[0], v.x);
+    mx[1] = fmaxf(mx[1], v.y);
   }
-  for (int c = threadIdx.x; c < kDv; c += blockDim.x) {
-    const int f = c >> 8;
-    float acc = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-      const long long slot = (static_cast<long long>(b) * splits + s) * heads + h;
-      const float w = exp2f(partial_lse[slot * 2 + f] - mx[f]) * inv[f];
-      if (w != 0.0f) acc += w * partial_o[slot * kDv + c];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+    mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+  }
+  float denom[2] = {0.0f, 0.0f};
+  for (int s = lane; s < n; s += 32) {
+    const float2 v = *reinterpret_cast<const float2*>(partial_lse + (slot0 + static_cast<long long>(s) * heads) * 2);
+    denom[0] += exp2f(v.x - mx[0]);
+    denom[1] += exp2f(v.y - mx[1]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    denom[0] += __shfl_xor_sync(0xffffffffu, denom[0], o);
+    denom[1] += __shfl_xor_sync(0xffffffffu, denom[1], o);
+  }
+  inv[0] = 1.0f / denom[0];
+  inv[1] = 1.0f / denom[1];
+  float4 acc[4] = {};
+  for (int s = 0; s < n; ++s) {
+    const long long slot = slot0 + static_cast<long long>(s) * heads;
+    const float2 lse = *reinterpret_cast<const float2*>(partial_lse + slot * 2);
+    const float w[2] = {exp2f(lse.x - mx[0]) * inv[0], exp2f(lse.y - mx[1]) * inv[1]};
+    const float4* src = reinterpret_cast<const float4*>(partial_o + slot * kDv) + lane;
+#pragma unroll
+    for (int qt = 0; qt < 4; ++qt) {
+      const float4 v = src[qt * 32];
+      const float wq = w[qt >> 1];   // quarters 0,1 belong to feature half 0
+      acc[qt].x += wq * v.x; acc[qt].y += wq * v.y; acc[qt].z += wq * v.z; acc[qt].w += wq * v.w;
     }
-    out[static_cast<long long>(bh) * kDv + c] = __float2bfloat16(acc);
   }
+  uint2* dst = reinterpret_cast<uint2*>(out + static_cast<long long>(bh) * kDv) + lane;
+#pragma unroll
+  for (int qt = 0; qt < 4; ++qt)
+    dst[qt * 32] = make_uint2(pack_bf16x2(acc[qt].x, acc[qt].y), pack_bf16x2(acc[qt].z, acc[qt].w));
 }
 
-size_t scratch_bytes(int batch, int heads, int d_v, int splits) {
-  if (splits <= 1) return 0;
-  const size_t slots = size_t(batch) * splits * heads;
+size_t scratch_bytes(int batch, int heads, int d_v, int pieces) {
+  if (pieces <= 1) return 0;
+  const size_t slots = size_t(batch) * pieces * heads;
   return ((slots * d_v * 4 + 255) / 256) * 256 + ((slots * 2 * 4 + 255) / 256) * 256;
+}
+
+// The automatic schedule picks, by a small cost model, between equal splits of every sequence
+// (one segment per cluster) and the balanced schedule (equal runs of chunks, a cluster may work
+// through pieces of several sequences).  The model's constants are measured figures of this
+// kernel on a B200, in microseconds: a chunk takes a cluster about 1.25, a launch has about 22
+// of fixed cost (start-up, pipeline fill and drain, epilogue), every further segment of a
+// cluster costs about 13 (drain, epilogue, new query, refill), and cutting sequences costs a
+// merge pass plus the FP32 partials' traffic.
+constexpr int kMinChunksPerCluster = 8;
+struct Schedule {
+  int balanced, clusters, pieces, chunks_per_seq;
+  long long units;
+};
+Schedule automatic_schedule(int batch, int seq, bool force_balanced) {
+  int sms = 148;
+  int device = 0;
+  if (cudaGetDevice(&device) == cudaSuccess)
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const int pairs = sms / 2 > 0 ? sms / 2 : 1;
+  constexpr double kChunkUs = 1.25, kFixedUs = 22.0, kSegmentUs = 13.0, kMergeUs = 5.0;
+  constexpr double kPartialUsPerSlot = 2.0 * 128 * 512 * 4 / 3.0e6;   // written and read back at ~3 TB/s
+  Schedule best;
+  best.chunks_per_seq = (seq + kKv - 1) / kKv;
+  best.units = static_cast<long long>(batch) * best.chunks_per_seq;
+  best.balanced = 0;
+  best.clusters = 0;
+  best.pieces = 1;
+  const int cps = best.chunks_per_seq;
+  double best_cost = 0.0;
+  // equal splits
+  const int max_splits = cps / kMinChunksPerCluster > 1 ? cps / kMinChunksPerCluster : 1;
+  for (int s = 1; s <= max_splits && s <= 2 * pairs; ++s) {
+    const long long waves = (static_cast<long long>(batch) * s + pairs - 1) / pairs;
+    double cost = waves * ((cps + s - 1) / s * kChunkUs + kFixedUs);
+    if (s > 1) cost += kMergeUs + kPartialUsPerSlot * batch * s;
+    if (s == 1 || cost < best_cost) {
+      best_cost = cost;
+      best.pieces = s;
+    }
+  }
+  // balanced runs
+  long long clusters = best.units / kMinChunksPerCluster;
+  if (clusters > pairs) clusters = pairs;
+  if (clusters >= 1) {
+    Schedule s = best;
+    s.balanced = 1;
+    s.clusters = int(clusters);
+    s.pieces = 1;
+    long long slots = 0;
+    for (int b = 0; b < batch; ++b) {
+      const long long u = static_cast<long long>(b) * cps;
+      const int n = cluster_of_unit(s.units, s.clusters, u + cps - 1) - cluster_of_unit(s.units, s.clusters, u) + 1;
+      if (n > s.pieces) s.pieces = n;
+      if (n > 1) slots += n;
+    }
+    int max_segments = 1;
+    long long longest = 0;
+    for (int k = 0; k < s.clusters; ++k) {
+      const long long u0 = unit_begin(s.units, s.clusters, k), u1 = unit_begin(s.units, s.clusters, k + 1);
+      const int segments = int((u1 - 1) / cps - u0 / cps) + 1;
+      if (segments > max_segments) max_segments = segments;
+      if (u1 - u0 > longest) longest = u1 - u0;
+    }
+    double cost = longest * kChunkUs + kFixedUs + (max_segments - 1) * kSegmentUs;
+    if (slots > 0) cost += kMergeUs + kPartialUsPerSlot * slots;
+    if (cost < best_cost || force_balanced) return s;
+  }
+  return best;
 }
 
 }  // namespace
@@ -751,17 +927,13 @@ extern "C" size_t trinity_sm100_mla_scratch_bytes(int32_t batch, int32_t heads, 
 }
 
 extern "C" int trinity_sm100_mla_default_splits(int32_t batch, int32_t seq) {
-  // Two CTAs (feature halves) per (batch, split); aim for about one CTA per SM without
-  // splitting a sequence more finely than 512 positions per split.
-  int sms = 148;
-  int device = 0;
-  if (cudaGetDevice(&device) == cudaSuccess)
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (batch <= 0 || seq <= 0) return 1;
-  int splits = sms / (2 * batch);
-  const int max_splits = (seq + 511) / 512;
-  if (splits > max_splits) splits = max_splits;
-  return splits < 1 ? 1 : splits;
+  return automatic_schedule(batch, seq, false).pieces;
+}
+
+extern "C" int trinity_sm100_mla_balanced_slots(int32_t batch, int32_t seq) {
+  if (batch <= 0 || seq <= 0) return 1;
+  return automatic_schedule(batch, seq, true).pieces;
 }
 
 extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void* stream_handle) {
@@ -778,14 +950,26 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   if (a.batch > 65535) return fail(TRINITY_SM100_E_UNSUPPORTED, "mla: batch above 65535");
   if (!aligned16(a.q) || !aligned16(a.cache) || !aligned16(a.out))
     return fail(TRINITY_SM100_E_INVALID, "mla: pointers must be 16-byte aligned");
-  int splits = a.kv_splits > 0 ? a.kv_splits : trinity_sm100_mla_default_splits(a.batch, a.seq);
+  // kv_splits > 0: that many equal splits of every sequence, one cluster each.
+  // kv_splits == 0: the automatic schedule; < 0: the balanced schedule whatever the cost model says.
   const int chunks = (a.seq + kKv - 1) / kKv;
-  if (splits > chunks) splits = chunks;
-  if (splits > 65535) return fail(TRINITY_SM100_E_UNSUPPORTED, "mla: too many splits");
+  Schedule schedule;
+  if (a.kv_splits <= 0) {
+    schedule = automatic_schedule(a.batch, a.seq, a.kv_splits < 0);
+  } else {
+    schedule.balanced = 0;
+    schedule.chunks_per_seq = chunks;
+    schedule.units = static_cast<long long>(a.batch) * chunks;
+    schedule.pieces = a.kv_splits > chunks ? chunks : a.kv_splits;
+    schedule.clusters = 0;
+    if (schedule.pieces > 65535) return fail(TRINITY_SM100_E_UNSUPPORTED, "mla: too many splits");
+  }
+  const bool balanced = schedule.balanced != 0;
+  const int splits = schedule.pieces;
   const size_t need = scratch_bytes(a.batch, a.heads, a.d_v, splits);
   if (need > 0) {
     if (!a.scratch || a.scratch_bytes < need)
-      return fail(TRINITY_SM100_E_INVALID, "mla: %d splits need %zu scratch bytes (got %zu)",
+      return fail(TRINITY_SM100_E_INVALID, "mla: %d partial slots per sequence need %zu scratch bytes (got %zu)",
                   splits, need, a.scratch_bytes);
     if (reinterpret_cast<uintptr_t>(a.scratch) & 255u)
       return fail(TRINITY_SM100_E_INVALID, "mla: scratch must be 256-byte aligned");
@@ -826,11 +1010,15 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   p.batch = a.batch;
   p.heads = a.heads;
   p.seq = a.seq;
-  p.splits = splits;
+  p.chunks_per_seq = schedule.chunks_per_seq;
+  p.pieces = schedule.pieces;
+  p.balanced = balanced ? 1 : 0;
+  p.clusters = schedule.clusters;
+  p.units = schedule.units;
   p.scale_log2 = fabsf(a.scale) * 1.4426950408889634f;
   p.negate = a.scale < 0.0f ? 1 : 0;
   cudaLaunchConfig_t config = {};
-  config.gridDim = dim3(2, splits, a.batch);
+  config.gridDim = balanced ? dim3(2, schedule.clusters, 1) : dim3(2, splits, a.batch);
   config.blockDim = dim3(kMlaThreads);
   config.dynamicSmemBytes = kMlaSmem;
   config.stream = stream;
@@ -847,8 +1035,10 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   count_launch();
   if ((rc = check_launch("mla_decode"))) return rc;
   if (splits > 1) {
-    mla_combine_kernel<<<a.batch * a.heads, 128, 0, stream>>>(p.partial_o, p.partial_lse, p.out,
-                                                              a.heads, splits);
+    const int rows = a.batch * a.heads;
+    mla_combine_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(p.partial_o, p.partial_lse, p.out, rows,
+                                                           a.heads, splits, p.balanced,
+                                                           p.chunks_per_seq, p.clusters, p.units);
     count_launch();
     if ((rc = check_launch("mla_combine"))) return rc;
   }
@@ -904,11 +1094,20 @@ extern "C" int trinity_sm100_mla_decode_bf16_noalloc(const trinity_sm100_mla* ar
   trinity_sm100_mla call = *args;
   if (call.batch <= 0 || call.heads <= 0 || call.seq <= 0)
     return fail(TRINITY_SM100_E_INVALID, "mla (no-alloc): empty extent");
-  int splits =
-      call.kv_splits > 0 ? call.kv_splits : trinity_sm100_mla_default_splits(call.batch, call.seq);
+  int splits = call.kv_splits > 0   ? call.kv_splits
+               : call.kv_splits == 0 ? trinity_sm100_mla_default_splits(call.batch, call.seq)
+                                     : trinity_sm100_mla_balanced_slots(call.batch, call.seq);
   const int chunks = (call.seq + kKv - 1) / kKv;
   if (splits > chunks) splits = chunks;
-  const size_t need = scratch_bytes(call.batch, call.heads, call.d_v, splits);
+  size_t need = scratch_bytes(call.batch, call.heads, call.d_v, splits);
+  if (call.kv_splits <= 0 && need > size_t(TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES)) {
+    // The automatic schedule's partials do not fit: take the most equal splits that do.
+    while (splits > 1 && scratch_bytes(call.batch, call.heads, call.d_v, splits) >
+                             size_t(TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES))
+      --splits;
+    call.kv_splits = splits;
+    need = scratch_bytes(call.batch, call.heads, call.d_v, splits);
+  }
   if (need > size_t(TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES))
     return fail(TRINITY_SM100_E_UNSUPPORTED,
                 "mla (no-alloc): batch %d x %d splits x %d heads needs %zu scratch bytes, above the "
@@ -917,7 +1116,6 @@ extern "C" int trinity_sm100_mla_decode_bf16_noalloc(const trinity_sm100_mla* ar
                 call.batch, splits, call.heads, need, size_t(TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES));
   void* scratch = nullptr;
   if (int rc = static_scratch_address(&scratch)) return rc;
-  call.kv_splits = splits;
   call.scratch = scratch;
   call.scratch_bytes = TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES;
   return trinity_sm100_mla_decode_bf16(&call, stream_handle);

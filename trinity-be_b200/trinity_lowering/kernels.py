@@ -22,6 +22,7 @@ EXPORTS = (
     "trinity_sm100_softmax_bf16",
     "trinity_sm100_mla_scratch_bytes",
     "trinity_sm100_mla_default_splits",
+    "trinity_sm100_mla_balanced_slots",
     "trinity_sm100_mla_decode_bf16",
     "trinity_sm100_mla_decode_bf16_noalloc",
     "trinity_sm100_allreduce_flag_words",
@@ -106,6 +107,7 @@ def library():
             lib.trinity_sm100_mla_scratch_bytes.argtypes = [ctypes.c_int32] * 4
             lib.trinity_sm100_mla_scratch_bytes.restype = ctypes.c_size_t
             lib.trinity_sm100_mla_default_splits.argtypes = [ctypes.c_int32] * 2
+            lib.trinity_sm100_mla_balanced_slots.argtypes = [ctypes.c_int32] * 2
             lib.trinity_sm100_mla_decode_bf16.argtypes = [ctypes.POINTER(MlaArgs), ctypes.c_void_p]
             lib.trinity_sm100_mla_decode_bf16_noalloc.argtypes = [
                 ctypes.POINTER(MlaArgs), ctypes.c_void_p]
@@ -226,6 +228,10 @@ def mla_default_splits(batch, seq):
     return int(library().trinity_sm100_mla_default_splits(batch, seq))
 
 
+def mla_balanced_slots(batch, seq):
+    return int(library().trinity_sm100_mla_balanced_slots(batch, seq))
+
+
 def mla_scratch_bytes(batch, heads, d_v, kv_splits):
     return int(library().trinity_sm100_mla_scratch_bytes(batch, heads, d_v, kv_splits))
 
@@ -240,11 +246,13 @@ def mla_decode(q, cache, scale, d_v=512, kv_splits=0, out=None, scratch=None, st
     if cache.shape[0] != batch or cache.shape[2] != d_qk:
         raise ValueError("mla_decode: q and cache disagree on batch or width")
     seq = cache.shape[1]
-    if kv_splits == 0:
-        kv_splits = mla_default_splits(batch, seq)
     if out is None:
         out = torch.empty((batch, heads, d_v), dtype=torch.bfloat16, device=q.device)
-    need = mla_scratch_bytes(batch, heads, d_v, kv_splits)
+    # kv_splits == 0 leaves the schedule to the library, kv_splits < 0 asks for the balanced one;
+    # either way the library says how many partial slots per sequence it needs scratch for.
+    slots = kv_splits if kv_splits > 0 else (
+        mla_default_splits(batch, seq) if kv_splits == 0 else mla_balanced_slots(batch, seq))
+    need = mla_scratch_bytes(batch, heads, d_v, slots)
     if scratch is None:
         scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
     args = MlaArgs()
