@@ -89,7 +89,14 @@ struct MlaParams {
 // Optional per-phase cycle counters of the softmax loop: a tuning harness that defines
 // TRINITY_MLA_TIMING reads g_mla_ticks; the library build compiles the hooks away.
 #ifdef TRINITY_MLA_TIMING
-__device__ unsigned long long g_mla_ticks[24];
+__device__ unsigned long long g_mla_ticks[40];
+__device__ __forceinline__ unsigned long long mla_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// wall-clock stamps (ns) of one CTA's milestones
+#define TRINITY_MLA_STAMP(i) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_mla_ticks[24 + (i)] = mla_now_ns();
 #define TRINITY_MLA_TICK_DECL long long tick_last = clock64(); unsigned long long tick_sum[12] = {};
 #define TRINITY_MLA_TICK(i) { const long long now = clock64(); tick_sum[i] += now - tick_last; tick_last = now; }
 #define TRINITY_MLA_TICK_FLUSH if (blockIdx.z == 0 && blockIdx.y == 0 && blockIdx.x == 0 && threadIdx.x == 64) { for (int i = 0; i < 12; ++i) g_mla_ticks[i] = tick_sum[i]; }
@@ -97,6 +104,7 @@ __device__ unsigned long long g_mla_ticks[24];
 #define TRINITY_MLA_ISSUER_TICK(i) { const long long now = clock64(); issuer_sum[i] += now - issuer_last; issuer_last = now; }
 #define TRINITY_MLA_ISSUER_FLUSH if (blockIdx.z == 0 && blockIdx.y == 0 && blockIdx.x == 0) { for (int i = 0; i < 5; ++i) g_mla_ticks[16 + i] = issuer_sum[i]; }
 #else
+#define TRINITY_MLA_STAMP(i)
 #define TRINITY_MLA_ISSUER_DECL
 #define TRINITY_MLA_ISSUER_TICK(i)
 #define TRINITY_MLA_ISSUER_FLUSH
@@ -313,6 +321,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) { TRINITY_MLA_STAMP(0) }
   const uint32_t half = cluster_rank();   // latent half and rope half owned by this CTA
   const uint32_t peer = half ^ 1u;
 
@@ -350,6 +359,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   Segment seg;
+  if (threadIdx.x == 0) { TRINITY_MLA_STAMP(1) }
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -358,9 +368,25 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       // thousand cycles, so the ring alone keeps too few bytes in flight to cover the memory
       // latency.  Chunks further ahead are therefore requested into L2 first; the ring's own
       // loads then find them there.
+      // The softmax threads read the query one head per lane, 16 bytes at a time from rows 1152
+      // bytes apart, which DRAM serves slowly (microseconds for a few megabytes over all CTAs).
+      // So each CTA first asks for its half of the heads' rows as one contiguous range into L2
+      // (both CTAs read every row), and for the next segment's rows a whole segment ahead.
+      auto prefetch_query = [&](const Segment& sg) {
+        const int first = int(half) * 64;
+        const int count = p.heads - first < 64 ? p.heads - first : 64;
+        if (count > 0)
+          bulk_prefetch_l2(p.q + (static_cast<long long>(sg.b) * p.heads + first) * kDqk,
+                           uint32_t(count) * kDqk * 2);
+      };
       int g = 0;
       bool ok = true;
+      if (get_segment(p, 0, seg)) prefetch_query(seg);
       for (int si = 0; ok && get_segment(p, si, seg); ++si) {
+        {
+          Segment next;
+          if (get_segment(p, si + 1, next)) prefetch_query(next);
+        }
         auto prefetch_chunk = [&](int c) {
           if (c >= seg.num_chunks) return;
           const int kv0 = (seg.first_chunk + c) * kKv;
@@ -369,11 +395,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
             tma_prefetch_l2_3d(&map_cache, int(half) * 256 + f * 64, kv0, seg.b);
           tma_prefetch_l2_3d(&map_rope, kDv + int(half) * 32, kv0, seg.b);
         };
-        for (int c = 0; c < kKvStages + kPrefetchAhead; ++c) prefetch_chunk(c);
         for (int j = 0; j < seg.num_chunks; ++j, ++g) {
           const int s = g % kKvStages;
           const uint32_t phase = (g / kKvStages) & 1u;
-          prefetch_chunk(j + kKvStages + kPrefetchAhead);
+          // Requests into L2 run a fixed distance ahead of the ring's loads, and never ahead of
+          // the loads that fill the empty ring at the start: those must not queue behind them.
+          if (j >= kKvStages) prefetch_chunk(j + kPrefetchAhead);
+          // At the start of the kernel every CTA asks for its query and its whole ring at once, and
+          // the query, which the first scores wait for, would queue behind the ring's loads for
+          // several microseconds.  So the first chunk goes out alone; the rest follows once the
+          // query has arrived.
+          if (g == 1 && !mbar_wait(q_tmem, 0, 0x402)) { ok = false; break; }
           if (!mbar_wait(kv_empty(s), phase ^ 1u, 0x401)) { ok = false; break; }
           mbar_arrive_expect_tx(kv_full(s), kStageBytes);
           const int kv0 = (seg.first_chunk + j) * kKv;
@@ -382,6 +414,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           for (int f = 0; f < 4; ++f)
             tma_load_3d(dst + f * kBoxBytes, &map_cache, kv_full(s), int(half) * 256 + f * 64, kv0, seg.b);
           tma_load_3d(dst + 4 * kBoxBytes, &map_rope, kv_full(s), kDv + int(half) * 32, kv0, seg.b);
+          if (j == kKvStages - 1)
+            for (int c = kKvStages; c < kKvStages + kPrefetchAhead; ++c) prefetch_chunk(c);
         }
       }
     }
@@ -403,12 +437,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       bool ok = true;
       for (int si = 0; ok && get_segment(p, si, seg); ++si) {
         ok = mbar_wait(q_tmem, si & 1u, 0x502);
+        if (si == 0) { TRINITY_MLA_STAMP(8) }
         for (int j = 0; ok && j < seg.num_chunks; ++j, ++g) {
           TRINITY_MLA_ISSUER_TICK(3)
           if (g > 0 && !mbar_wait(s_free, (g - 1) & 1u, 0x505)) { ok = false; break; }
           TRINITY_MLA_ISSUER_TICK(0)
           if (!mbar_wait(kv_full(g % kKvStages), (g / kKvStages) & 1u, 0x503)) { ok = false; break; }
           TRINITY_MLA_ISSUER_TICK(1)
+          if (g == 0) { TRINITY_MLA_STAMP(2) }
           tc_fence_after();
           // 16 K-steps over the latent boxes and 2 over the rope box, the query always from TMEM
           const uint32_t stage = kv_smem + (g % kKvStages) * kStageBytes;
@@ -445,6 +481,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         if (si > 0) ok = mbar_wait(o_free, (si - 1) & 1u, 0x506);
         for (int j = 0; ok && j < seg.num_chunks; ++j, ++g) {
           if (!mbar_wait(p_full, g & 1u, 0x504)) { ok = false; break; }
+          if (g == 0) { TRINITY_MLA_STAMP(3) }
+          if (j == seg.num_chunks - 1) { TRINITY_MLA_STAMP(4) }
           tc_fence_after();
           const int s = g % kKvStages;
           const uint64_t values = umma_smem_desc(kv_smem + s * kStageBytes, kBoxBytes, 1024);
@@ -481,29 +519,43 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         const uint32_t flip = p.negate ? 0x80008000u : 0u;
         const __nv_bfloat16* qhead =
             p.q + (static_cast<long long>(seg.b) * p.heads + (live ? row : 0)) * kDqk;
-#pragma unroll 1
-        for (int blk = group; blk < 5; blk += kGroups) {
+        // Group g takes blocks g and g + 3; all loads are issued before the first is used.
+        uint4 x[2][8];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int blk = group + i * kGroups;
           const uint4* src = reinterpret_cast<const uint4*>(blk < 4 ? qhead + half * 256 + blk * 64
                                                                     : qhead + kDv + half * 32);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+#ifdef TRINITY_MLA_SKIP_QUERY_LOADS
+            x[i][v] = make_uint4(0x3c003c00u, 0x3c003c00u, uint32_t(reinterpret_cast<uintptr_t>(src)), 0);
+#else
+            x[i][v] = (live && blk < 5 && (blk < 4 || v < 4)) ? __ldg(src + v) : make_uint4(0, 0, 0, 0);
+#endif
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int blk = group + i * kGroups;
           uint32_t w[32];
 #pragma unroll
           for (int v = 0; v < 8; ++v) {
-            uint4 x = (live && (blk < 4 || v < 4)) ? __ldg(src + v) : make_uint4(0, 0, 0, 0);
-            w[v * 4 + 0] = x.x ^ flip; w[v * 4 + 1] = x.y ^ flip;
-            w[v * 4 + 2] = x.z ^ flip; w[v * 4 + 3] = x.w ^ flip;
+            w[v * 4 + 0] = x[i][v].x ^ flip; w[v * 4 + 1] = x[i][v].y ^ flip;
+            w[v * 4 + 2] = x[i][v].z ^ flip; w[v * 4 + 3] = x[i][v].w ^ flip;
           }
           if (blk < 4) {
             tmem_st_32x32b_x32(lane_base + kColQ + blk * 32, w);
-          } else {
+          } else if (blk == 4) {
             uint32_t r[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = w[i];
+            for (int k = 0; k < 16; ++k) r[k] = w[k];
             tmem_st_32x32b_x16(lane_base + kColQ + 128, r);
           }
         }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
+        if (threadIdx.x == 64 && si == 0) { TRINITY_MLA_STAMP(9) }
         if (lane == 0) mbar_arrive(q_tmem);
       }
 
@@ -706,6 +758,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       if (m_l != m_final) l *= fast_exp2(m_l - m_final);   // a group without chunks holds l = 0
       l_part[group * 128 + row] = l;
       if (ready) ready = mbar_wait(pv_done(g_last), group_phase(g_last), 0x603);
+      if (threadIdx.x == 64) { TRINITY_MLA_STAMP(5) }
       asm volatile("bar.sync 4, %0;" ::"n"(kSoftmaxThreads) : "memory");
       l = 0.0f;
 #pragma unroll
@@ -756,6 +809,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           if (live && group == 0) p.partial_lse[slot * 2 + half] = m_final + log2f(l);
         }
       }
+      if (threadIdx.x == 64) { TRINITY_MLA_STAMP(6) }
       // the accumulator has been read: the next segment's values may overwrite it
       tc_fence_before();
       __syncwarp();
@@ -770,6 +824,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();
+  if (threadIdx.x == 0) { TRINITY_MLA_STAMP(7) }
   if (warp == 2) {
     if (g_device_status != 0)
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);

@@ -103,6 +103,10 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Brings a contiguous range of global memory into L2 (address and size multiples of 16 bytes).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* address, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(address), "r"(bytes) : "memory");
+}
 // Brings one box of a 3-D tensor into L2 without a shared-memory destination.
 __device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int32_t x, int32_t y,
                                                    int32_t z) {
