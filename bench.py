@@ -6,11 +6,15 @@ A[8192,8192] @ W[8192,8192] + bias[8192], BF16 in / FP32 accumulate / BF16 out, 
 in a CUDA Graph; one step = one graph replay.  Inputs are synthetic and seeded.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload gemm_relu|gemm_bias_1024|rmsnorm|softmax|mla]
+                    [--workload gemm_relu|gemm_bias_1024|rmsnorm|softmax|mla|mla_batch_sharded|
+                                tp_mlp|tp_mlp_unfused|tp_mlp_noreduce]
 
-Prints one JSON line (rank 0).  With N > 1 (launched under torch.distributed.run) every rank
-runs an independent replica of the workload on its own GPU ("replicas only": the path has no
-exchange step), timing is the maximum over ranks and `value` is the aggregate.
+Prints one JSON line (rank 0).  With N > 1 (launched under torch.distributed.run) the GEMM,
+RMSNorm and softmax workloads run an independent replica on every GPU ("replicas only": the
+path has no exchange step); `mla` shards the heads and `mla_batch_sharded` the sequences over
+the ranks, again without an exchange; the `tp_mlp*` workloads shard a SwiGLU MLP N ways with
+the sum all-reduce over NVLink peer memory.  Timing is the maximum over ranks and `value` is
+the aggregate.
 """
 import argparse
 import json
@@ -32,11 +36,12 @@ L2_BYTES = 126 * 1024 * 1024
 # DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), per workload.
 # None until a capture exists for that workload.  Sources: profiles/*.md.
 NCU_TRAFFIC_BYTES = {
-    "gemm_relu": 1.153e9,
+    "gemm_relu": 1.127e9,
     "gemm_bias_1024": None,
-    "rmsnorm": 4.889e8,
-    "softmax": 4.866e8,
-    "mla": 3.154e8,
+    "rmsnorm": 4.84e8,
+    "softmax": 4.83e8,
+    "mla": 3.17e8,
+    "mla_batch_sharded": None,
     "tp_mlp": None,
     "tp_mlp_unfused": None,
     "tp_mlp_noreduce": None,
@@ -229,11 +234,28 @@ def make_workload(name, device, world=None):
             dt = time.perf_counter() - t0
             return sample.numel() * 4 / 1e9 / dt, "4096 of 32768 rows, CPU oracle (FP32 torch)", dt
 
-    elif name == "mla":
+    elif name in ("mla", "mla_batch_sharded"):
         batch, heads, seq, d_qk, d_v = 64, 128, 4096, 576, 512
+        # On N GPUs "mla" shards the heads N ways and every rank holds the whole cache (the cache
+        # is shared by all heads, so tensor-parallel ranks replicate it); "mla_batch_sharded"
+        # gives each rank batch/N sequences with all their heads.  Neither has a collective.
+        ranks = int(os.environ.get("WORLD_SIZE", "1")) if on_gpu else 1
+        mine = int(os.environ.get("RANK", "0")) if on_gpu else 0
         q, cache = wl.mla_inputs(batch, heads, seq, d_qk, 1237)
+        if ranks > 1 and name == "mla":
+            share = heads // ranks
+            q = q[:, mine * share:(mine + 1) * share].contiguous()
+            heads = share
+            w.parallelism = f"{ranks}-way head sharding, cache replicated, no collective"
+        elif ranks > 1:
+            share = batch // ranks
+            q = q[mine * share:(mine + 1) * share].contiguous()
+            cache = cache[mine * share:(mine + 1) * share].contiguous()
+            batch = share
+            w.parallelism = f"{ranks}-way batch sharding, no collective"
+            w.strong = True
         scale = 1.0 / math.sqrt(192.0)
-        w.label = "mla_decode batch64 x 128 heads, cache[64,4096,576] bf16"
+        w.label = f"mla_decode batch{batch} x {heads} heads per GPU, cache[{batch},4096,576] bf16"
         w.metric, w.unit, w.bound, w.dtype = "mla_decode_hbm_gbs", "GB/s", "hbm", "bf16"
         w.alg_bytes = (q.numel() + cache.numel() + batch * heads * d_v) * 2
         w.work = w.alg_bytes / 1e9
@@ -501,8 +523,9 @@ def main():
         "warmup": args.warmup, "ms_per_step": per_step_ms, "higher_is_better": True,
         "scaling": scaling, "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
         "config": {"workload": w.label, "l2": w.l2_note,
-                   "parallelism": ("single GPU" if world == 1 else
-                                   f"tp{world} over NVLink peer memory" if w.strong else "replicas only"),
+                   "parallelism": (getattr(w, "parallelism", None) or
+                                   ("single GPU" if world == 1 else
+                                    f"tp{world} over NVLink peer memory" if w.strong else "replicas only")),
                    "launch": "direct" if args.no_graph else "CUDA Graph replay"},
         "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": roof_unit,
                      "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name),

@@ -184,12 +184,16 @@ TRINITY_SM100_API int trinity_sm100_stream_synchronize(void* stream);
  *   q      [batch, heads, d_qk]      bf16   (d_qk = d_v + d_rope; absorbed latent then rope)
  *   cache  [batch, seq, d_qk]        bf16   (values are cache[..., :d_v])
  *   out    [batch, heads, d_v]       bf16
- *   scratch: trinity_sm100_mla_scratch_bytes(...) bytes of device memory, 256-byte aligned,
- *            holding the per-split partial numerators, running maxima and denominators.
+ *   scratch: trinity_sm100_mla_scratch_bytes(batch, heads, d_v, slots) bytes of device memory,
+ *            256-byte aligned, holding normalised FP32 partial outputs and their log-sum-exps
+ *            for `slots` pieces per sequence (see kv_splits); not needed when slots == 1.
  *
  *   out[b,h,:] = softmax_s(scale * q[b,h,:] . cache[b,s,:]) @ cache[b,:,:d_v]
  *
- * Supported geometry: heads == 128, d_v == 512, d_qk == 576, seq % 32 == 0, seq >= 32.
+ * Supported geometry: d_v == 512, d_qk == 576, 1 <= heads <= 128, any seq >= 1, batch <= 65535.
+ * The sequence is processed in chunks of 64 positions; a pair of thread blocks shares each
+ * piece of work.  A sequence may be cut into pieces that different pairs process (split KV);
+ * the pieces are merged by a second, small kernel.
  * The math follows the reference's batched-MLA fixture
  * (tests/fixtures/batched_mla/batched_mla_postprocessed_stage14.txt:21-23,62-68,210-213;
  *  split/combine structure of ...stage20.txt:62-76,197-206) with the softmax scale and

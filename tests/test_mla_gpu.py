@@ -36,6 +36,7 @@ def test_golden_case(kernels, golden):
 @pytest.mark.parametrize("batch,heads,seq,splits", [
     (1, 128, 32, 1), (2, 128, 64, 1), (1, 128, 4096, 1), (3, 128, 1000, 0), (2, 64, 257, 2),
     (1, 16, 2048, 4), (4, 128, 512, 3), (1, 128, 40, 2),
+    (1, 1, 1, 0), (2, 128, 63, 1), (1, 7, 65, 2), (3, 128, 129, 0), (150, 8, 64, 0),
 ])
 def test_against_oracle(kernels, batch, heads, seq, splits):
     q, cache = wl.mla_inputs(batch, heads, seq, 576, 1237 + seq)
