@@ -159,3 +159,27 @@ def mlp_oracle(x, w_gate, w_up, w_down, rows=None):
     env = {"H": hidden, "Wd": w_down}
     return ev.run(ev.op("matmul", ev.load("H"), ev.load("Wd")), env,
                   [xs.shape[0], w_down.shape[1]], "bf16")
+
+
+def ffn_block_inputs(m, d_model, d_ff, seed):
+    """attn, Wo, residual, gain, Wg, Wu, Wd for the decode-time feed-forward block."""
+    g = _gen(seed)
+    return {
+        "attn": _normal((m, d_model), 1.0, g),
+        "Wo": _normal((d_model, d_model), 1.0 / math.sqrt(d_model), g),
+        "R": _normal((m, d_model), 1.0, g),
+        "g": _normal((d_model,), 0.02, g, mean=1.0),
+        "Wg": _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
+        "Wu": _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
+        "Wd": _normal((d_ff, d_model), 1.0 / math.sqrt(d_ff), g),
+    }
+
+
+def ffn_block_oracle(t, eps):
+    """X1 = attn@Wo + R; Xn = rmsnorm(X1)*g; H = (Xn@Wu)*silu(Xn@Wg); Y = H@Wd + X1, every
+    intermediate stored in BF16 as the plan declares (the block of the reference's
+    tests/fixtures/ir/IR.v3.txt, whose own interpreter is not part of that repository)."""
+    x1 = gemm_oracle(t["attn"], t["Wo"], t["R"], None, "matrix")
+    xn = rmsnorm_oracle(x1, t["g"], eps)
+    hidden = gated_oracle(xn, t["Wu"], t["Wg"])
+    return gemm_oracle(hidden, t["Wd"], x1, None, "matrix")

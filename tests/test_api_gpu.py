@@ -194,6 +194,27 @@ def test_gated_gemm_plan():
     module.close()
 
 
+@torch.inference_mode()
+@pytest.mark.parametrize("m,d_model,d_ff", [(16, 512, 1024), (200, 1024, 2816)])
+def test_ffn_block_plan(m, d_model, d_ff):
+    """Output projection + residual, RMSNorm, SwiGLU, down projection + residual as one plan of
+    four launches with BF16 intermediates (decode-time M = 16: one partly filled row tile).
+    Each stage is within one ulp of its own oracle, but a one-ulp difference in an
+    intermediate is amplified by the next product, so the chain is held to the path's
+    rel-L2 / max-abs bar."""
+    tensors = wl.ffn_block_inputs(m, d_model, d_ff, 31)
+    module = build(plans.ffn_block(m, d_model, d_ff, 1e-6))
+    execution = module.prepare({name: t.to(DEV) for name, t in tensors.items()})
+    out = execution.run().clone()
+    execution.wait(30)
+    expected = wl.ffn_block_oracle(tensors, 1e-6)
+    # outputs reach |y| ~ 7, where a BF16 ulp is 2^-5: allow two ulps of the largest output
+    top = expected.float().abs().max().item()
+    assert_close_bf16(out.cpu(), expected, max_ulp=None, max_abs=2.0 ** (math.floor(math.log2(top)) - 6))
+    execution.close()
+    module.close()
+
+
 # ---------------------------------------------------------------- primitive plans (reference fixtures)
 def _pointwise_plan(name, shape, dtypes, scalar=None):
     import struct

@@ -201,6 +201,21 @@ def test_emit_is_deterministic_and_counts_launches():
     assert [b.shape for b in fused.requirements.buffers] == [(64, 4096), (4096,), (64, 4096)]
 
 
+def test_ffn_block_plan_emits_four_launches():
+    """GEMM + residual, RMSNorm, gated GEMM, GEMM + residual: one launch per statement, the
+    intermediates are global values the runtime allocates."""
+    plan = plans.ffn_block(16, 512, 1024)
+    source = tl.emit(plan)
+    assert source.launch_count == 4
+    kernels = [line.split("rc = ")[1].split("(")[0] for line in source.code.splitlines()
+               if "rc = trinity_sm100_" in line and "_bf16" in line]
+    assert kernels == ["trinity_sm100_gemm_bf16", "trinity_sm100_rmsnorm_bf16",
+                       "trinity_sm100_gemm_bf16", "trinity_sm100_gemm_bf16"]
+    metadata = json.loads(plan.metadata_json())
+    assert [v["storage"] for v in metadata["values"]].count("global") == 3
+    assert [i["name"] for i in metadata["inputs"]] == sorted(["attn", "Wo", "R", "g", "Wg", "Wu", "Wd"])
+
+
 def test_world_size_other_than_one_is_refused_like_the_reference():
     # tests/streamed.rs:202-209, python/tests/test_tensor_ops.py:25-28
     with pytest.raises(NotImplementedError, match="Persistent"):

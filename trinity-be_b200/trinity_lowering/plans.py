@@ -198,6 +198,80 @@ def softmax(rows, cols, target="sm100"):
     return b.build([loop], "Y", y)
 
 
+# ---------------------------------------------------------------- whole FFN block
+def ffn_block(m, d_model, d_ff, eps=1e-6, target="sm100"):
+    """The decode-time feed-forward block of the reference's FFN fixture (tests/fixtures/ir/IR.v3.txt
+    there: output projection, residual add, RMSNorm, SwiGLU, down projection, residual add) as one
+    plan of four statements with BF16 intermediates in global memory:
+
+        X1 = attn @ Wo + R                      (GEMM, residual as a matrix side operand)
+        Xn = X1 / sqrt(mean(X1^2) + eps) * g    (RMSNorm)
+        H  = (Xn @ Wu) * silu(Xn @ Wg)          (gated GEMM)
+        Y  = H @ Wd + X1                        (GEMM, second residual)"""
+    b = PhysicalPlanBuilder(1, target)
+
+    def gemm(a, a_shape, weights, n, side, out, tag):
+        """out[m,n] = f(sum_k a @ weights[i]) with f given by `side`; returns the statement."""
+        k = a_shape[1]
+        tm, tn = f"(clipped_tile m{tag} 128)", f"(clipped_tile n{tag} 128)"
+        ci = index(tm, tn)
+        loops, accs = [], []
+        for i, weight in enumerate(weights):
+            acc = b.add_value("fp32", [m, n], "register")
+            var = f"k{tag}{i}"
+            kt = f"(clipped_tile {var} 64)"
+            rhs = (f"(+ {load(acc, [m, n], ci)} (@ {load(a, a_shape, index(tm, kt))} "
+                   f"{load(weight, [k, n], index(kt, tn))}))")
+            op = b.add_operation([a, weight], [acc], expression=store(acc, [m, n], rhs, ci))
+            loops.append(b.add_loop("sequential", var, 0, _ceil(k, 64), 64, [op]))
+            accs.append(acc)
+        inflows, value = side(accs, ci)
+        epilogue = b.add_operation(inflows, [out], expression=store(out, [m, n], value, ci))
+        cols = b.add_loop("parallel", f"n{tag}", 0, _ceil(n, 128), 128, [*loops, epilogue])
+        return b.add_loop("parallel", f"m{tag}", 0, _ceil(m, 128), 128, [cols])
+
+    attn = b.add_value("bf16", [m, d_model], "external")
+    wo = b.add_value("bf16", [d_model, d_model], "external")
+    residual = b.add_value("bf16", [m, d_model], "external")
+    gain = b.add_value("bf16", [d_model], "external")
+    wg = b.add_value("bf16", [d_model, d_ff], "external")
+    wu = b.add_value("bf16", [d_model, d_ff], "external")
+    wd = b.add_value("bf16", [d_ff, d_model], "external")
+    for name, v in (("attn", attn), ("Wo", wo), ("R", residual), ("g", gain), ("Wg", wg), ("Wu", wu), ("Wd", wd)):
+        b.bind_input(name, v)
+    x1 = b.add_value("bf16", [m, d_model], "global")
+    xn = b.add_value("bf16", [m, d_model], "global")
+    h = b.add_value("bf16", [m, d_ff], "global")
+    y = b.add_value("bf16", [m, d_model], "external")
+
+    def plus(matrix):
+        def side(accs, ci):
+            return [accs[0], matrix], f"(+ {load(accs[0], [m, d_model], ci)} {load(matrix, [m, d_model], ci)})"
+        return side
+
+    def swiglu(accs, ci):
+        g = load(accs[1], [m, d_ff], ci)
+        return [accs[0], accs[1]], f"(* {load(accs[0], [m, d_ff], ci)} (* {g} (sigmoid {g})))"
+
+    first = gemm(attn, [m, d_model], [wo], d_model, plus(residual), x1, "a")
+    # RMSNorm of X1 (the row kernels' plan form, see rmsnorm above)
+    ss = b.add_value("fp32", [m], "register")
+    row = "(tile row 1)"
+    red, chunk, tile = index(row), index(row, "(clipped_tile k 128)"), index(row, "(clipped_tile col 128)")
+    rhs = f"(+ {load(ss, [m], red)} (rsum (sqr {load(x1, [m, d_model], chunk)}) 1))"
+    reduce = b.add_operation([x1], [ss], expression=store(ss, [m], rhs, red))
+    kloop = b.add_loop("sequential", "k", 0, _ceil(d_model, 128), 128, [reduce])
+    mean = f"(+ (/ {load(ss, [m], red)} {float_bits(float(d_model))}) {float_bits(eps)})"
+    value = (f"(* (/ {load(x1, [m, d_model], tile)} (bcast (sqrt {mean}) 1)) "
+             f"(bcast {load(gain, [d_model], index('(clipped_tile col 128)'))} 0))")
+    norm = b.add_operation([x1, ss, gain], [xn], expression=store(xn, [m, d_model], value, tile))
+    cloop = b.add_loop("parallel", "col", 0, _ceil(d_model, 128), 128, [norm])
+    second = b.add_loop("parallel", "row", 0, m, 1, [kloop, cloop])
+    third = gemm(xn, [m, d_model], [wu, wg], d_ff, swiglu, h, "b")
+    fourth = gemm(h, [m, d_ff], [wd], d_model, plus(x1), y, "c")
+    return b.build([first, second, third, fourth], "Y", y)
+
+
 # ---------------------------------------------------------------- MLA decode
 def mla_decode(batch, heads, seq, d_qk=576, d_v=512, scale=None, target="sm100"):
     """out[b] = softmax(scale * q[b] @ cache[b]^T) @ cache[b][:, :d_v] for every batch entry."""
