@@ -1,6 +1,7 @@
 """Regenerates tests/golden/reference_eval.pt from the reference's own evaluator.
 
-Run where the reference tree is mounted:  python tests/golden/make_golden.py [/root/reference]
+Run where the reference tree is available:  python tests/golden/make_golden.py <reference root>
+(or set TRINITY_REFERENCE_ROOT).
 It imports ``_reference`` from <reference>/src/emit/wrapper/reference.py, evaluates the
 workload equations of ``oracle.workloads`` on small seeded inputs and stores inputs' seeds,
 shapes and the reference's results (BF16 bit patterns).  The committed fixture lets the oracle
@@ -32,7 +33,10 @@ def bits(t):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    import os
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TRINITY_REFERENCE_ROOT")
+    if not root:
+        raise SystemExit("usage: make_golden.py <reference root>")
     ref = reference_evaluator(root)
 
     def stored(equation, env, shape, dtype="bf16"):

@@ -88,6 +88,18 @@ def test_streamed_config_1024_uniform():
     torch.testing.assert_close(out.float(), expected.float(), atol=0.125, rtol=0.02)
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 8192, 1024), (1, 4096, 2048), (100, 1000, 4096)])
+def test_decode_time_shapes(m, n, k):
+    """A few output rows against a large weight: the kernel streams the weight through
+    64-column tiles (one partly filled row tile, many column tiles)."""
+    a, w, bias = wl.gemm_inputs(m, n, k, 77, "normal")
+    out = run_gemm(a, w, bias, bias_mode=kernels.BIAS_COL_VECTOR)
+    assert_close_bf16(out, wl.gemm_oracle(a, w, bias), max_ulp=1, max_abs=2e-2)
+    out32 = run_gemm(a, w, None, out_dtype=torch.float32)
+    exact = (a.double() @ w.double()).float()
+    assert (out32 - exact).norm() / exact.norm() < 1e-5
+
+
 @pytest.mark.parametrize("m,n,k", [(2048, 2304, 1024), (4096, 4096, 512)])
 def test_bias_relu_many_tiles(m, n, k):
     a, w, bias = wl.gemm_inputs(m, n, k, 1235, "normal")

@@ -163,7 +163,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   constexpr int kChunksB = kBN / 64;                 // 64-column TMA boxes per stage
   constexpr uint32_t kTmemCols = 2 * kBN;            // double-buffered accumulator
   constexpr uint32_t kIdesc = umma_idesc_bf16(kBM, kBN, 0, 1);
-  static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
+  static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
+                "TMEM allocation must be a power of two");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -562,11 +563,22 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
     return f32 ? launch_gemm<256, 4, true, true>(g, sm_count, stream)
                : launch_gemm<256, 4, true, false>(g, sm_count, stream);
   }
-  // Wide tiles once there are enough of them to fill the machine, narrow ones otherwise.
-  const long long wide_tiles = ((g.m + kBM - 1) / kBM) * ((g.n + 255) / 256);
+  // Wide tiles once there are enough of them to fill the machine.  Otherwise the tile width
+  // that finishes in the fewest column-steps: a persistent CTA works through
+  // ceil(tiles / SMs) tiles of that width.  With few output rows (decode-time GEMMs) the kernel
+  // streams the weight matrix, and 64-column tiles are what spreads an [K, 8192] weight over
+  // 128 SMs instead of 64, each with an eight-stage ring in flight.
+  const long long row_tiles = (g.m + kBM - 1) / kBM;
+  const long long wide_tiles = row_tiles * ((g.n + 255) / 256);
   if (wide_tiles >= sm_count) {
     return f32 ? launch_gemm<256, 4, false, true>(g, sm_count, stream)
                : launch_gemm<256, 4, false, false>(g, sm_count, stream);
+  }
+  const long long steps128 = (row_tiles * ((g.n + 127) / 128) + sm_count - 1) / sm_count * 128;
+  const long long steps64 = (row_tiles * ((g.n + 63) / 64) + sm_count - 1) / sm_count * 64;
+  if (steps64 < steps128) {
+    return f32 ? launch_gemm<64, 8, false, true>(g, sm_count, stream)
+               : launch_gemm<64, 8, false, false>(g, sm_count, stream);
   }
   return f32 ? launch_gemm<128, 6, false, true>(g, sm_count, stream)
              : launch_gemm<128, 6, false, false>(g, sm_count, stream);

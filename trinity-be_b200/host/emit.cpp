@@ -729,8 +729,8 @@ struct Emitter {
     launch.code = code.str();
     for (int i = 0; i < 5; ++i) launch.operations.push_back(top.body[i].operation);
     launch.operations.push_back(vloop.body[0].operation);
-    launch.shared_memory_bytes = 197888;
-    launch.block_threads = 192;
+    launch.shared_memory_bytes = 214528;   // four cache stages, four exchange tiles, barriers
+    launch.block_threads = 480;            // producer, two MMA issuers, twelve softmax warps
     launches.push_back(std::move(launch));
     return true;
   }
