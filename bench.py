@@ -178,6 +178,8 @@ def make_workload(name, device, world=None):
 
         w.h2d = sum(t.numel() * 2 for t in host)
         w.d2h = host_out.numel() * 2
+        # host cost of one launch through the public API (runtime checks + trinity_launch), no copies
+        w.host_launch = lambda: api["execution"].run()
 
         def cpu_sample(threads, budget_s):
             torch.set_num_threads(threads)
@@ -492,7 +494,16 @@ def main():
         stop.synchronize()
         e2e_ms = start.elapsed_time(stop)
         barrier()
-    launches = k.launch_count() - launches_before
+        launches_after = k.launch_count()
+        host_launch_us = None
+        if getattr(w, "host_launch", None) is not None:
+            calls = 100
+            t0 = time.perf_counter()
+            for _ in range(calls):
+                w.host_launch()
+            host_launch_us = (time.perf_counter() - t0) / calls * 1e6
+            barrier()
+    launches = launches_after - launches_before
     if not args.no_graph:
         launches += args.steps * w.kernels_per_step  # replays do not pass through the library
 
@@ -535,6 +546,8 @@ def main():
         "gpu_launches": launches,
         "clocks": clocks.summary(),
     }
+    if host_launch_us is not None:
+        line["host_launch_us"] = host_launch_us   # public-API launch, host side only
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         v, sample, _ = w.cpu_sample(threads, budget_s=10.0)
