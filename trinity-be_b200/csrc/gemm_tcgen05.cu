@@ -11,6 +11,8 @@
 //             buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps tile i+1
 //   warps 2-5 epilogue: tcgen05.ld 32 columns at a time, bias / activation in FP32, one
 //             rounding to the output type, 128B-swizzled staging and a TMA store per warp
+//   warps 6-9 only in the row-parallel form with the cross-GPU sum (320 threads): reducers that
+//             add the ranks' partial tiles over NVLink peer memory while the MMAs go on
 //
 // Algorithmic traffic per launch: (M*K + K*N [+K*N]) * 2 + bias + M*N*out_bytes.
 #include "host_common.h"
@@ -21,7 +23,8 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 192;        // TMA producer, MMA issuer, four epilogue warps
+constexpr int kGemmFusedThreads = 320;   // ... plus four warps that do the cross-GPU reduction
 constexpr int kGroupM = 16;           // tile rasterisation: 16 row blocks share B columns in L2
 constexpr int kStageBytesA = kBM * kBK * 2;
 constexpr int kStoreBufBytes = 32 * 128;  // 32 rows x 128 B per epilogue warp
@@ -71,15 +74,16 @@ __device__ __forceinline__ float apply_activation(float x, int activation) {
   return x;
 }
 
-// Fused all-reduce duty of the epilogue warps (128 threads, `tid` in [0,128)).  Every rank owns
-// the same 128/world rows of *every* tile: it waits until all ranks have stored their partial of
-// the tile, adds the partials of its rows in rank order in FP32, rounds once and pushes the
-// result into every rank's buffer.  Small equal duties after every tile keep NVLink busy all the
-// time and cost each CTA about one round trip per tile.
+// Fused all-reduce duty of the reducer warps (128 threads, `tid` in [0,128), named barrier
+// `barrier_id`).  Every rank owns the same 128/world rows of *every* tile: it waits until all
+// ranks have stored their partial of the tile, adds the partials of its rows in rank order in
+// FP32, rounds once and pushes the result into every rank's buffer.  Small equal duties per tile
+// keep NVLink busy all the time; a duty costs about one NVLink round trip, which is why it
+// runs on warps of its own and not on the epilogue warps the tensor pipe waits for.
 // Returns false if a wait gave up (uniform over the 128 threads).
 template <int kBN>
 __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const GemmPeers& peers, int tile,
-                                                  int m0, int n0, int tid) {
+                                                  int m0, int n0, int tid, int barrier_id) {
   uint32_t good = 1;
   if (tid < peers.world)
     good = wait_flag(peers.flags[peers.rank] + static_cast<long long>(tile) * peers.world + tid, peers.epoch,
@@ -89,11 +93,11 @@ __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const Gem
       "{\n"
       ".reg .pred a, b;\n"
       "setp.ne.u32 a, %1, 0;\n"
-      "bar.red.and.pred b, 1, 128, a;\n"
+      "bar.red.and.pred b, %2, 128, a;\n"
       "selp.u32 %0, 1, 0, b;\n"
       "}\n"
       : "=r"(all_good)
-      : "r"(good)
+      : "r"(good), "r"(barrier_id)
       : "memory");
   if (!all_good) return false;
   // Four vectors per thread and step, all loads issued before the first add: with NVLink round
@@ -152,7 +156,7 @@ __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const Gem
 }
 
 template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kFused ? kGemmFusedThreads : kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_b2,
@@ -268,7 +272,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (ok) umma_commit(tmem_full_bar(acc));
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     uint8_t* my_staging = staging + quad * 2 * kStoreBufBytes;
@@ -279,7 +283,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t store_buf = 0;
     bool ok = true;
     const int etid = threadIdx.x - 64;      // 0..127 within the epilogue group
-    int owed_tile = -1, owed_m0 = 0, owed_n0 = 0;   // fused all-reduce: duty carried one tile behind
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
       int m_blk, n_blk;
       tile_coords(p, tile, m_blk, n_blk);
@@ -420,9 +423,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
       if (kFused) {
-        // This rank's partial of the tile is complete in memory -> tell the tile's owner, then do
-        // the reduction this CTA still owes for its previous tile (peers have had a whole tile
-        // time to finish theirs, so the wait inside is short).
+        // This rank's partial of the tile is complete in memory -> tell every rank's reducer
+        // warps (this CTA's own included), which own a slice of the tile's rows each.
         if (lane == 0) {
           tma_store_wait_all();
           __threadfence_system();
@@ -430,20 +432,27 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (etid < peers.world)
           flag_store(peers.flags[etid] + static_cast<long long>(tile) * peers.world + peers.rank, peers.epoch);
-        if (owed_tile >= 0) ok = reduce_owned_tile<kBN>(p, peers, owed_tile, owed_m0, owed_n0, etid);
-        owed_tile = tile;
-        owed_m0 = m0;
-        owed_n0 = n0;
       }
     }
     if (lane == 0) tma_store_wait_all();
-    if (kFused) {
-      if (ok && owed_tile >= 0) ok = reduce_owned_tile<kBN>(p, peers, owed_tile, owed_m0, owed_n0, etid);
+  }
+  if (kFused && warp >= 6) {
+    // ------------------------------------------------------------ reducer warps (fused all-reduce)
+    // They follow the CTA's own tile sequence: the same CTA index on every rank works on the same
+    // tile at about the same time, so the partials of a tile arrive together.
+    const int rtid = threadIdx.x - kGemmThreads;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
+      ok = reduce_owned_tile<kBN>(p, peers, tile, m_blk * kBM, n_blk * kBN, rtid, 2);
+    }
+    {
       // Retire: once every CTA of this rank has pushed its tiles, tell the peers; the last CTA
       // stays until every peer has said the same, so the output is complete when the kernel ends.
       __threadfence_system();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (etid == 0) {
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (rtid == 0) {
         uint32_t* mine = peers.flags[peers.rank] + static_cast<long long>(p.num_tiles) * peers.world;
         const unsigned prev = atomicAdd(mine + kGemmMaxWorld, 1u);
         if (prev == gridDim.x - 1) {
@@ -513,7 +522,8 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
   const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
   GemmPeers peers = {};
   if (fused) peers = *fused;
-  kernel<<<grid, kGemmThreads, kSmem, stream>>>(map_a, map_b, map_b2, map_out, p, peers);
+  kernel<<<grid, kFused ? kGemmFusedThreads : kGemmThreads, kSmem, stream>>>(map_a, map_b, map_b2,
+                                                                            map_out, p, peers);
   count_launch();
   return check_launch("gemm_bf16_tcgen05");
 }
