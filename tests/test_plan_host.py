@@ -328,3 +328,49 @@ def test_c_abi_libraries_export_every_declared_symbol():
         missing = [name for name in sorted(declared) if not hasattr(handle, name)]
         assert not missing, missing
         assert len(declared) >= 15
+
+
+def test_mla_schedule_queries_need_no_device():
+    """The schedule the MLA entry point will pick is a host computation (148 SMs are assumed when
+    no device is current): scratch sizing and slot counts can be asked for ahead of time."""
+    import ctypes
+    from trinity_lowering import kernels
+    lib = ctypes.CDLL(str(kernels.library_path()))
+    lib.trinity_sm100_mla_default_splits.argtypes = [ctypes.c_int32] * 2
+    lib.trinity_sm100_mla_balanced_slots.argtypes = [ctypes.c_int32] * 2
+    lib.trinity_sm100_mla_scratch_bytes.argtypes = [ctypes.c_int32] * 4
+    lib.trinity_sm100_mla_scratch_bytes.restype = ctypes.c_size_t
+    # one cluster per sequence fills 64 of 74 SM pairs: sequences are not cut
+    assert lib.trinity_sm100_mla_default_splits(64, 4096) == 1
+    assert lib.trinity_sm100_mla_scratch_bytes(64, 128, 512, 1) == 0
+    # few long sequences: equal splits, about one cluster per SM pair
+    splits = lib.trinity_sm100_mla_default_splits(8, 16384)
+    assert 8 <= splits <= 9
+    # a sequence of 64 chunks over runs of 4096 / 74 = 55 chunks touches two or three clusters
+    assert lib.trinity_sm100_mla_balanced_slots(64, 4096) in (2, 3)
+    # more sequences than SM pairs, poorly filled second wave: balanced runs
+    assert lib.trinity_sm100_mla_default_splits(100, 4096) == lib.trinity_sm100_mla_balanced_slots(100, 4096) == 2
+    # never finer than eight chunks per cluster on average
+    assert lib.trinity_sm100_mla_default_splits(1, 512) == 1
+    assert lib.trinity_sm100_mla_balanced_slots(1, 65536) == 74
+    slots = lib.trinity_sm100_mla_balanced_slots(5, 1000)
+    need = lib.trinity_sm100_mla_scratch_bytes(5, 128, 512, slots)
+    assert need >= 5 * slots * 128 * (512 + 2) * 4 and need % 256 == 0
+    assert lib.trinity_sm100_mla_default_splits(0, 4096) == 1
+
+
+def test_package_keeps_the_reference_names():
+    """python/src/trinity_lowering/__init__.py:29-58 of the reference; the Triton entry points
+    import but refuse."""
+    reference_names = [
+        "CompileConfig", "CompileError", "CudaArtifact", "CudaSource", "Implementation", "PhysicalPlan",
+        "PhysicalPlanBuilder", "TritonProgram", "all_gather_implementations", "pointwise_implementations",
+        "reduce_sum_implementations", "broadcast_implementations", "compile", "emit", "emit_python",
+        "emit_triton", "lower_triton", "gemm_implementations", "lower_ir", "DistributedFailure",
+        "ResourceBusy", "RuntimeFailure", "Graph", "IOBuffers", "LoadedModule", "PreparedExecution",
+        "load", "World"]
+    for name in reference_names:
+        assert hasattr(tl, name) and name in tl.__all__, name
+    for refused in (tl.emit_python, tl.emit_triton, tl.lower_triton, tl.TritonProgram):
+        with pytest.raises(NotImplementedError):
+            refused(None)

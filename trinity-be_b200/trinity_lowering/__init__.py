@@ -8,10 +8,10 @@ library (``include/trinity_sm100.h``).
 """
 from . import kernels  # noqa: F401
 from .compiler import (CompileConfig, CompileError, CudaArtifact, CudaSource, Implementation,
-                       PhysicalPlan, PhysicalPlanBuilder, all_gather_implementations,
-                       broadcast_implementations, compile, emit, gemm_implementations,
-                       kernel_candidates, lower_ir, pointwise_implementations,
-                       reduce_sum_implementations)
+                       PhysicalPlan, PhysicalPlanBuilder, TritonProgram, all_gather_implementations,
+                       broadcast_implementations, compile, emit, emit_python, emit_triton,
+                       gemm_implementations, kernel_candidates, lower_ir, lower_triton,
+                       pointwise_implementations, reduce_sum_implementations)
 from .errors import DistributedFailure, ResourceBusy, RuntimeFailure
 from .graph import Graph
 from .runtime import IOBuffers, LoadedModule, PreparedExecution, load
@@ -19,7 +19,8 @@ from .world import World
 
 __all__ = [
     "CompileConfig", "CompileError", "CudaArtifact", "CudaSource", "Implementation", "PhysicalPlan",
-    "PhysicalPlanBuilder", "all_gather_implementations", "pointwise_implementations",
+    "PhysicalPlanBuilder", "TritonProgram", "emit_python", "emit_triton", "lower_triton",
+    "all_gather_implementations", "pointwise_implementations",
     "reduce_sum_implementations", "broadcast_implementations", "compile", "emit", "gemm_implementations",
     "kernel_candidates", "lower_ir", "DistributedFailure", "ResourceBusy", "RuntimeFailure", "Graph",
     "IOBuffers", "LoadedModule", "PreparedExecution", "load", "World", "kernels",

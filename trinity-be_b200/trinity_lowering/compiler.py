@@ -331,3 +331,27 @@ def all_gather_implementations(target_name=DEFAULT_TARGET):
         Implementation("nvshmem.peer_push", {"family": "collective", "tile": (64, 64), "legacy": True}),
         Implementation("nvshmem.peer_pull", {"family": "collective", "tile": (64, 64), "legacy": True}),
     ]
+
+
+# ---------------------------------------------------------------- names kept for importers
+class TritonProgram:
+    """The reference's Triton provider result (src/python.rs:726-753 there).  This provider has no
+    Triton path; the name exists so that ``from trinity_lowering import TritonProgram`` keeps
+    importing, and it cannot be constructed."""
+
+    def __init__(self, *args, **kwargs):
+        raise NotImplementedError("UnsupportedExecution: the sm_100a provider has no Triton path")
+
+
+def _no_triton(name):
+    def refuse(*args, **kwargs):
+        raise NotImplementedError(f"UnsupportedExecution: {name} belongs to the Triton provider, "
+                                  "which the sm_100a provider does not have")
+    refuse.__name__ = name
+    refuse.__doc__ = f"``{name}`` of the reference's Triton provider: refused here."
+    return refuse
+
+
+emit_python = _no_triton("emit_python")
+emit_triton = _no_triton("emit_triton")
+lower_triton = _no_triton("lower_triton")
