@@ -183,3 +183,33 @@ def ffn_block_oracle(t, eps):
     xn = rmsnorm_oracle(x1, t["g"], eps)
     hidden = gated_oracle(xn, t["Wu"], t["Wg"])
     return gemm_oracle(hidden, t["Wd"], x1, None, "matrix")
+
+
+def ffn_ir_inputs(m, d_model, d_ff, seed):
+    g = _gen(seed)
+    return {
+        "attn": _normal((m, d_model), 1.0, g),
+        "Wo": _normal((d_model, d_model), 1.0 / math.sqrt(d_model), g),
+        "X": _normal((m, d_model), 1.0, g),
+        "Wa": _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
+        "Wb": _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
+        "Wd": _normal((d_ff, d_model), 1.0 / math.sqrt(d_ff), g),
+    }
+
+
+def ffn_ir_oracle(t):
+    """The feed-forward block in the spelling of the reference's loop-IR fixture
+    (tests/fixtures/ir/IR.v3.txt:1-131 there): every named tensor is stored in BF16, the row sums
+    of squares in FP32, the normalisation has neither eps nor gain, SwiGLU is four separate
+    steps.  FP32 elementwise math, float64 products narrowed once, as the reference evaluator."""
+    d_model = t["attn"].shape[1]
+    bf = torch.bfloat16
+    p = gemm_oracle(t["attn"], t["Wo"], None)
+    q = (p.float() + t["X"].float()).to(bf)
+    s = q.float().square().sum(dim=1, keepdim=True)
+    n = (q.float() / torch.sqrt(s / float(d_model))).to(bf)
+    a = gemm_oracle(n, t["Wa"], None)
+    b = gemm_oracle(n, t["Wb"], None)
+    sw = (b.float() * torch.sigmoid(b.float())).to(bf)
+    h = (a.float() * sw.float()).to(bf)
+    return gemm_oracle(h, t["Wd"], None)

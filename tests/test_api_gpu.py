@@ -215,6 +215,26 @@ def test_ffn_block_plan(m, d_model, d_ff):
     module.close()
 
 
+@torch.inference_mode()
+def test_ffn_block_from_loop_ir_text():
+    """The same block read from loop-IR text in the reference fixture's spelling (rows taken
+    whole, symbolic tile widths, two projections under one tile loop, normalisation through a
+    broadcast expression): lower_ir -> nine launches -> oracle."""
+    m, d_model, d_ff = 16, 512, 1024
+    text, symbols, dtypes = plans.ffn_ir(m, d_model, d_ff)
+    (plan,) = tl.lower_ir(text, symbols, dtypes)
+    module = build(plan)
+    tensors = wl.ffn_ir_inputs(m, d_model, d_ff, 47)
+    execution = module.prepare({name: t.to(DEV) for name, t in tensors.items()})
+    out = execution.run().clone()
+    execution.wait(30)
+    expected = wl.ffn_ir_oracle(tensors)
+    top = expected.float().abs().max().item()
+    assert_close_bf16(out.cpu(), expected, max_ulp=None, max_abs=2.0 ** (math.floor(math.log2(top)) - 6))
+    execution.close()
+    module.close()
+
+
 # ---------------------------------------------------------------- primitive plans (reference fixtures)
 def _pointwise_plan(name, shape, dtypes, scalar=None):
     import struct

@@ -216,6 +216,26 @@ def test_ffn_block_plan_emits_four_launches():
     assert [i["name"] for i in metadata["inputs"]] == sorted(["attn", "Wo", "R", "g", "Wg", "Wu", "Wd"])
 
 
+def test_ffn_loop_ir_text_lowers_and_emits_nine_launches():
+    """Loop-IR text in the spelling of the reference's feed-forward fixture: rows are `fulltile`
+    (no row loop), tile widths are symbols bound at lowering, the two SwiGLU projections sit
+    under one tile loop, the normalisation broadcasts an expression over the row sums."""
+    text, symbols, dtypes = plans.ffn_ir(16, 512, 1024)
+    (plan,) = tl.lower_ir(text, symbols, dtypes)
+    metadata = json.loads(plan.metadata_json())
+    assert [i["name"] for i in metadata["inputs"]] == ["Wa", "Wb", "Wd", "Wo", "X", "attn"]
+    assert len(metadata["operations"]) == 9 and len(metadata["statements"]) == 8
+    source = tl.emit(plan)
+    kernels = [line.split("rc = ")[1].split("(")[0] for line in source.code.splitlines()
+               if "rc = trinity_sm100_" in line and "stream)" in line and "synchronize" not in line]
+    assert kernels == ["trinity_sm100_gemm_bf16", "trinity_sm100_pointwise", "trinity_sm100_row_reduce_sum",
+                       "trinity_sm100_pointwise", "trinity_sm100_gemm_bf16", "trinity_sm100_gemm_bf16",
+                       "trinity_sm100_pointwise", "trinity_sm100_pointwise", "trinity_sm100_gemm_bf16"]
+    # a tile width that does not divide the extent is refused, as for any `tile` access
+    with pytest.raises(ValueError, match="exactly divide"):
+        tl.emit(tl.lower_ir(text, {**symbols, "tile_n": 96}, dtypes)[0])
+
+
 def test_world_size_other_than_one_is_refused_like_the_reference():
     # tests/streamed.rs:202-209, python/tests/test_tensor_ops.py:25-28
     with pytest.raises(NotImplementedError, match="Persistent"):

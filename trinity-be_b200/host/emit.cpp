@@ -164,11 +164,17 @@ struct Emitter {
     auto tiled = [](const AccessIndex& i) {
       return (i.kind == AccessIndex::Tile || i.kind == AccessIndex::ClippedTile) && !i.width.symbolic;
     };
+    // The row axis may be taken whole (`fulltile`: a decode-time GEMM with a handful of rows and
+    // no row loop, as the reference's feed-forward IR writes it); every other axis is tiled.
+    const bool full_rows = A.indices[0].kind == AccessIndex::FullTile && C.indices[0].kind == AccessIndex::FullTile;
     for (auto* acc : {&A, &B, &C})
-      for (auto& i : acc->indices)
-        if (!tiled(i)) { why = "accesses must be constant-width tiles"; return false; }
+      for (size_t axis = 0; axis < 2; ++axis)
+        if (!tiled(acc->indices[axis]) && !(full_rows && axis == 0 && acc != &B)) {
+          why = "accesses must be constant-width tiles (rows may be fulltile)";
+          return false;
+        }
     const std::string &mv = C.indices[0].variable, &nv = C.indices[1].variable, &kv = k.variable;
-    if (A.indices[0].variable != mv || A.indices[1].variable != kv || B.indices[0].variable != kv ||
+    if ((!full_rows && A.indices[0].variable != mv) || A.indices[1].variable != kv || B.indices[0].variable != kv ||
         B.indices[1].variable != nv) { why = "tile variables do not form C[m,n] += A[m,k] B[k,n]"; return false; }
     const Value &va = value(A.value), &vb = value(B.value), &vc = value(C.value);
     if (va.dtype != DType::Bf16 || vb.dtype != DType::Bf16) { why = "operands must be bf16"; return false; }
@@ -176,12 +182,15 @@ struct Emitter {
     const int64_t M = va.shape[0], K = va.shape[1], N = vb.shape[1];
     if (vb.shape[0] != K || vc.shape[0] != M || vc.shape[1] != N) { why = "shape mismatch"; return false; }
     if (K % 8 || N % 8) { why = "K and N must be multiples of 8"; return false; }
-    const LoopInfo* ml = find_loop(parallel, mv);
+    const LoopInfo* ml = full_rows ? nullptr : find_loop(parallel, mv);
     const LoopInfo* nl = find_loop(parallel, nv);
-    if (!ml || !nl) { why = "output tiles must be indexed by the enclosing parallel loops"; return false; }
-    check_parallel_axis(C.indices[0], *ml, M, "gemm rows");
+    if ((!full_rows && !ml) || !nl) { why = "output tiles must be indexed by the enclosing parallel loops"; return false; }
+    if (parallel.size() != (full_rows ? 1u : 2u))
+      invalid_execution("gemm: overlap between CTAs (a parallel loop does not index the output)");
+    if (!full_rows) check_parallel_axis(C.indices[0], *ml, M, "gemm rows");
     check_parallel_axis(C.indices[1], *nl, N, "gemm columns");
-    if (A.indices[0].width.constant != C.indices[0].width.constant || B.indices[1].width.constant != C.indices[1].width.constant)
+    if ((!full_rows && A.indices[0].width.constant != C.indices[0].width.constant) ||
+        B.indices[1].width.constant != C.indices[1].width.constant)
       invalid_execution("gemm: operand tiles differ from the output tile");
     const int64_t wk = A.indices[1].width.constant;
     if (B.indices[0].width.constant != wk) invalid_execution("gemm: A and B disagree on the K tile width");
@@ -209,6 +218,28 @@ struct Emitter {
     }
   };
 
+  void emit_plain_gemm(const Accumulator& a) {
+    const Value& vo = value(a.acc);
+    std::ostringstream c;
+    c << "  {\n    trinity_sm100_gemm g = {};\n";
+    c << "    g.a = " << slot_ptr(slot(a.a)) << ";\n    g.b = " << slot_ptr(slot(a.b)) << ";\n";
+    c << "    g.out = " << slot_ptr(slot(a.acc)) << ";\n";
+    need_alignment(a.a, 16);
+    need_alignment(a.b, 16);
+    need_alignment(a.acc, 16);
+    c << "    g.m = " << a.m << "; g.n = " << a.n << "; g.k = " << a.k << ";\n";
+    c << "    g.lda = " << a.k << "; g.ldb = " << a.n << "; g.ldo = " << a.n << ";\n";
+    c << "    g.activation = 0;\n    g.out_dtype = " << dt_enum(vo.dtype) << ";\n";
+    c << "    rc = trinity_sm100_gemm_bf16(&g, stream);\n  }\n";
+    Launch l;
+    l.kernel = "trinity_sm100_gemm_bf16";
+    l.code = c.str();
+    l.operations = {a.op};
+    l.shared_memory_bytes = 230656;
+    l.block_threads = 192;
+    launches.push_back(std::move(l));
+  }
+
   bool try_gemm(const Statement& top) {
     std::vector<LoopInfo> parallel;
     const std::vector<Statement>* body = strip_parallel(top, parallel);
@@ -225,7 +256,18 @@ struct Emitter {
       accs.push_back(a);
       ++next;
     }
-    if (accs.empty() || accs.size() > 2) return false;
+    if (accs.empty()) return false;
+    // Several accumulations under one tile nest, each into its own global value and none consumed
+    // by an epilogue (the reference's feed-forward IR computes the two SwiGLU projections so):
+    // independent GEMMs, one launch each.
+    if (next == body->size() && accs.size() >= 2) {
+      for (auto& a : accs)
+        if (value(a.acc).storage == Storage::Register)
+          unsupported("NoProvider: sm100.gemm: a register accumulator without an epilogue is never stored");
+      for (auto& a : accs) emit_plain_gemm(a);
+      return true;
+    }
+    if (accs.size() > 2) return false;
     if (accs.size() == 2 && (accs[0].a != accs[1].a || accs[0].m != accs[1].m || accs[0].n != accs[1].n ||
                              !same_access(accs[0].acc_access.indices == accs[1].acc_access.indices ? accs[0].acc_access : accs[0].acc_access, accs[0].acc_access)))
       unsupported("NoProvider: sm100.gemm: two accumulators must share the left operand and shape");
@@ -375,6 +417,47 @@ struct Emitter {
     b.operands.emplace_back(value_id, broadcast);
     return int(b.operands.size()) - 1;
   }
+  // The operand of a broadcast: a vector along the output's rows (axis 1) or columns (axis 0), or
+  // a pointwise expression over such vectors and constants (`bcast (sqrt (/ v 4096)) 1`).  The
+  // interpreter evaluates it per output element, which repeats a little arithmetic per row.
+  bool pw_compile_vector(const Expression& e, const TensorAccess& dst, int axis, PwBuild& b, std::string& why) {
+    switch (e.kind) {
+      case Expression::ConstInt: {
+        const float f = float(e.integer);
+        uint32_t bits;
+        memcpy(&bits, &f, 4);
+        b.program.push_back(2);
+        b.program.push_back(bits);
+        return true;
+      }
+      case Expression::ConstF32: b.program.push_back(2); b.program.push_back(e.f32_bits); return true;
+      case Expression::Load: {
+        const TensorAccess& s = e.access;
+        if (s.indices.size() != 1 || !s.view_shape.empty()) { why = "broadcast of a non-vector"; return false; }
+        const int along = axis == 1 ? 0 : 1;   // the output axis the vector follows
+        if (s.indices[0] == dst.indices[along] && value(s.value).shape[0] == value(dst.value).shape[along]) {
+          b.program.push_back(1u | (uint32_t(pw_operand(b, s.value, axis == 1 ? 1 : 2)) << 8));
+          return true;
+        }
+        why = "broadcast operand does not follow the output rows or columns";
+        return false;
+      }
+      case Expression::Add: case Expression::Sub: case Expression::Mul: case Expression::Div: case Expression::Max: {
+        if (!pw_compile_vector(*e.args[0], dst, axis, b, why) || !pw_compile_vector(*e.args[1], dst, axis, b, why)) return false;
+        b.program.push_back(e.kind == Expression::Add ? 16 : e.kind == Expression::Sub ? 17 : e.kind == Expression::Mul ? 18 : e.kind == Expression::Div ? 19 : 20);
+        return true;
+      }
+      case Expression::Sqr: case Expression::Sqrt: case Expression::Sigmoid: case Expression::Relu: case Expression::Exp: {
+        if (!pw_compile_vector(*e.args[0], dst, axis, b, why)) return false;
+        b.program.push_back(e.kind == Expression::Sqr ? 32 : e.kind == Expression::Sqrt ? 33 : e.kind == Expression::Sigmoid ? 34 : e.kind == Expression::Relu ? 35 : 36);
+        return true;
+      }
+      default:
+        why = "broadcast of an expression that is not pointwise over vectors";
+        return false;
+    }
+  }
+
   bool pw_compile(const Expression& e, const TensorAccess& dst, PwBuild& b, std::string& why) {
     auto constant = [&](float f) {
       uint32_t bits;
@@ -391,18 +474,8 @@ struct Emitter {
         b.program.push_back(1u | (uint32_t(pw_operand(b, e.access.value, 0)) << 8));
         return true;
       case Expression::Broadcast: {
-        const Expression& s = *e.args[0];
-        if (s.kind != Expression::Load || s.access.indices.size() != 1 || dst.indices.size() != 2) { why = "broadcast of a non-vector"; return false; }
-        if (e.axis == 1 && s.access.indices[0] == dst.indices[0] && value(s.access.value).shape[0] == value(dst.value).shape[0]) {
-          b.program.push_back(1u | (uint32_t(pw_operand(b, s.access.value, 1)) << 8));
-          return true;
-        }
-        if (e.axis == 0 && s.access.indices[0] == dst.indices[1] && value(s.access.value).shape[0] == value(dst.value).shape[1]) {
-          b.program.push_back(1u | (uint32_t(pw_operand(b, s.access.value, 2)) << 8));
-          return true;
-        }
-        why = "broadcast operand does not follow the output rows or columns";
-        return false;
+        if (dst.indices.size() != 2 || (e.axis != 0 && e.axis != 1)) { why = "broadcast of a non-vector"; return false; }
+        return pw_compile_vector(*e.args[0], dst, e.axis, b, why);
       }
       case Expression::Add: case Expression::Sub: case Expression::Mul: case Expression::Div: case Expression::Max: {
         if (!pw_compile(*e.args[0], dst, b, why) || !pw_compile(*e.args[1], dst, b, why)) return false;
@@ -485,9 +558,12 @@ struct Emitter {
   // ------------------------------------------------------------------ row reduce-sum statement
   bool try_row_reduce(const Statement& top) {
     std::vector<LoopInfo> loops;
-    const std::vector<Statement>* body = strip_parallel(top, loops);
-    if (!body || loops.size() != 1 || body->size() != 1) return false;
-    const Statement& k = (*body)[0];
+    // Either one parallel row loop around the reduction loop, or the reduction loop alone with
+    // all rows taken at once (`fulltile`, as the reference's feed-forward IR writes it).
+    const bool whole = top.is_loop && top.kind == LoopKind::Sequential;
+    const std::vector<Statement>* body = whole ? nullptr : strip_parallel(top, loops);
+    if (!whole && (!body || loops.size() != 1 || body->size() != 1)) return false;
+    const Statement& k = whole ? top : (*body)[0];
     LoopInfo kl;
     if (!k.is_loop || k.kind != LoopKind::Sequential || k.body.size() != 1 || k.body[0].is_loop || !constant_loop(k, kl))
       return false;
@@ -508,10 +584,10 @@ struct Emitter {
     if (vx.shape.size() != 2 || vy.shape.size() != 1 || vy.shape[0] != vx.shape[0] || vy.dtype != DType::Fp32 ||
         vy.storage == Storage::Register || vx.dtype == DType::Fp16)
       return false;
-    if (Y.indices[0].kind == AccessIndex::FullTile || X.indices[0] != Y.indices[0] || X.indices[1].kind == AccessIndex::FullTile ||
-        X.indices[1].variable != kl.variable || X.indices[1].width.symbolic)
+    if ((Y.indices[0].kind == AccessIndex::FullTile) != whole || X.indices[0] != Y.indices[0] ||
+        X.indices[1].kind == AccessIndex::FullTile || X.indices[1].variable != kl.variable || X.indices[1].width.symbolic)
       return false;
-    check_parallel_axis(Y.indices[0], loops[0], vy.shape[0], "reduce rows");
+    if (!whole) check_parallel_axis(Y.indices[0], loops[0], vy.shape[0], "reduce rows");
     const int64_t wk = X.indices[1].width.constant;
     if (kl.start != 0 || kl.step != wk || kl.stop < vx.shape[1])
       invalid_execution("reduce_sum: the reduction loop must cover the row in steps of its tile width");

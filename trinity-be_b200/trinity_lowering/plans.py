@@ -272,6 +272,61 @@ def ffn_block(m, d_model, d_ff, eps=1e-6, target="sm100"):
     return b.build([first, second, third, fourth], "Y", y)
 
 
+def ffn_ir(m, d_model, d_ff, tile_n=128, tile_k=64, tile_p=128):
+    """The same block in the loop-IR *text* notation that ``lower_ir`` reads, spelled the way the
+    reference's feed-forward fixture spells it (tests/fixtures/ir/IR.v3.txt there): no row loop
+    (rows are ``fulltile``), symbolic tile widths, BF16 tensors between all steps, RMSNorm without
+    eps or gain, SwiGLU as two projections followed by separate pointwise steps:
+
+        P = attn @ Wo; Q = P + X; s = rsum(Q^2); N = Q / sqrt(s / d_model)
+        A = N @ Wa; B = N @ Wb; S = B * sigmoid(B); H = A * S; Y = H @ Wd
+
+    Returns (text, symbols, dtypes) for ``lower_ir``; nine launches on the sm_100a provider."""
+    def view(kind, name, *extents):
+        axes = " ".join(f"(axis a_{i} {n})" for i, n in enumerate(extents))
+        return f"(view ({kind} {name}) (layout {axes}))"
+
+    def at(*slots):
+        return "(keyed_index " + " ".join(f"(slot a_{i} {s})" for i, s in enumerate(slots)) + ")"
+
+    def tile(var):
+        return f"(tile {var} tile_{var})"
+
+    def matmul(dst_kind, dst, lhs_kind, lhs, weight, rows, inner, cols, out_var, k_var):
+        c = view(dst_kind, dst, rows, cols)
+        ci = at("fulltile", tile(out_var))
+        a = f"(load {view(lhs_kind, lhs, rows, inner)} {at('fulltile', tile(k_var))})"
+        b = f"(load {view('input', weight, inner, cols)} {at(tile(k_var), tile(out_var))})"
+        return f"(sloop 0 {inner} tile_{k_var} {k_var} (store {c} (+ (load {c} {ci}) (@ {a} {b})) {ci}))"
+
+    def pointwise(dst, cols, var, rhs):
+        return f"(ploop 0 {cols} tile_{var} {var} (store {view('tensor', dst, m, cols)} {rhs} {at('fulltile', tile(var))}))"
+
+    def elem(kind, name, cols, var):
+        return f"(load {view(kind, name, m, cols)} {at('fulltile', tile(var))})"
+
+    vec = view("tensor", "s", m)
+    steps = [
+        f"(ploop 0 {d_model} tile_n n {matmul('tensor', 'P', 'input', 'attn', 'Wo', m, d_model, d_model, 'n', 'k')})",
+        pointwise("Q", d_model, "n", f"(+ {elem('tensor', 'P', d_model, 'n')} {elem('input', 'X', d_model, 'n')})"),
+        (f"(sloop 0 {d_model} tile_k k (store {vec} (+ (load {vec} {at('fulltile')}) "
+         f"(rsum (sqr {elem('tensor', 'Q', d_model, 'k')}) 1)) {at('fulltile')}))"),
+        pointwise("N", d_model, "k",
+                  f"(/ {elem('tensor', 'Q', d_model, 'k')} (bcast (sqrt (/ (load {vec} {at('fulltile')}) {d_model})) 1))"),
+        (f"(ploop 0 {d_ff} tile_p p (seq {matmul('tensor', 'A', 'tensor', 'N', 'Wa', m, d_model, d_ff, 'p', 'k')} "
+         f"{matmul('tensor', 'B', 'tensor', 'N', 'Wb', m, d_model, d_ff, 'p', 'k')}))"),
+        pointwise("S", d_ff, "p", f"(* {elem('tensor', 'B', d_ff, 'p')} (sigmoid {elem('tensor', 'B', d_ff, 'p')}))"),
+        pointwise("H", d_ff, "p", f"(* {elem('tensor', 'A', d_ff, 'p')} {elem('tensor', 'S', d_ff, 'p')})"),
+        f"(ploop 0 {d_model} tile_n n {matmul('output', 'Y', 'tensor', 'H', 'Wd', m, d_ff, d_model, 'n', 'p')})",
+    ]
+    text = steps[-1]
+    for step in reversed(steps[:-1]):
+        text = f"(seq {step} {text})"
+    dtypes = {name: "bf16" for name in ("attn", "Wo", "X", "Wa", "Wb", "Wd", "P", "Q", "N", "A", "B", "S", "H", "Y")}
+    dtypes["s"] = "fp32"
+    return text, {"tile_n": tile_n, "tile_k": tile_k, "tile_p": tile_p}, dtypes
+
+
 # ---------------------------------------------------------------- MLA decode
 def mla_decode(batch, heads, seq, d_qk=576, d_v=512, scale=None, target="sm100"):
     """out[b] = softmax(scale * q[b] @ cache[b]^T) @ cache[b][:, :d_v] for every batch entry."""
