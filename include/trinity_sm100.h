@@ -91,6 +91,26 @@ typedef struct trinity_sm100_gemm {
 TRINITY_SM100_API int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* stream);
 
 /*
+ * Batched form: `batch` GEMMs of one shape in one launch.  Entry z reads a + z*stride_a and
+ * b + z*stride_b, adds bias + z*stride_bias and writes out + z*stride_out (strides in elements,
+ * multiples of 16 bytes).  stride_b == 0 shares one right operand, stride_bias == 0 one side
+ * operand.  The entries may be interleaved with the rows (stride_a < lda, stride_out < ldo), which
+ * is how per-head products over [tokens, heads, features] tensors are laid out.  The gated form
+ * is not batched.  The bias modes and activations of trinity_sm100_gemm_bf16 apply per entry.
+ *
+ * Serves the grouped per-head projections around latent attention: the absorb product
+ * Q_nope[b,h,:] @ W_DK[h] and the output product T2[b,h,:] @ W_DV[h] of the reference's
+ * batched-MLA fixtures (tests/fixtures/batched_mla/batched_mla_postprocessed_stage14.txt:19-59,
+ * 208-241), which the reference lowers through its Triton provider.
+ */
+typedef struct trinity_sm100_gemm_batch {
+  int64_t batch;
+  int64_t stride_a, stride_b, stride_out, stride_bias;
+} trinity_sm100_gemm_batch;
+TRINITY_SM100_API int trinity_sm100_gemm_batched_bf16(const trinity_sm100_gemm* args,
+                                                      const trinity_sm100_gemm_batch* batch, void* stream);
+
+/*
  * RMSNorm over the last axis:
  *   y[r,c] = x[r,c] / sqrt(sum_c(x[r,c]^2) / cols + eps) * gain[c]      (FP32 math, BF16 I/O)
  * gain may be NULL (no gain) and eps may be 0, which keeps the reference's 0/0 -> NaN for an

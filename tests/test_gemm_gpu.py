@@ -145,3 +145,50 @@ def test_invalid_arguments_are_rejected():
         kernels.gemm(a, b)
     with pytest.raises(ValueError):
         kernels.gemm(a.float(), b)
+
+
+def test_batched_matches_the_single_launches():
+    """One batched launch equals the per-entry launches bit for bit (same tiles, same order of
+    accumulation), with a shared and a per-entry right operand, bias and activation."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(11)
+    a = torch.randn(5, 200, 192, generator=g).bfloat16().to(dev)
+    w = (torch.randn(5, 192, 264, generator=g) / 14).bfloat16().to(dev)
+    bias = torch.randn(5, 264, generator=g).bfloat16().to(dev)
+    out = kernels.gemm_batched(a, w, bias=bias, activation=kernels.ACT_RELU)
+    for z in range(5):
+        single = kernels.gemm(a[z], w[z], bias=bias[z], bias_mode=kernels.BIAS_COL_VECTOR, activation=kernels.ACT_RELU)
+        assert torch.equal(out[z], single)
+    shared = kernels.gemm_batched(a, w[0], out_dtype=torch.float32)
+    for z in range(5):
+        assert torch.equal(shared[z], kernels.gemm(a[z], w[0], out_dtype=torch.float32))
+    torch.cuda.synchronize()
+
+
+def test_per_head_projections_around_latent_attention():
+    """The grouped products of the reference's batched-MLA fixtures: absorb
+    q_nope[b,h,:128] @ W_DK[h] -> [b,h,512] and output t2[b,h,:512] @ W_DV[h] -> [b,h,128], the
+    heads interleaved with the tokens in memory (batch stride below the row pitch), against
+    float64 einsum rounded once."""
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(12)
+    tokens, heads = 64, 128
+    q_nope = torch.randn(tokens, heads, 128, generator=g).bfloat16()
+    w_dk = (torch.randn(heads, 128, 512, generator=g) / 11.3).bfloat16()
+    absorbed = torch.empty(tokens, heads, 512, dtype=torch.bfloat16, device=dev)
+    kernels.gemm_batched(q_nope.to(dev).permute(1, 0, 2), w_dk.to(dev), out=absorbed.permute(1, 0, 2))
+    expected = torch.einsum("thk,hkn->thn", q_nope.double(), w_dk.double()).float().bfloat16()
+    assert_close_bf16(absorbed.cpu(), expected, max_ulp=1, max_abs=2e-2)
+    t2 = torch.randn(tokens, heads, 512, generator=g).bfloat16()
+    w_dv = (torch.randn(heads, 512, 128, generator=g) / 22.6).bfloat16()
+    projected = torch.full((tokens, heads, 128), -123.0, dtype=torch.bfloat16, device=dev)
+    kernels.gemm_batched(t2.to(dev).permute(1, 0, 2), w_dv.to(dev), out=projected.permute(1, 0, 2))
+    expected = torch.einsum("thk,hkn->thn", t2.double(), w_dv.double()).float().bfloat16()
+    assert_close_bf16(projected.cpu(), expected, max_ulp=1, max_abs=2e-2)
+    # ragged: 37 tokens, 3 heads, rows clipped per head without touching the next head's rows
+    small = torch.full((37, 3, 72), -123.0, dtype=torch.bfloat16, device=dev)
+    x = torch.randn(37, 3, 40, generator=g).bfloat16()
+    w = torch.randn(3, 40, 72, generator=g).bfloat16()
+    kernels.gemm_batched(x.to(dev).permute(1, 0, 2), w.to(dev), out=small.permute(1, 0, 2))
+    expected = torch.einsum("thk,hkn->thn", x.double(), w.double()).float().bfloat16()
+    assert_close_bf16(small.cpu(), expected, max_ulp=1)

@@ -47,6 +47,14 @@ struct GemmParams {
   int activation;
   int m, n, k;
   int tiles_m, tiles_n, num_tiles, num_kb;
+  // batched form: num_tiles = batch * tiles_per_batch, batch z = tile / tiles_per_batch
+  int tiles_per_batch;
+  int b_shared;            // one right operand for every batch entry (its map has no batch axis)
+  // A tensor map lists its axes by increasing pitch.  When the batch entries are interleaved
+  // (batch stride below the row pitch, e.g. [rows, heads, k] with the heads as the batch), the
+  // batch axis comes before the row axis and the two coordinates swap places.
+  int a_batch_inside, out_batch_inside;
+  long long stride_bias;   // elements between the side operands of consecutive batch entries
 };
 
 template <int kBN>
@@ -155,7 +163,7 @@ __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const Gem
   return true;
 }
 
-template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false>
+template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false>
 __global__ void __launch_bounds__(kFused ? kGemmFusedThreads : kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b,
@@ -169,6 +177,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   constexpr uint32_t kIdesc = umma_idesc_bf16(kBM, kBN, 0, 1);
   static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
                 "TMEM allocation must be a power of two");
+  static_assert(!(kBatched && (kFused || kGated)), "the batched form is the plain GEMM + epilogue");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -218,7 +227,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(p, tile, m_blk, n_blk);
+        const int z = kBatched ? tile / p.tiles_per_batch : 0;   // batch entry (tensor maps are 3-D)
+        tile_coords(p, kBatched ? tile - z * p.tiles_per_batch : tile, m_blk, n_blk);
         const int m0 = m_blk * kBM;
         const int n0 = n_blk * kOutN;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
@@ -228,6 +238,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           mbar_arrive_expect_tx(full_bar(s), kStage);
           const uint32_t a_dst = smem_base + s * kStage;
           const uint32_t b_dst = a_dst + kStageBytesA;
+          if (kBatched) {
+            tma_load_3d(a_dst, &map_a, full_bar(s), kb * kBK, p.a_batch_inside ? z : m0,
+                        p.a_batch_inside ? m0 : z);
+#pragma unroll
+            for (int j = 0; j < kChunksB; ++j)
+              tma_load_3d(b_dst + j * 8192, &map_b, full_bar(s), n0 + j * 64, kb * kBK, p.b_shared ? 0 : z);
+            continue;
+          }
           tma_load_2d(a_dst, &map_a, full_bar(s), kb * kBK, m0);
 #pragma unroll
           for (int j = 0; j < kChunksB; ++j) {
@@ -285,7 +303,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const int etid = threadIdx.x - 64;      // 0..127 within the epilogue group
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
       int m_blk, n_blk;
-      tile_coords(p, tile, m_blk, n_blk);
+      const int z = kBatched ? tile / p.tiles_per_batch : 0;
+      tile_coords(p, kBatched ? tile - z * p.tiles_per_batch : tile, m_blk, n_blk);
+      const __nv_bfloat16* bias_base = p.bias + (kBatched ? z * p.stride_bias : 0);
       const int m0 = m_blk * kBM;
       const int n0 = n_blk * kOutN;
       const uint32_t acc = local_tile & 1u;
@@ -310,7 +330,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * kBN;
       float row_bias = 0.0f;
       if (p.bias_mode == TRINITY_SM100_BIAS_ROW_VECTOR && row < p.m)
-        row_bias = __bfloat162float(p.bias[row]);
+        row_bias = __bfloat162float(bias_base[row]);
 
       for (int c0 = 0; c0 < kOutN; c0 += kColsPerStore) {
         if (lane == 0) tma_store_wait_read<1>();
@@ -339,7 +359,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           const int gcol = n0 + col;
           if (p.bias_mode == TRINITY_SM100_BIAS_COL_VECTOR) {
             if (gcol + 32 <= p.n) {
-              const uint4* src = reinterpret_cast<const uint4*>(p.bias + gcol);
+              const uint4* src = reinterpret_cast<const uint4*>(bias_base + gcol);
 #pragma unroll
               for (int v4 = 0; v4 < 4; ++v4) {
                 const uint4 b = __ldg(src + v4);
@@ -353,14 +373,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (gcol + j < p.n) x[j] += __bfloat162float(p.bias[gcol + j]);
+                if (gcol + j < p.n) x[j] += __bfloat162float(bias_base[gcol + j]);
             }
           } else if (p.bias_mode == TRINITY_SM100_BIAS_ROW_VECTOR) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) x[j] += row_bias;
           } else if (p.bias_mode == TRINITY_SM100_BIAS_MATRIX) {
             if (row < p.m) {
-              const __nv_bfloat16* brow = p.bias + static_cast<long long>(row) * p.ld_bias + gcol;
+              const __nv_bfloat16* brow = bias_base + static_cast<long long>(row) * p.ld_bias + gcol;
               if (gcol + 32 <= p.n) {
                 const uint4* src = reinterpret_cast<const uint4*>(brow);
 #pragma unroll
@@ -412,9 +432,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (m0 + quad * 32 < p.m && n0 + c0 < p.n)
-            tma_store_2d(&map_out, my_staging_u32 + store_buf * kStoreBufBytes, n0 + c0,
-                         m0 + quad * 32);
+          if (m0 + quad * 32 < p.m && n0 + c0 < p.n) {
+            if (kBatched)
+              tma_store_3d(&map_out, my_staging_u32 + store_buf * kStoreBufBytes, n0 + c0,
+                           p.out_batch_inside ? z : m0 + quad * 32, p.out_batch_inside ? m0 + quad * 32 : z);
+            else
+              tma_store_2d(&map_out, my_staging_u32 + store_buf * kStoreBufBytes, n0 + c0,
+                           m0 + quad * 32);
+          }
           tma_store_commit();
         }
         store_buf ^= 1u;
@@ -480,12 +505,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
-template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false>
-int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, const GemmPeers* fused = nullptr) {
+template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false>
+int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, const GemmPeers* fused = nullptr,
+                const trinity_sm100_gemm_batch* batch = nullptr) {
   constexpr int kOutN = kGated ? kBN / 2 : kBN;
   constexpr int kSmem = gemm_smem_bytes<kBN, kStages>();
   static_assert(kSmem <= 232448, "exceeds the 227 KB shared-memory limit");
-  auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused>;
+  auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched>;
   static bool configured[64] = {};
   int device = 0;
   cudaGetDevice(&device);
@@ -498,15 +524,39 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
   }
   CUtensorMap map_a, map_b, map_b2, map_out;
   int rc;
-  if ((rc = make_tensor_map_2d(&map_a, g.a, 2, g.k, g.m, g.lda * 2, kBK, kBM, true))) return rc;
-  if ((rc = make_tensor_map_2d(&map_b, g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK, true))) return rc;
-  if ((rc = make_tensor_map_2d(&map_b2, kGated ? g.b2 : g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK,
-                               true)))
-    return rc;
   const int out_bytes = kOutF32 ? 4 : 2;
-  if ((rc = make_tensor_map_2d(&map_out, g.out, out_bytes, g.n, g.m, g.ldo * out_bytes,
-                               128 / out_bytes, 32, true)))
-    return rc;
+  const long long entries = kBatched ? batch->batch : 1;
+  if (kBatched) {
+    // a third, outermost axis over the batch entries; a shared right operand keeps extent 1
+    const bool shared_b = batch->stride_b == 0;
+    if (batch->stride_a < g.lda) {
+      if ((rc = make_tensor_map_3d(&map_a, g.a, 2, g.k, entries, g.m, batch->stride_a * 2, g.lda * 2, kBK, 1, kBM, 128)))
+        return rc;
+    } else if ((rc = make_tensor_map_3d(&map_a, g.a, 2, g.k, g.m, entries, g.lda * 2, batch->stride_a * 2, kBK, kBM, 1, 128))) {
+      return rc;
+    }
+    if ((rc = make_tensor_map_3d(&map_b, g.b, 2, g.n, g.k, shared_b ? 1 : entries, g.ldb * 2,
+                                 shared_b ? g.ldb * 2 * g.k : batch->stride_b * 2, 64, kBK, 1, 128)))
+      return rc;
+    map_b2 = map_b;
+    if (batch->stride_out < g.ldo) {
+      if ((rc = make_tensor_map_3d(&map_out, g.out, out_bytes, g.n, entries, g.m, batch->stride_out * out_bytes,
+                                   g.ldo * out_bytes, 128 / out_bytes, 1, 32, 128)))
+        return rc;
+    } else if ((rc = make_tensor_map_3d(&map_out, g.out, out_bytes, g.n, g.m, entries, g.ldo * out_bytes,
+                                        batch->stride_out * out_bytes, 128 / out_bytes, 32, 1, 128))) {
+      return rc;
+    }
+  } else {
+    if ((rc = make_tensor_map_2d(&map_a, g.a, 2, g.k, g.m, g.lda * 2, kBK, kBM, true))) return rc;
+    if ((rc = make_tensor_map_2d(&map_b, g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK, true))) return rc;
+    if ((rc = make_tensor_map_2d(&map_b2, kGated ? g.b2 : g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK,
+                                 true)))
+      return rc;
+    if ((rc = make_tensor_map_2d(&map_out, g.out, out_bytes, g.n, g.m, g.ldo * out_bytes,
+                                 128 / out_bytes, 32, true)))
+      return rc;
+  }
   GemmParams p;
   p.bias = static_cast<const __nv_bfloat16*>(g.bias);
   p.ld_bias = g.ld_bias;
@@ -517,7 +567,12 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
   p.k = int(g.k);
   p.tiles_m = int((g.m + kBM - 1) / kBM);
   p.tiles_n = int((g.n + kOutN - 1) / kOutN);
-  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.tiles_per_batch = p.tiles_m * p.tiles_n;
+  p.num_tiles = int(p.tiles_per_batch * entries);
+  p.b_shared = kBatched && batch->stride_b == 0 ? 1 : 0;
+  p.a_batch_inside = kBatched && batch->stride_a < g.lda ? 1 : 0;
+  p.out_batch_inside = kBatched && batch->stride_out < g.ldo ? 1 : 0;
+  p.stride_bias = kBatched ? batch->stride_bias : 0;
   p.num_kb = int((g.k + kBK - 1) / kBK);
   const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
   GemmPeers peers = {};
@@ -533,13 +588,13 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
 
 using namespace trinity_sm100;
 
-extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* stream_handle) {
-  if (!args) return fail(TRINITY_SM100_E_INVALID, "gemm: null argument block");
-  const trinity_sm100_gemm& g = *args;
+namespace {
+// Argument checks shared by the single and the batched entry point.
+int check_gemm_arguments(const trinity_sm100_gemm& g) {
+  const bool gated = g.activation == TRINITY_SM100_ACT_SILU_GATE;
   if (!g.a || !g.b || !g.out) return fail(TRINITY_SM100_E_INVALID, "gemm: null operand");
   if (g.m <= 0 || g.n <= 0 || g.k <= 0 || g.m > INT32_MAX || g.n > INT32_MAX || g.k > INT32_MAX)
     return fail(TRINITY_SM100_E_INVALID, "gemm: extents must be in [1, 2^31)");
-  const bool gated = g.activation == TRINITY_SM100_ACT_SILU_GATE;
   if (gated && !g.b2) return fail(TRINITY_SM100_E_INVALID, "gemm: gated form needs b2");
   if (g.activation < TRINITY_SM100_ACT_NONE || g.activation > TRINITY_SM100_ACT_SILU_GATE)
     return fail(TRINITY_SM100_E_INVALID, "gemm: unknown activation %d", g.activation);
@@ -565,6 +620,15 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
   if (g.bias_mode == TRINITY_SM100_BIAS_MATRIX &&
       (!aligned16(g.bias) || g.ld_bias % 8 || g.ld_bias < g.n))
     return fail(TRINITY_SM100_E_INVALID, "gemm: bias matrix needs 16-byte aligned rows");
+  return 0;
+}
+}  // namespace
+
+extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* stream_handle) {
+  if (!args) return fail(TRINITY_SM100_E_INVALID, "gemm: null argument block");
+  const trinity_sm100_gemm& g = *args;
+  if (int rc = check_gemm_arguments(g)) return rc;
+  const bool gated = g.activation == TRINITY_SM100_ACT_SILU_GATE;
   int sm_count = 0;
   if (int rc = require_sm100(&sm_count)) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
@@ -592,6 +656,42 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
   }
   return f32 ? launch_gemm<128, 6, false, true>(g, sm_count, stream)
              : launch_gemm<128, 6, false, false>(g, sm_count, stream);
+}
+
+extern "C" int trinity_sm100_gemm_batched_bf16(const trinity_sm100_gemm* args,
+                                               const trinity_sm100_gemm_batch* batch, void* stream_handle) {
+  if (!args || !batch) return fail(TRINITY_SM100_E_INVALID, "gemm_batched: null argument block");
+  const trinity_sm100_gemm& g = *args;
+  const trinity_sm100_gemm_batch& b = *batch;
+  if (int rc = check_gemm_arguments(g)) return rc;
+  if (g.activation == TRINITY_SM100_ACT_SILU_GATE)
+    return fail(TRINITY_SM100_E_UNSUPPORTED, "gemm_batched: the gated form is not batched");
+  if (b.batch <= 0 || b.batch > 65535) return fail(TRINITY_SM100_E_INVALID, "gemm_batched: batch must be in [1, 65535]");
+  const int out_bytes = g.out_dtype == TRINITY_SM100_FP32 ? 4 : 2;
+  if (b.stride_a <= 0 || b.stride_a % 8 || b.stride_b < 0 || b.stride_b % 8 || b.stride_out <= 0 ||
+      (b.stride_out * out_bytes) % 16)
+    return fail(TRINITY_SM100_E_INVALID,
+                "gemm_batched: strides must be positive multiples of 16 bytes (stride_b may be 0 for a shared operand)");
+  if (g.bias_mode != TRINITY_SM100_BIAS_NONE && (b.stride_bias < 0 || b.stride_bias % 8))
+    return fail(TRINITY_SM100_E_INVALID, "gemm_batched: stride_bias must be a non-negative multiple of 8 elements");
+  const long long row_tiles = (g.m + kBM - 1) / kBM;
+  if (row_tiles * ((g.n + 63) / 64) * b.batch > INT32_MAX)
+    return fail(TRINITY_SM100_E_UNSUPPORTED, "gemm_batched: too many tiles");
+  int sm_count = 0;
+  if (int rc = require_sm100(&sm_count)) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  const bool f32 = g.out_dtype == TRINITY_SM100_FP32;
+  // tile width as for the single GEMM, counting the tiles of all batch entries
+  if (row_tiles * ((g.n + 255) / 256) * b.batch >= sm_count)
+    return f32 ? launch_gemm<256, 4, false, true, false, true>(g, sm_count, stream, nullptr, &b)
+               : launch_gemm<256, 4, false, false, false, true>(g, sm_count, stream, nullptr, &b);
+  const long long steps128 = (row_tiles * ((g.n + 127) / 128) * b.batch + sm_count - 1) / sm_count * 128;
+  const long long steps64 = (row_tiles * ((g.n + 63) / 64) * b.batch + sm_count - 1) / sm_count * 64;
+  if (steps64 < steps128)
+    return f32 ? launch_gemm<64, 8, false, true, false, true>(g, sm_count, stream, nullptr, &b)
+               : launch_gemm<64, 8, false, false, false, true>(g, sm_count, stream, nullptr, &b);
+  return f32 ? launch_gemm<128, 6, false, true, false, true>(g, sm_count, stream, nullptr, &b)
+             : launch_gemm<128, 6, false, false, false, true>(g, sm_count, stream, nullptr, &b);
 }
 
 extern "C" size_t trinity_sm100_gemm_allreduce_flag_words(int64_t m, int64_t n, int32_t world) {

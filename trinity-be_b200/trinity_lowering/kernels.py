@@ -18,6 +18,7 @@ DT_BF16, DT_FP32 = 0, 1
 
 EXPORTS = (
     "trinity_sm100_gemm_bf16",
+    "trinity_sm100_gemm_batched_bf16",
     "trinity_sm100_rmsnorm_bf16",
     "trinity_sm100_softmax_bf16",
     "trinity_sm100_mla_scratch_bytes",
@@ -59,6 +60,11 @@ class GemmArgs(ctypes.Structure):
         ("bias_mode", ctypes.c_int32), ("activation", ctypes.c_int32),
         ("out_dtype", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
+
+
+class GemmBatchArgs(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_int64), ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64),
+                ("stride_out", ctypes.c_int64), ("stride_bias", ctypes.c_int64)]
 
 
 class MlaArgs(ctypes.Structure):
@@ -192,6 +198,45 @@ def gemm(a, b, *, bias=None, bias_mode=None, activation=ACT_NONE, b2=None, out=N
         args.bias_mode = bias_mode
     with torch.cuda.device(a.device):
         _check(library().trinity_sm100_gemm_bf16(ctypes.byref(args), _stream(stream)))
+    return out
+
+
+def gemm_batched(a, b, *, bias=None, activation=ACT_NONE, out=None, out_dtype=torch.bfloat16, stream=None):
+    """out[z] = act(a[z] @ b[z] + bias[z]) for every batch entry z in one launch; see
+    ``trinity_sm100_gemm_batched_bf16``.  ``a`` is [batch, m, k] and ``out`` [batch, m, n], any
+    strides with a unit inner stride (so ``x.permute(1, 0, 2)`` of a [tokens, heads, k] tensor is
+    fine); ``b`` is [batch, k, n] or a shared [k, n]; ``bias`` is [batch, n] or a shared [n]."""
+    _require(a, torch.bfloat16, "a")
+    _require(b, torch.bfloat16, "b")
+    if a.dim() != 3 or b.dim() not in (2, 3) or a.shape[2] != b.shape[-2] or a.stride(2) != 1 or b.stride(-1) != 1:
+        raise ValueError("gemm_batched: a must be [batch,m,k], b [batch,k,n] or [k,n], unit inner strides")
+    batch, m, k = a.shape
+    n = b.shape[-1]
+    if b.dim() == 3 and b.shape[0] != batch:
+        raise ValueError("gemm_batched: a and b disagree on the batch")
+    if out is None:
+        out = torch.empty((batch, m, n), dtype=out_dtype, device=a.device)
+    if tuple(out.shape) != (batch, m, n) or out.stride(2) != 1 or out.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError("gemm_batched: out must be [batch,m,n] with a unit inner stride, bf16 or fp32")
+    args = GemmArgs()
+    args.a, args.b, args.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.m, args.n, args.k = m, n, k
+    args.lda, args.ldb, args.ldo = a.stride(1), b.stride(-2), out.stride(1)
+    args.activation = activation
+    args.out_dtype = DT_FP32 if out.dtype == torch.float32 else DT_BF16
+    how = GemmBatchArgs()
+    how.batch = batch
+    how.stride_a, how.stride_out = a.stride(0), out.stride(0)
+    how.stride_b = b.stride(0) if b.dim() == 3 else 0
+    if bias is not None:
+        _require(bias, torch.bfloat16, "bias")
+        if tuple(bias.shape) not in ((n,), (batch, n)) or bias.stride(-1) != 1:
+            raise ValueError("gemm_batched: bias must be [n] or [batch,n]")
+        args.bias = bias.data_ptr()
+        args.bias_mode = BIAS_COL_VECTOR
+        how.stride_bias = bias.stride(0) if bias.dim() == 2 else 0
+    with torch.cuda.device(a.device):
+        _check(library().trinity_sm100_gemm_batched_bf16(ctypes.byref(args), ctypes.byref(how), _stream(stream)))
     return out
 
 
