@@ -106,6 +106,34 @@ def test_full_size_properties(kernels):
     assert (flat.float() - const.float()).abs().max().item() <= 1.0 / 128
 
 
+def test_decode_between_its_per_head_projections(kernels):
+    """The whole latent-attention step of the reference's batched-MLA fixtures
+    (tests/fixtures/batched_mla/batched_mla_postprocessed_stage14.txt:19-68, 208-241): absorb
+    q_nope through W_DK per head straight into the query's latent columns, decode over the
+    compressed cache, project the result through W_DV per head.  Three launches, BF16 between
+    them; the oracle rounds at the same points."""
+    g = torch.Generator().manual_seed(2024)
+    batch, heads, seq = 4, 128, 640
+    q_nope = torch.randn(batch, heads, 128, generator=g).bfloat16()
+    q_rope = torch.randn(batch, heads, 64, generator=g).bfloat16()
+    w_dk = (torch.randn(heads, 128, 512, generator=g) / math.sqrt(128)).bfloat16()
+    w_dv = (torch.randn(heads, 512, 128, generator=g) / math.sqrt(512)).bfloat16()
+    cache = torch.randn(batch, seq, 576, generator=g).bfloat16()
+    q = torch.empty(batch, heads, 576, dtype=torch.bfloat16, device=DEV)
+    q[:, :, 512:] = q_rope.to(DEV)
+    kernels.gemm_batched(q_nope.to(DEV).permute(1, 0, 2), w_dk.to(DEV), out=q[:, :, :512].permute(1, 0, 2))
+    latent = kernels.mla_decode(q, cache.to(DEV), SCALE)
+    out = torch.empty(batch, heads, 128, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_batched(latent.permute(1, 0, 2), w_dv.to(DEV), out=out.permute(1, 0, 2))
+
+    absorbed = torch.einsum("bhk,hkn->bhn", q_nope.double(), w_dk.double()).float().bfloat16()
+    assert_close_bf16(q[:, :, :512].cpu(), absorbed, max_ulp=1, max_abs=2e-2)
+    assert torch.equal(q[:, :, 512:].cpu(), q_rope)          # the rope columns are untouched
+    expected_latent = wl.mla_oracle(torch.cat([absorbed, q_rope], dim=2), cache, SCALE, 512)
+    expected = torch.einsum("bhk,hkn->bhn", expected_latent.double(), w_dv.double()).float().bfloat16()
+    assert_close_bf16(out.cpu(), expected, max_ulp=None, max_abs=2e-2)
+
+
 def test_rejects_unsupported_geometry(kernels):
     q = torch.zeros(1, 128, 512, dtype=torch.bfloat16, device=DEV)
     c = torch.zeros(1, 64, 512, dtype=torch.bfloat16, device=DEV)
