@@ -429,22 +429,26 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     // tensor-pipe time, so one descriptor per operand kind is built per chunk and the K-steps
     // only add constants to its address field (units of 16 bytes; the field cannot overflow,
     // shared memory ends below 256 KB).
-    if (lane == 0) {
+    // The whole warp runs the loops (so that chunk counters, stage addresses and descriptors are
+    // warp-uniform values the compiler can keep in uniform registers, which is where the MMA
+    // instruction takes them from); lane 0 alone issues the MMAs and the commits.
+    {
       constexpr uint32_t kIdescQK = umma_idesc_bf16(128, kKv, 0, 0);
       const uint32_t d_scores = tmem_base + kColS, a_query = tmem_base + kColQ;
       TRINITY_MLA_ISSUER_DECL
       int g = 0;
       bool ok = true;
       for (int si = 0; ok && get_segment(p, si, seg); ++si) {
-        ok = mbar_wait(q_tmem, si & 1u, 0x502);
-        if (si == 0) { TRINITY_MLA_STAMP(8) }
+        ok = __all_sync(0xffffffffu, mbar_wait(q_tmem, si & 1u, 0x502));
+        if (si == 0 && lane == 0) { TRINITY_MLA_STAMP(8) }
         for (int j = 0; ok && j < seg.num_chunks; ++j, ++g) {
           TRINITY_MLA_ISSUER_TICK(3)
-          if (g > 0 && !mbar_wait(s_free, (g - 1) & 1u, 0x505)) { ok = false; break; }
+          if (g > 0) ok = __all_sync(0xffffffffu, mbar_wait(s_free, (g - 1) & 1u, 0x505));
           TRINITY_MLA_ISSUER_TICK(0)
-          if (!mbar_wait(kv_full(g % kKvStages), (g / kKvStages) & 1u, 0x503)) { ok = false; break; }
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(kv_full(g % kKvStages), (g / kKvStages) & 1u, 0x503));
+          if (!ok) break;
           TRINITY_MLA_ISSUER_TICK(1)
-          if (g == 0) { TRINITY_MLA_STAMP(2) }
+          if (g == 0 && lane == 0) { TRINITY_MLA_STAMP(2) }
           tc_fence_after();
           // 16 K-steps over the latent boxes and 2 over the rope box, the query always from TMEM
           const uint32_t stage = kv_smem + (g % kKvStages) * kStageBytes;
@@ -452,45 +456,56 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           const uint64_t rope = umma_smem_desc_sw64(stage + 4 * kBoxBytes, 512);
           const uint32_t latent_lo = uint32_t(latent), latent_hi = uint32_t(latent >> 32);
           const uint32_t rope_lo = uint32_t(rope), rope_hi = uint32_t(rope >> 32);
+          const uint32_t done_bar = s_full(g);
+          if (lane == 0) {
 #pragma unroll
-          for (int ks = 0; ks < 16; ++ks)
-            umma_bf16_ts_split(d_scores, a_query + ks * 8,
-                               latent_lo + (((ks / 4) * kBoxBytes + (ks % 4) * 32) >> 4), latent_hi,
-                               kIdescQK, ks != 0);
+            for (int ks = 0; ks < 16; ++ks)
+              umma_bf16_ts_split(d_scores, a_query + ks * 8,
+                                 latent_lo + (((ks / 4) * kBoxBytes + (ks % 4) * 32) >> 4), latent_hi,
+                                 kIdescQK, ks != 0);
 #pragma unroll
-          for (int r = 0; r < 2; ++r)
-            umma_bf16_ts_split(d_scores, a_query + 128 + r * 8, rope_lo + ((r * 32) >> 4), rope_hi,
-                               kIdescQK, 1u);
-          umma_commit(s_full(g));
+            for (int r = 0; r < 2; ++r)
+              umma_bf16_ts_split(d_scores, a_query + 128 + r * 8, rope_lo + ((r * 32) >> 4), rope_hi,
+                                 kIdescQK, 1u);
+            umma_commit(done_bar);
+          }
+          __syncwarp();
         }
       }
       TRINITY_MLA_ISSUER_TICK(3)
-      TRINITY_MLA_ISSUER_FLUSH
+      if (lane == 0) { TRINITY_MLA_ISSUER_FLUSH }
     }
   } else if (warp == 2 + kSoftmaxWarps) {
     // ------------------------------------------------------------ value MMA issuer
     // Probabilities from TMEM, the chunk's latent boxes N-major (64-latent boxes 8192 B apart,
-    // 8-position groups 1024 B apart).
-    if (lane == 0) {
+    // 8-position groups 1024 B apart).  Warp-uniform loops, lane 0 issues (see above).
+    {
       constexpr uint32_t kIdescPV = umma_idesc_bf16(128, 256, 0, 1);
       const uint32_t d_out = tmem_base + kColO, a_prob = tmem_base + kColP;
       int g = 0;
       bool ok = true;
       for (int si = 0; ok && get_segment(p, si, seg); ++si) {
         // the previous segment's accumulator must have been read before it is overwritten
-        if (si > 0) ok = mbar_wait(o_free, (si - 1) & 1u, 0x506);
+        if (si > 0) ok = __all_sync(0xffffffffu, mbar_wait(o_free, (si - 1) & 1u, 0x506));
         for (int j = 0; ok && j < seg.num_chunks; ++j, ++g) {
-          if (!mbar_wait(p_full, g & 1u, 0x504)) { ok = false; break; }
-          if (g == 0) { TRINITY_MLA_STAMP(3) }
-          if (j == seg.num_chunks - 1) { TRINITY_MLA_STAMP(4) }
+          ok = __all_sync(0xffffffffu, mbar_wait(p_full, g & 1u, 0x504));
+          if (!ok) break;
+          if (lane == 0) {
+            if (g == 0) { TRINITY_MLA_STAMP(3) }
+            if (j == seg.num_chunks - 1) { TRINITY_MLA_STAMP(4) }
+          }
           tc_fence_after();
           const int s = g % kKvStages;
           const uint64_t values = umma_smem_desc(kv_smem + s * kStageBytes, kBoxBytes, 1024);
+          const uint32_t free_bar = kv_empty(s), done_bar = pv_done(g);
+          if (lane == 0) {
 #pragma unroll
-          for (int ks = 0; ks < kKv / 16; ++ks)
-            umma_bf16_ts(d_out, a_prob + ks * 8, values + ((ks * 2048) >> 4), kIdescPV, (j | ks) != 0);
-          umma_commit(kv_empty(s));
-          umma_commit(pv_done(g));
+            for (int ks = 0; ks < kKv / 16; ++ks)
+              umma_bf16_ts(d_out, a_prob + ks * 8, values + ((ks * 2048) >> 4), kIdescPV, (j | ks) != 0);
+            umma_commit(free_bar);
+            umma_commit(done_bar);
+          }
+          __syncwarp();
         }
       }
     }
