@@ -238,6 +238,17 @@ TRINITY_SM100_API size_t trinity_sm100_mla_scratch_bytes(int32_t batch, int32_t 
                                        int32_t kv_splits);
 TRINITY_SM100_API int trinity_sm100_mla_default_splits(int32_t batch, int32_t seq);
 TRINITY_SM100_API int trinity_sm100_mla_balanced_slots(int32_t batch, int32_t seq);
+/*
+ * The launch schedule for (batch, seq, kv_splits), computed on the host without a launch:
+ *   info    = {balanced, clusters in grid y (equal splits: the split count), partial slots per
+ *              sequence, chunks of 64 positions per sequence}
+ *   segment = {sequence, first chunk, chunk count, partial slot, whole-sequence flag} of the
+ *             index-th piece of cluster (y, z); returns 1 if it exists, 0 if not.
+ * Every (sequence, chunk) belongs to exactly one piece.  For tools and tests.
+ */
+TRINITY_SM100_API int trinity_sm100_mla_schedule(int32_t batch, int32_t seq, int32_t kv_splits, int32_t* info);
+TRINITY_SM100_API int trinity_sm100_mla_schedule_segment(int32_t batch, int32_t seq, int32_t kv_splits, int32_t y,
+                                                         int32_t z, int32_t index, int64_t* segment);
 TRINITY_SM100_API int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void* stream);
 
 /*

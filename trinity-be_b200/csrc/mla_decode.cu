@@ -251,17 +251,18 @@ struct Segment {
   long long slot;
   bool whole;
 };
-// The i-th segment of this cluster; false when the cluster has no such segment.
-__device__ __forceinline__ bool get_segment(const MlaParams& p, int i, Segment& s) {
+// The i-th segment of the cluster with grid coordinates (y, z); false when it has no such segment.
+// Host and device: the host side serves trinity_sm100_mla_schedule_segment.
+__host__ __device__ inline bool segment_of(const MlaParams& p, int y, int z, int i, Segment& s) {
   if (p.balanced == 0) {
     if (i != 0) return false;
-    s.b = blockIdx.z;
-    split_range(p.chunks_per_seq, p.pieces, blockIdx.y, s.first_chunk, s.num_chunks);
-    s.slot = static_cast<long long>(s.b) * p.pieces + blockIdx.y;
+    s.b = z;
+    split_range(p.chunks_per_seq, p.pieces, y, s.first_chunk, s.num_chunks);
+    s.slot = static_cast<long long>(s.b) * p.pieces + y;
     s.whole = p.pieces == 1;
     return s.num_chunks > 0;
   }
-  const int k = blockIdx.y;
+  const int k = y;
   const long long u0 = unit_begin(p.units, p.clusters, k), u1 = unit_begin(p.units, p.clusters, k + 1);
   const long long cps = p.chunks_per_seq;
   const long long b = u0 / cps + i;
@@ -274,6 +275,9 @@ __device__ __forceinline__ bool get_segment(const MlaParams& p, int i, Segment& 
   s.slot = b * p.pieces + (k - cluster_of_unit(p.units, p.clusters, b * cps));
   s.whole = s.num_chunks == p.chunks_per_seq;
   return true;
+}
+__device__ __forceinline__ bool get_segment(const MlaParams& p, int i, Segment& s) {
+  return segment_of(p, blockIdx.y, blockIdx.z, i, s);
 }
 
 __global__ void __launch_bounds__(kMlaThreads, 1)
@@ -985,10 +989,61 @@ Schedule automatic_schedule(int batch, int seq, bool force_balanced) {
   return best;
 }
 
+// kv_splits > 0: that many equal splits of every sequence, one cluster each.
+// kv_splits == 0: the automatic schedule; < 0: the balanced schedule whatever the cost model says.
+Schedule choose_schedule(int batch, int seq, int kv_splits) {
+  if (kv_splits <= 0) return automatic_schedule(batch, seq, kv_splits < 0);
+  Schedule s;
+  const int chunks = (seq + kKv - 1) / kKv;
+  s.balanced = 0;
+  s.chunks_per_seq = chunks;
+  s.units = static_cast<long long>(batch) * chunks;
+  s.pieces = kv_splits > chunks ? chunks : kv_splits;
+  s.clusters = 0;
+  return s;
+}
+
 }  // namespace
 }  // namespace trinity_sm100
 
 using namespace trinity_sm100;
+
+// What trinity_sm100_mla_decode_bf16 will do for (batch, seq, kv_splits), without a launch:
+// info = {balanced, clusters (grid y), pieces (partial slots per sequence), chunks per sequence}.
+extern "C" int trinity_sm100_mla_schedule(int32_t batch, int32_t seq, int32_t kv_splits, int32_t* info) {
+  if (batch <= 0 || seq <= 0 || !info) return fail(TRINITY_SM100_E_INVALID, "mla_schedule: bad argument");
+  const Schedule s = choose_schedule(batch, seq, kv_splits);
+  info[0] = s.balanced;
+  info[1] = s.balanced ? s.clusters : s.pieces;
+  info[2] = s.pieces;
+  info[3] = s.chunks_per_seq;
+  return 0;
+}
+
+// The index-th piece of work of cluster (y, z) of that launch's grid (z is always 0 under the
+// balanced schedule): segment = {sequence, first chunk, chunk count, partial slot, whole}.
+// Returns 1 if the cluster has such a piece, 0 if not, a negative code on bad arguments.
+extern "C" int trinity_sm100_mla_schedule_segment(int32_t batch, int32_t seq, int32_t kv_splits, int32_t y,
+                                                  int32_t z, int32_t index, int64_t* segment) {
+  if (batch <= 0 || seq <= 0 || !segment || y < 0 || z < 0 || index < 0)
+    return fail(TRINITY_SM100_E_INVALID, "mla_schedule_segment: bad argument");
+  const Schedule s = choose_schedule(batch, seq, kv_splits);
+  if (y >= (s.balanced ? s.clusters : s.pieces) || z >= (s.balanced ? 1 : batch)) return 0;
+  MlaParams p = {};
+  p.chunks_per_seq = s.chunks_per_seq;
+  p.pieces = s.pieces;
+  p.balanced = s.balanced;
+  p.clusters = s.clusters;
+  p.units = s.units;
+  Segment piece;
+  if (!segment_of(p, y, z, index, piece)) return 0;
+  segment[0] = piece.b;
+  segment[1] = piece.first_chunk;
+  segment[2] = piece.num_chunks;
+  segment[3] = piece.slot;
+  segment[4] = piece.whole ? 1 : 0;
+  return 1;
+}
 
 extern "C" size_t trinity_sm100_mla_scratch_bytes(int32_t batch, int32_t heads, int32_t d_v,
                                                   int32_t kv_splits) {
@@ -1020,20 +1075,8 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   if (a.batch > 65535) return fail(TRINITY_SM100_E_UNSUPPORTED, "mla: batch above 65535");
   if (!aligned16(a.q) || !aligned16(a.cache) || !aligned16(a.out))
     return fail(TRINITY_SM100_E_INVALID, "mla: pointers must be 16-byte aligned");
-  // kv_splits > 0: that many equal splits of every sequence, one cluster each.
-  // kv_splits == 0: the automatic schedule; < 0: the balanced schedule whatever the cost model says.
-  const int chunks = (a.seq + kKv - 1) / kKv;
-  Schedule schedule;
-  if (a.kv_splits <= 0) {
-    schedule = automatic_schedule(a.batch, a.seq, a.kv_splits < 0);
-  } else {
-    schedule.balanced = 0;
-    schedule.chunks_per_seq = chunks;
-    schedule.units = static_cast<long long>(a.batch) * chunks;
-    schedule.pieces = a.kv_splits > chunks ? chunks : a.kv_splits;
-    schedule.clusters = 0;
-    if (schedule.pieces > 65535) return fail(TRINITY_SM100_E_UNSUPPORTED, "mla: too many splits");
-  }
+  const Schedule schedule = choose_schedule(a.batch, a.seq, a.kv_splits);
+  if (schedule.pieces > 65535) return fail(TRINITY_SM100_E_UNSUPPORTED, "mla: too many splits");
   const bool balanced = schedule.balanced != 0;
   const int splits = schedule.pieces;
   const size_t need = scratch_bytes(a.batch, a.heads, a.d_v, splits);

@@ -24,6 +24,8 @@ EXPORTS = (
     "trinity_sm100_mla_scratch_bytes",
     "trinity_sm100_mla_default_splits",
     "trinity_sm100_mla_balanced_slots",
+    "trinity_sm100_mla_schedule",
+    "trinity_sm100_mla_schedule_segment",
     "trinity_sm100_mla_decode_bf16",
     "trinity_sm100_mla_decode_bf16_noalloc",
     "trinity_sm100_allreduce_flag_words",
