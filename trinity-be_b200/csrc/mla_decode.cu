@@ -65,6 +65,9 @@ constexpr int kBoxBytes = kKv * 128;           // 8192: one [64 positions x 64 f
 constexpr int kRopeBoxBytes = kKv * 64;        // 4096: [64 positions x 32 rope features]
 constexpr int kStageBytes = 4 * kBoxBytes + kRopeBoxBytes;  // 36864
 constexpr int kXchgBytes = 128 * kKv * 2;      // one partial score tile in FP16: 16384
+constexpr int kQueryBoxBytes = 128 * 64;       // [128 heads x 32 features] of the query
+constexpr int kQueryLandingBytes = 9 * kQueryBoxBytes;   // eight latent boxes and the rope box
+static_assert(kQueryLandingBytes <= 2 * kStageBytes, "the query lands in two cache stages");
 // two receive tiles + two send tiles: the exchange of chunk j+1 overlaps the softmax of chunk j
 constexpr int kMlaSmem = 1024 + kKvStages * kStageBytes + 4 * kXchgBytes + 512;
 // TMEM columns: accumulator, scores, probabilities, query (128 latent + 16 rope word columns)
@@ -282,7 +285,8 @@ __device__ __forceinline__ bool get_segment(const MlaParams& p, int i, Segment& 
 
 __global__ void __launch_bounds__(kMlaThreads, 1)
 mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
-                  const __grid_constant__ CUtensorMap map_rope, const MlaParams p) {
+                  const __grid_constant__ CUtensorMap map_rope,
+                  const __grid_constant__ CUtensorMap map_query, const MlaParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ float m_shared[128];               // reference maximum of each head (log2 domain)
   __shared__ float l_part[kGroups * 128];       // [group][head] sums of probabilities at the end
@@ -320,8 +324,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   // m_ready[group][quadrant]: the reference maxima after chunk c are in m_shared (one arrival a
   // chunk, by the warp of group c % 3 that serves the quadrant)
   auto m_ready = [&](int c, int q) { return s_free + 32u + 8u * ((c % kGroups) * 4 + q); };
+  // q_land: the first segment's query has landed in shared memory (see the producer)
+  const uint32_t q_land = s_free + 32u + 8u * (4 * kGroups);
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(
-      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 4 + 2 * kGroups + 4 + 4 * kGroups));
+      xchg + 4 * kXchgBytes + 8 * (2 * kKvStages + 4 + 2 * kGroups + 5 + 4 * kGroups));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -348,10 +354,12 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     mbar_init(p_full, 4);
     mbar_init(q_tmem, kSoftmaxWarps);
     mbar_init(o_free, kSoftmaxWarps);
+    mbar_init(q_land, 1);
     for (int q = 0; q < 4 * kGroups; ++q) mbar_init(m_ready(q >> 2, q & 3), 1);
     mbar_fence_init();
     tma_prefetch_desc(&map_cache);
     tma_prefetch_desc(&map_rope);
+    tma_prefetch_desc(&map_query);
   }
   if (warp == 2) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
@@ -385,7 +393,17 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       };
       int g = 0;
       bool ok = true;
-      if (get_segment(p, 0, seg)) prefetch_query(seg);
+      // The first segment's query comes by TMA instead: nine [128 heads x 32 features] boxes
+      // (64-byte swizzle) into cache stages 1 and 2, which stay empty until the query has been
+      // moved on into tensor memory (see below).  That takes the query off the slow per-lane path
+      // exactly where nothing can hide it, at the start of the kernel.
+      if (get_segment(p, 0, seg)) {
+        mbar_arrive_expect_tx(q_land, kQueryLandingBytes);
+#pragma unroll
+        for (int i = 0; i < 9; ++i)
+          tma_load_3d(kv_smem + kStageBytes + i * kQueryBoxBytes, &map_query, q_land,
+                      i < 8 ? int(half) * 256 + i * 32 : kDv + int(half) * 32, 0, seg.b);
+      }
       for (int si = 0; ok && get_segment(p, si, seg); ++si) {
         {
           Segment next;
@@ -536,6 +554,27 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         // features and one of 32 rope features, dealt out to the groups.  (All MMAs of the
         // previous segment have completed: its epilogue waited for the last of them.)
         const uint32_t flip = p.negate ? 0x80008000u : 0u;
+        if (si == 0) {
+          // From the landing zone: box i holds features [32 i, 32 i + 32) of this CTA's half (box 8
+          // the rope features), one 64-byte row per head with its 16-byte units swizzled by
+          // (row >> 1) & 3; heads beyond p.heads were filled with zeros.  Group g takes boxes g,
+          // g + 3 and g + 6, each 16 columns of packed pairs.
+          if (!bad) bad = !mbar_wait(q_land, 0, 0x608);
+          const uint8_t* landing = smem + kStageBytes;
+#pragma unroll
+          for (int i = 0; i < 3; ++i) {
+            const int box = group + i * kGroups;
+            const uint8_t* src = landing + box * kQueryBoxBytes + row * 64;
+            uint32_t w[16];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const uint4 x = *reinterpret_cast<const uint4*>(src + ((v ^ ((row >> 1) & 3)) << 4));
+              w[v * 4 + 0] = x.x ^ flip; w[v * 4 + 1] = x.y ^ flip;
+              w[v * 4 + 2] = x.z ^ flip; w[v * 4 + 3] = x.w ^ flip;
+            }
+            tmem_st_32x32b_x16(lane_base + kColQ + (box < 8 ? box * 16 : 128), w);
+          }
+        } else {
         const __nv_bfloat16* qhead =
             p.q + (static_cast<long long>(seg.b) * p.heads + (live ? row : 0)) * kDqk;
         // Group g takes blocks g and g + 3; all loads are issued before the first is used.
@@ -570,6 +609,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
             for (int k = 0; k < 16; ++k) r[k] = w[k];
             tmem_st_32x32b_x16(lane_base + kColQ + 128, r);
           }
+        }
         }
         tmem_st_wait();
         tc_fence_before();
@@ -1109,6 +1149,10 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   if ((rc = make_tensor_map_3d(&map_rope, a.cache, 2, kDqk, a.seq, a.batch, kDqk * 2ull,
                                uint64_t(a.seq) * kDqk * 2, 32, kKv, 1, 64)))
     return rc;
+  CUtensorMap map_query;
+  if ((rc = make_tensor_map_3d(&map_query, a.q, 2, kDqk, a.heads, a.batch, kDqk * 2ull,
+                               uint64_t(a.heads) * kDqk * 2, 32, 128, 1, 64)))
+    return rc;
   MlaParams p;
   p.q = static_cast<const __nv_bfloat16*>(a.q);
   p.out = static_cast<__nv_bfloat16*>(a.out);
@@ -1142,7 +1186,7 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   cluster.val.clusterDim.z = 1;
   config.attrs = &cluster;
   config.numAttrs = 1;
-  cudaError_t launch_error = cudaLaunchKernelEx(&config, mla_decode_kernel, map_cache, map_rope, p);
+  cudaError_t launch_error = cudaLaunchKernelEx(&config, mla_decode_kernel, map_cache, map_rope, map_query, p);
   if (launch_error != cudaSuccess)
     return fail(TRINITY_SM100_E_CUDA, "mla_decode launch: %s", cudaGetErrorString(launch_error));
   count_launch();
