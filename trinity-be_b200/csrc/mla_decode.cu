@@ -67,7 +67,7 @@ constexpr int kStageBytes = 4 * kBoxBytes + kRopeBoxBytes;  // 36864
 constexpr int kXchgBytes = 128 * kKv * 2;      // one partial score tile in FP16: 16384
 constexpr int kQueryBoxBytes = 128 * 64;       // [128 heads x 32 features] of the query
 constexpr int kQueryLandingBytes = 9 * kQueryBoxBytes;   // eight latent boxes and the rope box
-static_assert(kQueryLandingBytes <= 2 * kStageBytes, "the query lands in two cache stages");
+static_assert(kQueryLandingBytes <= 2 * kStageBytes && kKvStages >= 4, "the query lands in cache stages 2 and 3");
 // two receive tiles + two send tiles: the exchange of chunk j+1 overlaps the softmax of chunk j
 constexpr int kMlaSmem = 1024 + kKvStages * kStageBytes + 4 * kXchgBytes + 512;
 // TMEM columns: accumulator, scores, probabilities, query (128 latent + 16 rope word columns)
@@ -394,14 +394,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       int g = 0;
       bool ok = true;
       // The first segment's query comes by TMA instead: nine [128 heads x 32 features] boxes
-      // (64-byte swizzle) into cache stages 1 and 2, which stay empty until the query has been
+      // (64-byte swizzle) into cache stages 2 and 3, which stay empty until the query has been
       // moved on into tensor memory (see below).  That takes the query off the slow per-lane path
       // exactly where nothing can hide it, at the start of the kernel.
       if (get_segment(p, 0, seg)) {
         mbar_arrive_expect_tx(q_land, kQueryLandingBytes);
 #pragma unroll
         for (int i = 0; i < 9; ++i)
-          tma_load_3d(kv_smem + kStageBytes + i * kQueryBoxBytes, &map_query, q_land,
+          tma_load_3d(kv_smem + 2 * kStageBytes + i * kQueryBoxBytes, &map_query, q_land,
                       i < 8 ? int(half) * 256 + i * 32 : kDv + int(half) * 32, 0, seg.b);
       }
       for (int si = 0; ok && get_segment(p, si, seg); ++si) {
@@ -423,11 +423,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           // Requests into L2 run a fixed distance ahead of the ring's loads, and never ahead of
           // the loads that fill the empty ring at the start: those must not queue behind them.
           if (j >= kKvStages) prefetch_chunk(j + kPrefetchAhead);
-          // At the start of the kernel every CTA asks for its query and its whole ring at once, and
-          // the query, which the first scores wait for, would queue behind the ring's loads for
-          // several microseconds.  So the first chunk goes out alone; the rest follows once the
-          // query has arrived.
-          if (g == 1 && !mbar_wait(q_tmem, 0, 0x402)) { ok = false; break; }
+          // Stages 2 and 3 hold the first segment's query until it has been moved into tensor
+          // memory; the third chunk's load waits for that.  (It also keeps the start of the kernel,
+          // where every CTA asks for its query and its ring at once, from queueing the query
+          // behind the whole ring.)
+          if (g == 2 && !mbar_wait(q_tmem, 0, 0x402)) { ok = false; break; }
           if (!mbar_wait(kv_empty(s), phase ^ 1u, 0x401)) { ok = false; break; }
           mbar_arrive_expect_tx(kv_full(s), kStageBytes);
           const int kv0 = (seg.first_chunk + j) * kKv;
@@ -560,7 +560,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           // (row >> 1) & 3; heads beyond p.heads were filled with zeros.  Group g takes boxes g,
           // g + 3 and g + 6, each 16 columns of packed pairs.
           if (!bad) bad = !mbar_wait(q_land, 0, 0x608);
-          const uint8_t* landing = smem + kStageBytes;
+          const uint8_t* landing = smem + 2 * kStageBytes;
 #pragma unroll
           for (int i = 0; i < 3; ++i) {
             const int box = group + i * kGroups;
