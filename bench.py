@@ -40,7 +40,7 @@ NCU_TRAFFIC_BYTES = {
     "gemm_bias_1024": None,
     "rmsnorm": 4.84e8,
     "softmax": 4.83e8,
-    "mla": 3.17e8,
+    "mla": 3.15e8,
     "mla_batch_sharded": None,
     "tp_mlp": None,
     "tp_mlp_unfused": None,
