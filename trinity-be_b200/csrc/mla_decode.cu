@@ -586,11 +586,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
                                                                     : qhead + kDv + half * 32);
 #pragma unroll
           for (int v = 0; v < 8; ++v)
-#ifdef TRINITY_MLA_SKIP_QUERY_LOADS
-            x[i][v] = make_uint4(0x3c003c00u, 0x3c003c00u, uint32_t(reinterpret_cast<uintptr_t>(src)), 0);
-#else
             x[i][v] = (live && blk < 5 && (blk < 4 || v < 4)) ? __ldg(src + v) : make_uint4(0, 0, 0, 0);
-#endif
         }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
