@@ -7,6 +7,7 @@ in a CUDA Graph; one step = one graph replay.  Inputs are synthetic and seeded.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload gemm_relu|gemm_bias_1024|rmsnorm|softmax|mla|mla_batch_sharded|
+                                gemm_decode_square|gemm_decode_up|gemm_decode_down|
                                 tp_mlp|tp_mlp_unfused|tp_mlp_noreduce]
 
 Prints one JSON line (rank 0).  With N > 1 (launched under torch.distributed.run) the GEMM,
@@ -42,6 +43,9 @@ NCU_TRAFFIC_BYTES = {
     "softmax": 4.83e8,
     "mla": 3.15e8,
     "mla_batch_sharded": None,
+    "gemm_decode_square": None,
+    "gemm_decode_up": None,
+    "gemm_decode_down": None,
     "tp_mlp": None,
     "tp_mlp_unfused": None,
     "tp_mlp_noreduce": None,
@@ -245,6 +249,42 @@ def make_workload(name, device, world=None):
                 wl.softmax_oracle(sample)
             dt = time.perf_counter() - t0
             return sample.numel() * 4 / 1e9 / dt, "4096 of 32768 rows, CPU oracle (FP32 torch)", dt
+
+    elif name in ("gemm_decode_square", "gemm_decode_up", "gemm_decode_down"):
+        # Decode-time GEMMs: 16 tokens against a large weight, which the kernel streams once.
+        m = 16
+        kk, n = {"gemm_decode_square": (8192, 8192), "gemm_decode_up": (8192, 28672),
+                 "gemm_decode_down": (28672, 8192)}[name]
+        a, wt, _ = wl.gemm_inputs(m, n, kk, 1240, "normal")
+        w.label = f"gemm A[16,{kk}]@W[{kk},{n}] bf16 (decode-time shape)"
+        w.metric, w.unit, w.bound, w.dtype = "gemm_decode_hbm_gbs", "GB/s", "hbm", "bf16"
+        w.alg_bytes = (m * kk + kk * n + m * n) * 2
+        w.work = w.alg_bytes / 1e9
+        host_a, host_w = pin(a), pin(wt)
+        ad, wd = a.to(device), wt.to(device)
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+        host_out = pin(torch.empty((m, n), dtype=torch.bfloat16))
+        w.kernels_per_step = 1
+        w.l2_note, w.flush = "inputs larger than L2", False
+
+        def device_step():
+            k.gemm(ad, wd, out=out)
+
+        def e2e_step():
+            ad.copy_(host_a, non_blocking=True)
+            wd.copy_(host_w, non_blocking=True)
+            device_step()
+            host_out.copy_(out, non_blocking=True)
+
+        w.h2d, w.d2h = (a.numel() + wt.numel()) * 2, out.numel() * 2
+
+        def cpu_sample(threads, budget_s):
+            torch.set_num_threads(threads)
+            af, wf = a.float(), wt.float()
+            t0 = time.perf_counter()
+            (af @ wf).bfloat16()
+            dt = time.perf_counter() - t0
+            return w.alg_bytes / 1e9 / dt, "whole GEMM, torch CPU FP32 matmul", dt
 
     elif name in ("mla", "mla_batch_sharded"):
         batch, heads, seq, d_qk, d_v = 64, 128, 4096, 576, 512
