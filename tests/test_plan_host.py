@@ -394,3 +394,33 @@ def test_package_keeps_the_reference_names():
     for refused in (tl.emit_python, tl.emit_triton, tl.lower_triton, tl.TritonProgram):
         with pytest.raises(NotImplementedError):
             refused(None)
+
+
+def test_text_reader_grammar_and_located_errors():
+    """Comments to end of line, located errors with a byte offset, arity of `seq`, the nesting
+    limit, ranks 1-3 only, unknown operators; loop variables are renamed, so spelling them
+    differently gives the same plan (the reader rules of src/analysis/ir/syntax.rs:82-143 and
+    src/analysis/plan/ir.rs:447,503 in the reference)."""
+    base = ("(ploop 0 256 128 c (store (view (output Y) (layout (axis a 256))) (relu (load (view (input X) "
+            "(layout (axis a 256))) (keyed_index (slot a (tile c 128))))) (keyed_index (slot a (tile c 128)))))")
+    dtypes = {"X": "bf16", "Y": "bf16"}
+    (plan,) = tl.lower_ir("; a comment line\n" + base + " ; trailing comment", {}, dtypes)
+    renamed = base.replace("128 c (store", "128 col (store").replace("tile c 128", "tile col 128")
+    assert plan.same_body(tl.lower_ir(renamed, {}, dtypes)[0])
+    assert not plan.same_body(tl.lower_ir(base.replace("relu", "sqrt"), {}, dtypes)[0])
+    domain = json.loads(plan.metadata_json())["statements"][0]["loop"]["domain"]
+    assert domain == {"variable": "lv0", "start": {"Constant": 0}, "stop": {"Constant": 256}, "step": {"Constant": 128}}
+    rank4 = ("(ploop 0 4 1 c (store (view (output Y) (layout (axis a 4) (axis b 2) (axis c 2) (axis d 2))) (load "
+             "(view (input X) (layout (axis a 4) (axis b 2) (axis c 2) (axis d 2))) (keyed_index (slot a (elem c)) "
+             "(slot b fulltile) (slot c fulltile) (slot d fulltile))) (keyed_index (slot a (elem c)) (slot b fulltile) "
+             "(slot c fulltile) (slot d fulltile))))")
+    for text, fragment in ((base + " (extra)", "unexpected trailing input"),
+                           (base[:-1], "unclosed expression"),
+                           ("(" * 300 + ")" * 300, "nesting exceeds 256"),
+                           (f"(seq {base} {base} {base})", "'seq' expects 2 arguments"),
+                           (base.replace("relu", "tanh"), "unsupported operation tanh"),
+                           (rank4, "supported tensor ranks are 1, 2, 3")):
+        with pytest.raises(ValueError, match=fragment + ".* at byte"):
+            tl.lower_ir(text, {}, dtypes)
+    with pytest.raises(ValueError, match="missing dtype"):
+        tl.lower_ir(base, {}, {"X": "bf16"})
