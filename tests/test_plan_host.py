@@ -424,3 +424,31 @@ def test_text_reader_grammar_and_located_errors():
             tl.lower_ir(text, {}, dtypes)
     with pytest.raises(ValueError, match="missing dtype"):
         tl.lower_ir(base, {}, {"X": "bf16"})
+
+
+def test_text_reader_rejects_hazards_where_the_reference_does():
+    """Reader-level rejections with the reference's message fragments (tests/streamed.rs:183-190,
+    tests/ir.rs:52-63, src/analysis/storage/mod.rs:303-312, :352-363 there): parallel work inside
+    a sequential loop, a write that a parallel loop does not index, a read beyond what earlier
+    kernels wrote.  A write of a loop-invariant value to an un-indexed location is allowed."""
+    def view(kind, name):
+        return f"(view ({kind} {name}) (layout (axis a 256)))"
+    tile, half, full = ("(keyed_index (slot a (tile c 128)))", "(keyed_index (slot a (tile c 64)))",
+                        "(keyed_index (slot a fulltile))")
+    dtypes = {"X": "bf16", "Y": "bf16", "T": "fp32"}
+
+    def produce(index, stop=256):
+        return f"(ploop 0 {stop} 128 c (store {view('tensor', 'T')} (sqr (load {view('input', 'X')} {index})) {index}))"
+    consume = f"(ploop 0 256 128 c (store {view('output', 'Y')} (relu (load {view('tensor', 'T')} {tile})) {tile}))"
+    (plan,) = tl.lower_ir(f"(seq {produce(tile)} {consume})", {}, dtypes)
+    assert [v["storage"] for v in json.loads(plan.metadata_json())["values"]] == ["external", "global", "external"]
+    for text, fragment in (
+            (f"(seq {produce(tile, stop=128)} {consume})", "not covered"),
+            (f"(seq {produce(half)} {consume})", "not covered"),          # 64-wide tiles every 128: gaps
+            (f"(ploop 0 256 128 c (store {view('output', 'Y')} (relu (load {view('input', 'X')} {tile})) {full}))",
+             "not proven disjoint"),
+            (f"(sloop 0 256 128 k {consume.replace('tensor', 'input').replace(' T)', ' X)')})", "parallel work inside")):
+        with pytest.raises(ValueError, match=fragment + ".* at byte [1-9]"):
+            tl.lower_ir(text, {}, dtypes)
+    invariant = f"(ploop 0 256 128 c (store {view('output', 'Y')} (relu (load {view('input', 'X')} {full})) {full}))"
+    assert len(tl.lower_ir(invariant, {}, dtypes)) == 1

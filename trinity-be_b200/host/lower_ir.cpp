@@ -7,6 +7,14 @@
 // written tensor touched by one top-level kernel only and always through the same index and
 // view lives in a Register; every other tensor is Global.  mloop (split loops) are not read:
 // the native provider rejects them anyway (src/emit/native/mod.rs:174-185).
+//
+// Three of the reference reader's rejections are restated with their message fragments
+// (src/analysis/storage/mod.rs:303-312, :352-363; tests/streamed.rs:183-190, tests/ir.rs:52-63
+// there): a parallel loop inside a sequential one ("parallel work inside"), a write to memory
+// that an enclosing parallel loop does not index although the value depends on the loop ("not
+// proven disjoint"), and a read of an intermediate tensor beyond what earlier kernels wrote
+// ("not covered").  The interval reasoning is per axis over tile / elem / fulltile indices with
+// numeric loop bounds; any other index form is taken as covering.
 #include <functional>
 
 #include "plan.hpp"
@@ -15,6 +23,26 @@ namespace trinity::host {
 
 namespace {
 
+struct LoopScope {
+  std::string variable;
+  bool parallel = false, numeric = false;
+  int64_t start = 0, stop = 0, step = 1;
+};
+
+// One load or store as the reader saw it: which elements it can touch, per axis, as a half-open
+// interval (exact = the interval is touched without gaps).
+struct AccessRecord {
+  int kernel = 0;
+  bool write = false;
+  size_t offset = 0;
+  bool known = true;                           // false: an index form the interval reasoning skips
+  std::vector<std::pair<int64_t, int64_t>> range;
+  bool exact = true;
+  std::set<std::string> index_variables;       // loop variables the index mentions
+  std::vector<std::string> unindexed_parallel; // enclosing parallel loops the index does not mention
+  bool value_depends_on_unindexed = false;     // (writes) the stored value mentions one of those
+};
+
 struct TensorInfo {
   std::string role;            // input | output | tensor
   std::vector<int64_t> shape;  // first view seen = base shape
@@ -22,7 +50,16 @@ struct TensorInfo {
   std::set<std::string> regions;  // distinct (view, index) spellings
   bool written = false;
   int value = -1;
+  std::vector<AccessRecord> accesses;
 };
+
+void atoms_of(const Node& n, std::set<std::string>& out) {
+  if (n.is_atom) {
+    out.insert(n.text);
+    return;
+  }
+  for (auto& c : n.children) atoms_of(c, out);
+}
 
 std::string spelling(const Node& n) {
   if (n.is_atom) return n.text;
@@ -61,11 +98,41 @@ struct Reader {
     }
   }
 
+  std::vector<LoopScope> loops;   // enclosing loops of the node being collected, outermost first
+
   void collect(const Node& n, int kernel, bool is_store_destination) {
     if (n.is_atom) return;
+    if (n.op() == "ploop" || n.op() == "sloop") {
+      const auto& a = n.args(5);
+      LoopScope scope;
+      scope.variable = a[3].atom();
+      scope.parallel = n.op() == "ploop";
+      if (scope.parallel)
+        for (auto& outer : loops)
+          if (!outer.parallel)
+            throw SyntaxError(n.offset, "parallel work inside a sequential loop (" + outer.variable + ") is not supported");
+      try {
+        scope.start = number(a[0]);
+        scope.stop = number(a[1]);
+        scope.step = number(a[2]);
+        scope.numeric = scope.step > 0;
+      } catch (const SyntaxError&) {
+        scope.numeric = false;   // bounds that are expressions or unbound symbols: no interval reasoning
+      }
+      loops.push_back(scope);
+      collect(a[4], kernel, false);
+      loops.pop_back();
+      return;
+    }
     if (n.op() == "store") {
       const auto& a = n.args(3);
-      note_access(a[0], a[2], kernel, true);
+      AccessRecord* record = note_access(a[0], a[2], kernel, true);
+      if (record && !record->unindexed_parallel.empty()) {
+        std::set<std::string> mentioned;
+        atoms_of(a[1], mentioned);
+        for (auto& v : record->unindexed_parallel)
+          if (mentioned.count(v)) record->value_depends_on_unindexed = true;
+      }
       collect(a[1], kernel, false);
       return;
     }
@@ -78,7 +145,46 @@ struct Reader {
     for (auto& c : n.children) collect(c, kernel, false);
   }
 
-  void note_access(const Node& view, const Node& index, int kernel, bool write) {
+  // The interval of one axis that an index form can touch under the enclosing loops.
+  void axis_range(const Node& form, int64_t extent, AccessRecord& r) {
+    auto clip = [&](int64_t lo, int64_t hi) {
+      r.range.emplace_back(lo < 0 ? 0 : lo, hi > extent ? extent : hi);
+    };
+    if (form.is_atom) {
+      if (form.text == "fulltile") clip(0, extent);
+      else { r.known = false; r.range.emplace_back(0, extent); }
+      return;
+    }
+    const std::string& kind = form.op();
+    if (kind != "tile" && kind != "clipped_tile" && kind != "elem") {
+      r.known = false;
+      r.range.emplace_back(0, extent);
+      return;
+    }
+    const std::string& variable = form.children.at(0).atom();
+    r.index_variables.insert(variable);
+    int64_t width = 1;
+    if (kind != "elem") {
+      try {
+        width = number(form.children.at(1));
+      } catch (const SyntaxError&) {
+        r.known = false;
+      }
+    }
+    const LoopScope* loop = nullptr;
+    for (auto& l : loops)
+      if (l.variable == variable) loop = &l;
+    if (!loop || !loop->numeric || !r.known || loop->stop <= loop->start) {
+      r.known = false;
+      r.range.emplace_back(0, extent);
+      return;
+    }
+    const int64_t last = loop->start + (loop->stop - 1 - loop->start) / loop->step * loop->step;
+    if (loop->step > width) r.exact = false;   // gaps between the tiles
+    clip(loop->start, last + width);
+  }
+
+  AccessRecord* note_access(const Node& view, const Node& index, int kernel, bool write) {
     if (view.is_atom || view.op() != "view") throw SyntaxError(view.offset, "expected view");
     const auto& v = view.args(2);
     const std::string role = v[0].is_atom ? "" : v[0].op();
@@ -109,6 +215,59 @@ struct Reader {
     it->second.kernels.insert(kernel);
     it->second.regions.insert(spelling(v[1]) + spelling(index));
     it->second.written |= write;
+    // interval record: slots are keyed by axis name
+    AccessRecord record;
+    record.kernel = kernel;
+    record.write = write;
+    record.offset = view.offset;
+    if (index.is_atom || index.op() != "keyed_index" || index.children.size() != v[1].children.size()) {
+      record.known = false;
+    } else {
+      for (size_t axis = 0; axis < v[1].children.size() && record.known; ++axis) {
+        const std::string& axis_name = v[1].children[axis].children.at(0).atom();
+        const Node* form = nullptr;
+        for (auto& slot : index.children)
+          if (!slot.is_atom && slot.op() == "slot" && slot.children.size() == 2 && slot.children[0].is_atom &&
+              slot.children[0].text == axis_name)
+            form = &slot.children[1];
+        if (!form) { record.known = false; break; }
+        axis_range(*form, shape[axis], record);
+      }
+    }
+    for (auto& l : loops)
+      if (l.parallel && !record.index_variables.count(l.variable)) record.unindexed_parallel.push_back(l.variable);
+    it->second.accesses.push_back(record);
+    return &it->second.accesses.back();
+  }
+
+  // The reader-level rejections that need the whole program (see the head of this file).
+  void check_hazards(const std::string& name, const TensorInfo& t, bool in_register) const {
+    if (in_register) return;
+    for (auto& a : t.accesses) {
+      if (a.write && a.known && a.value_depends_on_unindexed)
+        throw SyntaxError(a.offset, "write to " + name + " is not proven disjoint across parallel loop " +
+                                        a.unindexed_parallel.front());
+    }
+    if (t.role == "input") return;
+    for (auto& read : t.accesses) {
+      if (read.write || !read.known) continue;
+      bool produced_here = false, covered = false, any_earlier = false;
+      for (auto& w : t.accesses) {
+        if (!w.write) continue;
+        if (w.kernel == read.kernel) produced_here = true;
+        if (w.kernel >= read.kernel) continue;
+        any_earlier = true;
+        if (!w.known) { covered = true; break; }
+        if (!w.exact || w.range.size() != read.range.size()) continue;
+        bool inside = true;
+        for (size_t axis = 0; axis < w.range.size(); ++axis)
+          if (read.range[axis].first < w.range[axis].first || read.range[axis].second > w.range[axis].second) inside = false;
+        if (inside) { covered = true; break; }
+      }
+      if (produced_here || covered) continue;   // accumulators and in-kernel values are the planner's business
+      if (any_earlier)
+        throw SyntaxError(read.offset, "read of " + name + " is not covered by the writes of earlier kernels");
+    }
   }
 };
 
@@ -123,7 +282,7 @@ std::vector<PhysicalPlan> lower_ir(const std::string& text, const std::map<std::
     invalid(e.what());
   }
   try {
-    Reader reader{symbols, dtypes, {}, {}};
+    Reader reader{symbols, dtypes, {}, {}, {}};
     std::vector<const Node*> kernels;
     reader.flatten(root, kernels);
     for (size_t k = 0; k < kernels.size(); ++k) reader.collect(*kernels[k], int(k), false);
@@ -138,6 +297,7 @@ std::vector<PhysicalPlan> lower_ir(const std::string& text, const std::map<std::
       Storage storage = Storage::Global;
       if (t.role == "input" || t.role == "output") storage = Storage::External;
       else if (t.written && t.kernels.size() == 1 && t.regions.size() == 1) storage = Storage::Register;
+      reader.check_hazards(name, t, storage == Storage::Register);
       t.value = builder.add_value(parse_dtype(dt->second), t.shape, storage, name);
       if (t.role == "input") builder.bind_input(name, t.value);
       if (t.role == "output") {
