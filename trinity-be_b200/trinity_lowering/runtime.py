@@ -41,31 +41,36 @@ class _Native:
 
 
 def device_of(device, target="sm100"):
+    """The execution device as a torch.device with an index; it must be a CUDA device of the
+    compute capability the artifact was built for."""
     import torch
-    d = torch.device(device)
-    if d.type != "cuda":
+    chosen = torch.device(device)
+    if chosen.type != "cuda":
         raise ValueError("a CUDA device is required")
-    if d.index is None:
-        d = torch.device("cuda", torch.cuda.current_device())
-    if target not in TARGET_CAPABILITIES:
+    if chosen.index is None:
+        chosen = torch.device("cuda", torch.cuda.current_device())
+    capability = TARGET_CAPABILITIES.get(target)
+    if capability is None:
         raise ValueError("unsupported artifact target")
-    if torch.cuda.get_device_capability(d) != TARGET_CAPABILITIES[target]:
+    if tuple(torch.cuda.get_device_capability(chosen)) != capability:
         raise ValueError(f"this artifact requires a {target} device")
-    return d
+    return chosen
 
 
 def stream_of(device, stream=None, wait_for=()):
+    """The stream a launch goes to (the current one by default), after making it wait for the
+    caller's events."""
     import torch
-    if stream is None:
-        stream = torch.cuda.current_stream(device)
-    if not isinstance(stream, torch.cuda.Stream) or stream.device != device:
+    chosen = torch.cuda.current_stream(device) if stream is None else stream
+    if not (isinstance(chosen, torch.cuda.Stream) and chosen.device == device):
         raise ValueError("stream must be a torch.cuda.Stream on the execution device")
-    events = tuple(wait_for)
-    if any(not isinstance(e, torch.cuda.Event) for e in events):
-        raise ValueError("wait_for must contain recorded CUDA events on the execution device")
-    for event in events:
-        stream.wait_event(event)
-    return stream
+    pending = list(wait_for)
+    for event in pending:
+        if not isinstance(event, torch.cuda.Event):
+            raise ValueError("wait_for must contain recorded CUDA events on the execution device")
+    for event in pending:
+        chosen.wait_event(event)
+    return chosen
 
 
 def tensor_check(tensor, b, device, world=None):
@@ -73,39 +78,53 @@ def tensor_check(tensor, b, device, world=None):
     import torch
     if not isinstance(tensor, torch.Tensor):
         raise TypeError(f"binding {b.value} requires a Tensor")
-    if (tensor.device != device or tensor.layout != torch.strided
-            or tensor.dtype != getattr(torch, _TORCH_DTYPE[b.dtype])
-            or tuple(tensor.shape) != b.shape or tuple(tensor.stride()) != b.strides):
+    wanted = getattr(torch, _TORCH_DTYPE[b.dtype])
+    layout_ok = (tensor.layout == torch.strided and tuple(tensor.shape) == b.shape
+                 and tuple(tensor.stride()) == b.strides)
+    if not (layout_ok and tensor.dtype == wanted and tensor.device == device):
         raise ValueError(f"binding {b.value}: dtype/shape/stride/device mismatch")
-    if torch.is_grad_enabled() and tensor.requires_grad:
+    if tensor.requires_grad and torch.is_grad_enabled():
         raise ValueError("use no_grad or inference_mode for gradient Tensors")
-    available = tensor.untyped_storage().nbytes() - tensor.storage_offset() * tensor.element_size()
-    if tensor.data_ptr() % b.alignment or available < b.bytes:
+    behind = tensor.untyped_storage().nbytes() - tensor.storage_offset() * tensor.element_size()
+    if behind < b.bytes or tensor.data_ptr() % b.alignment != 0:
         raise ValueError(f"binding {b.value}: alignment/storage mismatch")
-    if b.symmetric and world is None:
+    if world is None and b.symmetric:
         raise ValueError(f"binding {b.value} requires this world's symmetric allocation")
 
 
+def _overlapping(first, second):
+    (a0, a_len), (b0, b_len) = first, second
+    return a0 < b0 + b_len and b0 < a0 + a_len
+
+
 def resolve_bindings(req, inputs, out, device, world=None, allow_missing=False):
+    """Maps buffer slots to the caller's tensors: every input name must be known (and, unless
+    ``allow_missing``, present), aliases of one value must be one region, distinct values must not
+    overlap."""
     if not isinstance(inputs, Mapping):
         raise TypeError("inputs must be a mapping of binding names to Tensors")
-    names = {name for b in req.buffers for name in b.input_names}
-    if set(inputs) - names or (not allow_missing and set(inputs) != names):
-        raise ValueError(f"expected exactly input names {sorted(names)}")
+    known = set()
+    for requirement in req.buffers:
+        known.update(requirement.input_names)
+    given = set(inputs)
+    if not given <= known or (given != known and not allow_missing):
+        raise ValueError(f"expected exactly input names {sorted(known)}")
     bound = {}
-    for b in req.buffers:
-        candidates = [inputs[name] for name in b.input_names if name in inputs]
-        if b.output_name is not None and out is not None:
-            candidates.append(out)
-        for tensor in candidates:
-            tensor_check(tensor, b, device, world)
-        if candidates:
-            if any(t.data_ptr() != candidates[0].data_ptr() for t in candidates[1:]):
-                raise ValueError("names referring to the same value must share one Tensor region")
-            bound[b.value] = candidates[0]
-    regions = [(t.data_ptr(), req.buffers[i].bytes) for i, t in bound.items()]
-    for i, (address, length) in enumerate(regions):
-        if any(address < other + size and other < address + length for other, size in regions[:i]):
+    for requirement in req.buffers:
+        tensors = [inputs[name] for name in requirement.input_names if name in inputs]
+        if out is not None and requirement.output_name is not None:
+            tensors.append(out)
+        if not tensors:
+            continue
+        for tensor in tensors:
+            tensor_check(tensor, requirement, device, world)
+        first = tensors[0]
+        if any(other.data_ptr() != first.data_ptr() for other in tensors[1:]):
+            raise ValueError("names referring to the same value must share one Tensor region")
+        bound[requirement.value] = first
+    spans = [(tensor.data_ptr(), req.buffers[slot].bytes) for slot, tensor in bound.items()]
+    for position, span in enumerate(spans):
+        if any(_overlapping(span, earlier) for earlier in spans[:position]):
             raise ValueError("different canonical values overlap")
     return bound
 
