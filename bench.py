@@ -1,21 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the native-provider hot path on B200.
 
-Default workload (the configuration the headline metric is quoted on): GEMM + bias + ReLU,
-A[8192,8192] @ W[8192,8192] + bias[8192], BF16 in / FP32 accumulate / BF16 out, captured once
-in a CUDA Graph; one step = one graph replay.  Inputs are synthetic and seeded.
+Default workload at every GPU count: the tensor-parallel SwiGLU MLP
+Y = (silu(X Wg) * (X Wu)) Wd with X[16384,8192], Wg/Wu[8192,28672] column-sharded and
+Wd[28672,8192] row-sharded over the GPUs, BF16 in / FP32 accumulate / BF16 out.  One step = one
+forward pass: the gated GEMM and the row-parallel down GEMM whose epilogue sums the partial
+outputs across GPUs over NVLink peer memory (one GPU: the same two GEMMs without an exchange).
+Total work is fixed, so the scaling is strong.  Inputs are synthetic and seeded.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload gemm_relu|gemm_bias_1024|rmsnorm|softmax|mla|mla_batch_sharded|
-                                gemm_decode_square|gemm_decode_up|gemm_decode_down|
-                                tp_mlp|tp_mlp_unfused|tp_mlp_noreduce]
+                    [--workload tp_mlp|tp_mlp_unfused|tp_mlp_noreduce|gemm_relu|gemm_bias_1024|
+                                rmsnorm|softmax|mla|mla_batch_sharded|
+                                gemm_decode_square|gemm_decode_up|gemm_decode_down]
+                    [--no-configs] [--no-cpu-baseline] [--no-graph]
 
-Prints one JSON line (rank 0).  With N > 1 (launched under torch.distributed.run) the GEMM,
-RMSNorm and softmax workloads run an independent replica on every GPU ("replicas only": the
-path has no exchange step); `mla` shards the heads and `mla_batch_sharded` the sequences over
-the ranks, again without an exchange; the `tp_mlp*` workloads shard a SwiGLU MLP N ways with
-the sum all-reduce over NVLink peer memory.  Timing is the maximum over ranks and `value` is
-the aggregate.
+Prints one JSON line (rank 0).  With the default workload the line also carries a "configs" block:
+on one GPU the other benchmark configurations (GEMM+bias 1024^3, GEMM+bias+ReLU 8192^3 over 100
+graph replays, RMSNorm, softmax, MLA decode), on N GPUs the head-sharded and the batch-sharded MLA
+decode.  Every workload's result is checked once, outside the timed region, on sampled rows
+against a float64 evaluation on the host ("parity").  Timing is by CUDA events, the maximum over
+ranks, and `value` is the aggregate over all GPUs.
 """
 import argparse
 import json
@@ -33,9 +37,10 @@ sys.path.insert(0, str(REPO / "trinity-be_b200"))
 import torch  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
+REL_L2_BOUND, MAX_ABS_BOUND = 1e-2, 2e-2   # the path's stated floating-point bar
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), per workload.
-# None until a capture exists for that workload.  Sources: profiles/*.md.
+# None where no capture exists for that workload.  Sources: profiles/*.md.
 NCU_TRAFFIC_BYTES = {
     "gemm_relu": 1.127e9,
     "gemm_bias_1024": None,
@@ -116,84 +121,169 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": []}
         ordered = sorted(self.samples)
         return {"sm_mhz": ordered[len(ordered) // 2], "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(ordered)}
+                "sm_mhz_min": ordered[0], "reasons": sorted(self.reasons), "samples": len(ordered)}
+
+
+# ---------------------------------------------------------------- parity (float64 on the host)
+def error_figures(actual, expected, rows):
+    """rel-L2 and max-abs of a BF16 result against a float64 expectation of the same rows."""
+    a, e = actual.double(), expected.double()
+    rel = ((a - e).norm() / e.norm().clamp_min(1e-300)).item()
+    worst = (a - e).abs().max().item()
+    return {"rel_l2": rel, "max_abs": worst, "rows": int(rows),
+            "ok": bool(rel <= REL_L2_BOUND and worst <= MAX_ABS_BOUND)}
+
+
+def sampled_rows(total, count):
+    step = max(1, total // count)
+    rows = list(range(0, total, step))[:count]
+    if rows[-1] != total - 1:
+        rows.append(total - 1)
+    return torch.tensor(rows, dtype=torch.long)
+
+
+def swiglu_partial_float64(xs, w_gate, w_up, w_down, block=4096):
+    """(silu(xs Wg) * (xs Wu)) Wd for a few rows in float64, the hidden activation rounded to
+    BF16 once as the plan stores it.  Weights are device tensors; they are brought over in
+    column blocks so the host never holds a float64 copy of a whole weight."""
+    xs = xs.double()
+    y = torch.zeros((xs.shape[0], w_down.shape[1]), dtype=torch.float64)
+    for c0 in range(0, w_gate.shape[1], block):
+        c1 = min(c0 + block, w_gate.shape[1])
+        gate = xs @ w_gate[:, c0:c1].cpu().double()
+        up = xs @ w_up[:, c0:c1].cpu().double()
+        hidden = (up * (gate * torch.sigmoid(gate))).float().bfloat16().double()
+        y += hidden @ w_down[c0:c1].cpu().double()
+    return y
 
 
 # ---------------------------------------------------------------- workloads
 class Workload:
-    """name, metric, unit, bound, work per step, device step, end-to-end step, CPU sample."""
+    """name, metric, unit, bound, work per step, device step, end-to-end slots, checks."""
+
+    parallelism = None
+    strong = False
+    no_graph = False
+    host_launch = None
+    e2e_work = None
 
 
-def make_workload(name, device, world=None):
-    from oracle import workloads as wl  # seeded input generators only (no oracle math here)
+def workload_label(name):
+    """Description of a workload that does not depend on the arm or on the GPU count."""
+    mlp = ("tp_swiglu_mlp X[16384,8192], W_gate/W_up[8192,28672] column-sharded, "
+           "W_down[28672,8192] row-sharded")
+    return {
+        "gemm_relu": "gemm_bias_relu A[8192,8192]@W[8192,8192]+bias[8192], CUDA-Graph replay",
+        "gemm_bias_1024": ("gemm_bias A[1024,1024]@B[1024,1024]+bias[1024], CUDA-Graph replay of 32 "
+                           "launches over 32 operand sets"),
+        "rmsnorm": "rmsnorm X[32768,4096] bf16, gain[4096], eps 1e-6",
+        "softmax": "softmax X[32768,4096] bf16",
+        "gemm_decode_square": "gemm A[16,8192]@W[8192,8192] bf16 (decode-time shape)",
+        "gemm_decode_up": "gemm A[16,8192]@W[8192,28672] bf16 (decode-time shape)",
+        "gemm_decode_down": "gemm A[16,28672]@W[28672,8192] bf16 (decode-time shape)",
+        "mla": "mla_decode batch 64 x 128 heads, cache[64,4096,576] bf16, heads sharded over the GPUs",
+        "mla_batch_sharded": "mla_decode batch 64 x 128 heads, cache[64,4096,576] bf16, sequences sharded over the GPUs",
+        "tp_mlp": mlp + ", all-reduce fused into the down GEMM",
+        "tp_mlp_unfused": mlp + ", separate all-reduce kernel",
+        "tp_mlp_noreduce": mlp + ", NO all-reduce (timing baseline, result incomplete)",
+    }[name]
+
+
+def workload_parallelism(name, ranks):
+    if ranks == 1:
+        return "single GPU"
+    if name.startswith("tp_mlp"):
+        return f"tp{ranks} over NVLink peer memory"
+    if name == "mla":
+        return f"{ranks}-way head sharding, cache replicated, no collective"
+    if name == "mla_batch_sharded":
+        return f"{ranks}-way batch sharding, no collective"
+    return "replicas only"
+
+
+def make_workload(name, device, world=None, ranks=1, rank=0):
     from trinity_lowering import kernels as k
+    from trinity_lowering import synthetic as syn
 
     w = Workload()
     w.name = name
-    w.world = world
-    w.strong = False
-    w.no_graph = False
+    w.label = workload_label(name)
+    w.parallelism = workload_parallelism(name, ranks)
     on_gpu = device.type == "cuda"
 
     def pin(t):
         return t.pin_memory() if on_gpu else t
+
     if name in ("gemm_relu", "gemm_bias_1024"):
         if name == "gemm_relu":
             m = n = kk = 8192
-            a, wt, bias = wl.gemm_inputs(m, n, kk, 1235, "normal")
+            a, wt, bias = syn.gemm_inputs(m, n, kk, 1235, "normal")
             act = k.ACT_RELU
-            w.label = "gemm_bias_relu A[8192,8192]@W[8192,8192]+bias[8192], CUDA-Graph replay"
         else:
             m = n = kk = 1024
-            a, wt, bias = wl.gemm_inputs(m, n, kk, 1234, "uniform")
+            a, wt, bias = syn.gemm_inputs(m, n, kk, 1234, "uniform")
             act = k.ACT_NONE
-            w.label = ("gemm_bias A[1024,1024]@B[1024,1024]+bias[1024], CUDA-Graph replay of 32 launches "
-                       "over 32 operand sets")
         w.metric, w.unit, w.bound, w.dtype = "bf16_gemm_epilogue_tflops", "TFLOP/s", "tensor", "bf16"
         w.work = 2.0 * m * n * kk / 1e12                       # TFLOP per step
         w.alg_bytes = (m * kk + kk * n + n + m * n) * 2
-        host = [pin(t) for t in (a, wt, bias)]
-        host_out = pin(torch.empty((m, n), dtype=torch.bfloat16))
-        dev = [t.to(device) for t in (a, wt, bias)]
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
-        w.kernels_per_step = 1
-        w.l2_note, w.flush = "inputs larger than L2", False
-        # A single small GEMM would be timed with one event pair per launch, which measures the
-        # launch path rather than the kernel.  The small configuration therefore runs 32 launches
-        # per step over 32 operand sets (32 x 6.3 MB > L2), back to back.
-        sets = 1 if (m * kk + kk * n) * 2 > L2_BYTES or not on_gpu else 32
-        rotating = [(dev[0].clone(), dev[1].clone(), torch.empty_like(out)) for _ in range(sets - 1)]
-        rotating.append((dev[0], dev[1], out))
-        w.kernels_per_step = sets
-        w.work *= sets
-        w.e2e_work = w.work / sets
-        w.alg_bytes *= sets
+        w.l2_note = "inputs larger than L2"
+        if on_gpu:
+            dev = [t.to(device) for t in (a, wt, bias)]
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+            # A single small GEMM would be timed with one event pair per launch, which measures the
+            # launch path rather than the kernel.  The small configuration therefore runs 32 launches
+            # per step over 32 operand sets (32 x 6.3 MB > L2), back to back.
+            sets = 1 if (m * kk + kk * n) * 2 > L2_BYTES else 32
+            rotating = [(dev[0].clone(), dev[1].clone(), torch.empty_like(out)) for _ in range(sets - 1)]
+            rotating.append((dev[0], dev[1], out))
+            w.kernels_per_step = sets
+            w.e2e_work = w.work
+            w.work *= sets
+            w.alg_bytes *= sets
 
-        def device_step():
-            for a_i, w_i, out_i in rotating:
-                k.gemm(a_i, w_i, bias=dev[2], bias_mode=k.BIAS_COL_VECTOR, activation=act, out=out_i)
+            def device_step():
+                for a_i, w_i, out_i in rotating:
+                    k.gemm(a_i, w_i, bias=dev[2], bias_mode=k.BIAS_COL_VECTOR, activation=act, out=out_i)
 
-        # End to end goes through the public path: plan -> emit -> compile -> load -> prepare,
-        # then per step host->device copies, execution.run(), device->host copy.
-        api = {}
+            # End to end goes through the public path: plan -> emit -> compile -> load -> prepare,
+            # then per step host->device copies, execution.run(), device->host copy.
+            host = [pin(t) for t in (a, wt, bias)]
+            api = {}
 
-        def e2e_step():
-            if not api:
+            def make_slot(index):
                 import trinity_lowering as tl
                 from trinity_lowering import plans
-                artifact = tl.compile(tl.emit(plans.gemm_bias(m, n, kk, "relu" if act else None)))
-                api["module"] = tl.load(artifact, device)
-                artifact.close()
-                api["execution"] = api["module"].prepare({"A": dev[0], "W": dev[1], "bias": dev[2]}, out=out)
-            for src, dst in zip(host, dev):
-                dst.copy_(src, non_blocking=True)
-            api["execution"].run()
-            host_out.copy_(out, non_blocking=True)
+                if not api:
+                    artifact = tl.compile(tl.emit(plans.gemm_bias(m, n, kk, "relu" if act else None)))
+                    api["module"] = tl.load(artifact, device)
+                    artifact.close()
+                mine = dev if index == 0 else [torch.empty_like(t) for t in dev]
+                mine_out = out if index == 0 else torch.empty_like(out)
+                host_out = pin(torch.empty((m, n), dtype=torch.bfloat16))
+                execution = api["module"].prepare({"A": mine[0], "W": mine[1], "bias": mine[2]}, out=mine_out)
+                if index == 0:
+                    w.host_launch = execution.run
 
-        w.h2d = sum(t.numel() * 2 for t in host)
-        w.d2h = host_out.numel() * 2
-        # host cost of one launch through the public API (runtime checks + trinity_launch), no copies
-        w.host_launch = lambda: api["execution"].run()
+                def h2d():
+                    for src, dst in zip(host, mine):
+                        dst.copy_(src, non_blocking=True)
+
+                def d2h():
+                    host_out.copy_(mine_out, non_blocking=True)
+                return h2d, execution.run, d2h
+
+            w.make_slot = make_slot
+            w.h2d = sum(t.numel() * 2 for t in host)
+            w.d2h = m * n * 2
+
+            def check():
+                rows = sampled_rows(m, 64)
+                expected = a[rows].double() @ wt.double() + bias.double()
+                if act:
+                    expected = torch.relu(expected)
+                return error_figures(out[rows.to(device)].cpu(), expected, len(rows))
+            w.check = check
+            w.device_step = device_step
 
         def cpu_sample(threads, budget_s):
             torch.set_num_threads(threads)
@@ -214,32 +304,46 @@ def make_workload(name, device, world=None):
 
     elif name in ("rmsnorm", "softmax"):
         rows, cols = 32768, 4096
-        x, g = wl.rownorm_inputs(rows, cols, 1236)
-        w.label = f"{name} X[32768,4096] bf16" + (", gain[4096], eps 1e-6" if name == "rmsnorm" else "")
+        x, g = syn.rownorm_inputs(rows, cols, 1236)
         w.metric, w.unit, w.bound, w.dtype = f"{name}_hbm_gbs", "GB/s", "hbm", "bf16"
         w.alg_bytes = rows * cols * 4 + (cols * 2 if name == "rmsnorm" else 0)
         w.work = w.alg_bytes / 1e9
-        host_x = pin(x)
-        host_y = pin(torch.empty_like(x))
-        xd, gd = x.to(device), g.to(device)
-        yd = torch.empty_like(xd)
         w.kernels_per_step = 1
-        w.l2_note, w.flush = "inputs larger than L2", False
+        w.l2_note = "inputs larger than L2"
+        if on_gpu:
+            host_x = pin(x)
+            xd, gd = x.to(device), g.to(device)
+            yd = torch.empty_like(xd)
 
-        def device_step():
-            if name == "rmsnorm":
-                k.rmsnorm(xd, gd, 1e-6, out=yd)
-            else:
-                k.softmax(xd, out=yd)
+            def run(src, dst):
+                if name == "rmsnorm":
+                    k.rmsnorm(src, gd, 1e-6, out=dst)
+                else:
+                    k.softmax(src, out=dst)
 
-        def e2e_step():
-            xd.copy_(host_x, non_blocking=True)
-            device_step()
-            host_y.copy_(yd, non_blocking=True)
+            def make_slot(index):
+                xs = xd if index == 0 else torch.empty_like(xd)
+                ys = yd if index == 0 else torch.empty_like(yd)
+                host_y = pin(torch.empty_like(x))
+                return (lambda: xs.copy_(host_x, non_blocking=True), lambda: run(xs, ys),
+                        lambda: host_y.copy_(ys, non_blocking=True))
 
-        w.h2d, w.d2h = x.numel() * 2, x.numel() * 2
+            w.make_slot = make_slot
+            w.device_step = lambda: run(xd, yd)
+            w.h2d, w.d2h = x.numel() * 2, x.numel() * 2
+
+            def check():
+                picks = sampled_rows(rows, 64)
+                xs = x[picks].double()
+                if name == "rmsnorm":
+                    expected = xs / torch.sqrt(xs.square().mean(dim=1, keepdim=True) + 1e-6) * g.double()
+                else:
+                    expected = torch.softmax(xs, dim=1)
+                return error_figures(yd[picks.to(device)].cpu(), expected, len(picks))
+            w.check = check
 
         def cpu_sample(threads, budget_s):
+            from oracle import workloads as wl   # the CPU baseline times the oracle
             torch.set_num_threads(threads)
             sample = x[:4096]
             t0 = time.perf_counter()
@@ -255,28 +359,32 @@ def make_workload(name, device, world=None):
         m = 16
         kk, n = {"gemm_decode_square": (8192, 8192), "gemm_decode_up": (8192, 28672),
                  "gemm_decode_down": (28672, 8192)}[name]
-        a, wt, _ = wl.gemm_inputs(m, n, kk, 1240, "normal")
-        w.label = f"gemm A[16,{kk}]@W[{kk},{n}] bf16 (decode-time shape)"
+        a, wt, _ = syn.gemm_inputs(m, n, kk, 1240, "normal")
         w.metric, w.unit, w.bound, w.dtype = "gemm_decode_hbm_gbs", "GB/s", "hbm", "bf16"
         w.alg_bytes = (m * kk + kk * n + m * n) * 2
         w.work = w.alg_bytes / 1e9
-        host_a, host_w = pin(a), pin(wt)
-        ad, wd = a.to(device), wt.to(device)
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
-        host_out = pin(torch.empty((m, n), dtype=torch.bfloat16))
         w.kernels_per_step = 1
-        w.l2_note, w.flush = "inputs larger than L2", False
+        w.l2_note = "inputs larger than L2"
+        if on_gpu:
+            host_a, host_w = pin(a), pin(wt)
+            ad, wd = a.to(device), wt.to(device)
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
 
-        def device_step():
-            k.gemm(ad, wd, out=out)
+            def make_slot(index):
+                a_s = ad if index == 0 else torch.empty_like(ad)
+                w_s = wd if index == 0 else torch.empty_like(wd)
+                o_s = out if index == 0 else torch.empty_like(out)
+                host_out = pin(torch.empty((m, n), dtype=torch.bfloat16))
 
-        def e2e_step():
-            ad.copy_(host_a, non_blocking=True)
-            wd.copy_(host_w, non_blocking=True)
-            device_step()
-            host_out.copy_(out, non_blocking=True)
+                def h2d():
+                    a_s.copy_(host_a, non_blocking=True)
+                    w_s.copy_(host_w, non_blocking=True)
+                return h2d, lambda: k.gemm(a_s, w_s, out=o_s), lambda: host_out.copy_(o_s, non_blocking=True)
 
-        w.h2d, w.d2h = (a.numel() + wt.numel()) * 2, out.numel() * 2
+            w.make_slot = make_slot
+            w.device_step = lambda: k.gemm(ad, wd, out=out)
+            w.h2d, w.d2h = (a.numel() + wt.numel()) * 2, out.numel() * 2
+            w.check = lambda: error_figures(out.cpu(), a.double() @ wt.double(), m)
 
         def cpu_sample(threads, budget_s):
             torch.set_num_threads(threads)
@@ -291,101 +399,112 @@ def make_workload(name, device, world=None):
         # On N GPUs "mla" shards the heads N ways and every rank holds the whole cache (the cache
         # is shared by all heads, so tensor-parallel ranks replicate it); "mla_batch_sharded"
         # gives each rank batch/N sequences with all their heads.  Neither has a collective.
-        ranks = int(os.environ.get("WORLD_SIZE", "1")) if on_gpu else 1
-        mine = int(os.environ.get("RANK", "0")) if on_gpu else 0
-        q, cache = wl.mla_inputs(batch, heads, seq, d_qk, 1237)
+        q, cache = syn.mla_inputs(batch, heads, seq, d_qk, 1237)
         if ranks > 1 and name == "mla":
             share = heads // ranks
-            q = q[:, mine * share:(mine + 1) * share].contiguous()
+            q = q[:, rank * share:(rank + 1) * share].contiguous()
             heads = share
-            w.parallelism = f"{ranks}-way head sharding, cache replicated, no collective"
         elif ranks > 1:
             share = batch // ranks
-            q = q[mine * share:(mine + 1) * share].contiguous()
-            cache = cache[mine * share:(mine + 1) * share].contiguous()
+            q = q[rank * share:(rank + 1) * share].contiguous()
+            cache = cache[rank * share:(rank + 1) * share].contiguous()
             batch = share
-            w.parallelism = f"{ranks}-way batch sharding, no collective"
             w.strong = True
         scale = 1.0 / math.sqrt(192.0)
-        w.label = f"mla_decode batch{batch} x {heads} heads per GPU, cache[{batch},4096,576] bf16"
         w.metric, w.unit, w.bound, w.dtype = "mla_decode_hbm_gbs", "GB/s", "hbm", "bf16"
         w.alg_bytes = (q.numel() + cache.numel() + batch * heads * d_v) * 2
         w.work = w.alg_bytes / 1e9
-        host_q, host_c = pin(q), pin(cache)
-        qd, cd = q.to(device), cache.to(device)
-        od = torch.empty((batch, heads, d_v), dtype=torch.bfloat16, device=device)
-        host_o = pin(torch.empty_like(od, device="cpu"))
-        splits = k.mla_default_splits(batch, seq) if on_gpu else 1
-        scratch = torch.empty(max(256, k.mla_scratch_bytes(batch, heads, d_v, splits)) if on_gpu
-                              else 256, dtype=torch.uint8, device=device)
-        w.kernels_per_step = 1 if splits == 1 else 2
-        w.l2_note, w.flush = "inputs larger than L2", False
+        w.l2_note = "inputs larger than L2"
+        if on_gpu:
+            host_q, host_c = pin(q), pin(cache)
+            qd, cd = q.to(device), cache.to(device)
+            od = torch.empty((batch, heads, d_v), dtype=torch.bfloat16, device=device)
+            splits = k.mla_default_splits(batch, seq)
+            scratch = torch.empty(max(256, k.mla_scratch_bytes(batch, heads, d_v, splits)),
+                                  dtype=torch.uint8, device=device)
+            w.kernels_per_step = 1 if splits == 1 else 2
 
-        def device_step():
-            k.mla_decode(qd, cd, scale, kv_splits=0, out=od, scratch=scratch)
+            def make_slot(index):
+                q_s = qd if index == 0 else torch.empty_like(qd)
+                c_s = cd if index == 0 else torch.empty_like(cd)
+                o_s = od if index == 0 else torch.empty_like(od)
+                host_o = pin(torch.empty_like(od, device="cpu"))
 
-        def e2e_step():
-            qd.copy_(host_q, non_blocking=True)
-            cd.copy_(host_c, non_blocking=True)
-            device_step()
-            host_o.copy_(od, non_blocking=True)
+                def h2d():
+                    q_s.copy_(host_q, non_blocking=True)
+                    c_s.copy_(host_c, non_blocking=True)
+                return (h2d, lambda: k.mla_decode(q_s, c_s, scale, kv_splits=0, out=o_s, scratch=scratch),
+                        lambda: host_o.copy_(o_s, non_blocking=True))
 
-        w.h2d, w.d2h = (q.numel() + cache.numel()) * 2, od.numel() * 2
+            w.make_slot = make_slot
+            w.device_step = lambda: k.mla_decode(qd, cd, scale, kv_splits=0, out=od, scratch=scratch)
+            w.h2d, w.d2h = (q.numel() + cache.numel()) * 2, od.numel() * 2
+
+            def check():
+                picks = sorted({0, batch - 1})
+                got = od[picks].cpu()
+                scores = torch.einsum("bhd,bsd->bhs", q[picks].double(), cache[picks].double()) * scale
+                expected = torch.softmax(scores, dim=2) @ cache[picks][:, :, :d_v].double()
+                return error_figures(got, expected, len(picks) * heads)
+            w.check = check
 
         def cpu_sample(threads, budget_s):
+            from oracle import workloads as wl   # the CPU baseline times the oracle
             torch.set_num_threads(threads)
             t0 = time.perf_counter()
             wl.mla_oracle(q, cache, scale, d_v, batches=[0, 1])
             dt = time.perf_counter() - t0
-            return (w.alg_bytes * 2 / batch) / 1e9 / dt, "2 of 64 sequences, CPU oracle", dt
+            return (w.alg_bytes * 2 / batch) / 1e9 / dt, f"2 of {batch} sequences, CPU oracle", dt
+
     elif name in ("tp_mlp", "tp_mlp_unfused", "tp_mlp_noreduce"):
         # Tensor-parallel SwiGLU MLP: total work fixed, sharded over the ranks (strong scaling).
         m, d_model, d_ff = 16384, 8192, 28672
-        w.label = ("tp_swiglu_mlp X[16384,8192], W_gate/W_up[8192,28672] column-sharded, "
-                   "W_down[28672,8192] row-sharded" + {
-                       "tp_mlp": ", all-reduce fused into the down GEMM",
-                       "tp_mlp_unfused": ", separate all-reduce kernel",
-                       "tp_mlp_noreduce": ", NO all-reduce (timing baseline, result incomplete)"}[name])
         w.metric, w.unit, w.bound, w.dtype = "tp_mlp_tflops", "TFLOP/s", "tensor", "bf16"
         w.total_work = 3 * 2.0 * m * d_model * d_ff / 1e12
-        w.alg_bytes = (m * d_model * 2 + 3 * d_model * d_ff + m * d_ff * 2) * 2
-        w.flush, w.l2_note = False, "inputs larger than L2"
+        w.alg_bytes = (m * d_model * 2 + 3 * d_model * d_ff // ranks + m * (d_ff // ranks) * 2) * 2
+        w.l2_note = "inputs larger than L2"
         w.strong = True
         w.no_graph = True     # the all-reduce epoch is a launch argument
+        w.work = w.total_work / ranks
         if on_gpu:
             from trinity_lowering.tp_mlp import TensorParallelMLP
-            world = w.world
-            size = world.size if world is not None else 1
-            rank = world.rank if world is not None else 0
-            shard = d_ff // size
-            g = torch.Generator(device=device)
-            g.manual_seed(1238 + rank)
-            def normal(shape, std):
-                return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std).bfloat16()
-            gx = torch.Generator(device=device)
-            gx.manual_seed(1238)
-            xd = (torch.randn((m, d_model), generator=gx, device=device)).bfloat16()
-            wg = normal((d_model, shard), 1.0 / math.sqrt(d_model))
-            wu = normal((d_model, shard), 1.0 / math.sqrt(d_model))
-            wd = normal((shard, d_model), 1.0 / math.sqrt(d_ff))
-            mlp = TensorParallelMLP(world, m, d_model, d_ff, wg, wu, wd,
-                                    fused={"tp_mlp": True, "tp_mlp_unfused": False}.get(name))
+            shard = d_ff // ranks
+            xd = syn.mlp_activations_on_device(m, d_model, device)
+            wg, wu, wd = syn.mlp_shard_on_device(rank, d_model, shard, d_ff, device)
+            fused = {"tp_mlp": True, "tp_mlp_unfused": False}.get(name)
+            mlp = TensorParallelMLP(world, m, d_model, d_ff, wg, wu, wd, fused=fused)
             host_x = xd.cpu().pin_memory()
-            host_y = torch.empty((m, d_model), dtype=torch.bfloat16).pin_memory()
-            w.work = w.total_work / size
-            w.kernels_per_step = 2 if (size == 1 or name == "tp_mlp") else 3
+            w.kernels_per_step = 2 if (ranks == 1 or name != "tp_mlp_unfused") else 3
 
-            def device_step():
-                mlp.forward(xd)
+            def make_slot(index):
+                layer = mlp if index == 0 else TensorParallelMLP(world, m, d_model, d_ff, wg, wu, wd, fused=fused)
+                xs = xd if index == 0 else torch.empty_like(xd)
+                host_y = torch.empty((m, d_model), dtype=torch.bfloat16).pin_memory()
+                return (lambda: xs.copy_(host_x, non_blocking=True), lambda: layer.forward(xs),
+                        lambda: host_y.copy_(layer.output, non_blocking=True))
 
-            def e2e_step():
-                xd.copy_(host_x, non_blocking=True)
-                mlp.forward(xd)
-                host_y.copy_(mlp.output, non_blocking=True)
-
+            w.make_slot = make_slot
+            w.device_step = lambda: mlp.forward(xd)
             w.h2d, w.d2h = xd.numel() * 2, m * d_model * 2
-        else:
-            device_step = e2e_step = None
+
+            def check():
+                # Every rank evaluates its own partial product for the sampled rows in float64 and
+                # rounds it to BF16 (the partials cross NVLink in BF16); rank 0 adds the partials in
+                # rank order in FP32, as the kernel does, and compares.
+                rows = sampled_rows(m, 32)
+                partial = swiglu_partial_float64(host_x[rows], wg, wu, wd).float().bfloat16()
+                if ranks > 1 and name != "tp_mlp_noreduce":
+                    import torch.distributed as dist
+                    parts = [torch.empty_like(partial, device=device) for _ in range(ranks)]
+                    dist.all_gather(parts, partial.to(device))
+                    total = torch.zeros(partial.shape, dtype=torch.float32)
+                    for part in parts:
+                        total += part.cpu().float()
+                    expected = total
+                else:
+                    expected = partial.float()
+                return error_figures(mlp.output[rows.to(device)].cpu(), expected, len(rows))
+            w.check = check
 
         def cpu_sample(threads, budget_s):
             torch.set_num_threads(threads)
@@ -403,37 +522,110 @@ def make_workload(name, device, world=None):
             return 3 * 2.0 * rows * d_model * d_ff / 1e12 / dt, f"{rows} of {m} rows, torch CPU FP32", dt
     else:
         raise SystemExit(f"unknown workload {name}")
-    w.device_step, w.e2e_step, w.cpu_sample = device_step, e2e_step, cpu_sample
+    w.cpu_sample = cpu_sample
     return w
 
 
-def flush_l2(buffer):
-    buffer.zero_()
+def config_of(w, graph):
+    return {"workload": w.label, "l2": w.l2_note, "parallelism": w.parallelism,
+            "launch": "CUDA Graph replay" if graph else "direct"}
 
 
-def timed(step, steps, flush_buffer, stream):
-    """CUDA-event time (ms) of `steps` calls on `stream`; L2 flushes are excluded from the sum."""
-    if flush_buffer is None:
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record(stream)
-        for _ in range(steps):
-            step()
-        stop.record(stream)
-        stop.synchronize()
-        return start.elapsed_time(stop)
-    total = 0.0
-    events = []
+# ---------------------------------------------------------------- timing
+def timed(step, steps, stream):
+    """CUDA-event time (ms) of `steps` calls on `stream`."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
     for _ in range(steps):
-        flush_l2(flush_buffer)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(stream)
         step()
-        b.record(stream)
-        events.append((a, b))
-    torch.cuda.synchronize()
-    for a, b in events:
-        total += a.elapsed_time(b)
-    return total
+    stop.record(stream)
+    stop.synchronize()
+    return start.elapsed_time(stop)
+
+
+def end_to_end(w, steps, device):
+    """The step through the public call with host buffers: the host->device copy of step i+1, the
+    kernels of step i and the device->host copy of step i-1 run on three streams over two sets
+    of device buffers; every step's copies are inside the timed region.  Returns ms."""
+    slots = [w.make_slot(0), w.make_slot(1)]
+    s_in, s_run, s_out = (torch.cuda.Stream(device=device) for _ in range(3))
+    copied = [torch.cuda.Event() for _ in range(2)]
+    ran = [torch.cuda.Event() for _ in range(2)]
+    read = [torch.cuda.Event() for _ in range(2)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def pipeline(count, timing):
+        torch.cuda.synchronize()
+        if timing:
+            start.record(s_in)
+        for i in range(count):
+            j = i % 2
+            h2d, run, d2h = slots[j]
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ran[j])       # the kernels of step i-2 have consumed this input
+                h2d()
+                copied[j].record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(copied[j])
+                if i >= 2:
+                    s_run.wait_event(read[j])     # the result of step i-2 has left this buffer
+                run()
+                ran[j].record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ran[j])
+                d2h()
+                read[j].record(s_out)
+        if timing:
+            stop.record(s_out)
+        torch.cuda.synchronize()
+
+    pipeline(3, False)
+    pipeline(steps, True)
+    return start.elapsed_time(stop)
+
+
+def measure(w, steps, warmup, stream, device, use_graph, barrier, clock_index=None):
+    """Device-timed steps of one workload; returns (ms, launches through the library, clocks)."""
+    from trinity_lowering import kernels as k
+    with torch.cuda.stream(stream):
+        w.device_step()
+        torch.cuda.synchronize()
+        if use_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                w.device_step()
+            replay = graph.replay
+        else:
+            replay = w.device_step
+        for _ in range(warmup):
+            replay()
+        barrier()
+        before = k.launch_count()
+        if clock_index is None:
+            ms, clocks = timed(replay, steps, stream), None
+        else:
+            with ClockSampler(clock_index) as sampler:
+                ms = timed(replay, steps, stream)
+            clocks = sampler.summary()
+        barrier()
+        launches = k.launch_count() - before
+        if use_graph:
+            launches += steps * w.kernels_per_step   # replays do not pass through the library
+    return ms, launches, clocks
+
+
+def roofline_of(w, per_step_ms, long_run):
+    pk = peaks()
+    achieved = w.work / (per_step_ms / 1e3)            # per GPU
+    if w.bound == "tensor":
+        peak = pk["bf16_tflops_sustained"] if long_run else pk["bf16_tflops"]
+        note = ("sustained" if long_run else "burst") + " cuBLAS bf16, " + pk["source"]
+        unit = "TFLOP/s"
+    else:
+        peak, note, unit = pk["hbm_gbs"], "copy bandwidth, " + pk["source"], "GB/s"
+    return {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+            "traffic": NCU_TRAFFIC_BYTES.get(w.name), "algorithmic_bytes": w.alg_bytes, "peak_kind": note}
 
 
 def run_reference(args, rank, world):
@@ -441,7 +633,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    w = make_workload(args.workload, torch.device("cpu"))
+    w = make_workload(args.workload, torch.device("cpu"), ranks=world)
     values = []
     sample = ""
     for i in range(args.warmup + args.steps):
@@ -452,9 +644,9 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference", "metric": w.metric, "value": value, "unit": w.unit,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": w.dtype, "data": "synthetic",
-        "config": {"workload": w.label, "note": "reference plan evaluation on host cores"},
+        "ms_per_step": None, "higher_is_better": True, "scaling": "strong" if w.strong else "weak",
+        "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+        "config": config_of(w, not (w.no_graph or args.no_graph)),
         "cpu_baseline": {"value": value, "unit": w.unit, "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -465,11 +657,13 @@ def run_reference(args, rank, world):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=100)
+    parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="gemm_relu")
+    parser.add_argument("--workload", default="tp_mlp")
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-configs", action="store_true",
+                        help="skip the block with the other benchmark configurations")
     parser.add_argument("--no-graph", action="store_true",
                         help="launch directly instead of replaying a CUDA Graph (for profilers)")
     args = parser.parse_args()
@@ -492,20 +686,18 @@ def main():
     distributed = world > 1
     if distributed:
         import torch.distributed as dist
+        # the kernels use plain peer loads and stores; nothing here needs a multicast binding
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=device)
 
     from trinity_lowering import kernels as k
     k.library()
     world_obj = None
     if distributed and args.workload.startswith("tp_mlp"):
-        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         from trinity_lowering.world import World
         world_obj = World.from_torchrun(timeout=120.0)
-    w = make_workload(args.workload, device, world_obj)
-    if w.no_graph:
-        args.no_graph = True
     stream = torch.cuda.Stream(device=device)
-    flush_buffer = (torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device) if w.flush else None)
 
     def barrier():
         torch.cuda.synchronize()
@@ -513,100 +705,101 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    with torch.cuda.stream(stream):
-        # Capture one step (all launches of the hot path) in a CUDA Graph, as the configuration asks.
-        w.device_step()
-        torch.cuda.synchronize()
-        if args.no_graph:
-            replay = w.device_step
-        else:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                w.device_step()
-            replay = graph.replay
-        for _ in range(args.warmup):
-            replay()
-        barrier()
-        launches_before = k.launch_count()
-        with ClockSampler(local_rank) as clocks:
-            ms = timed(replay, args.steps, flush_buffer, stream)
-        barrier()
-        # end to end: host buffers in, result out, every step
-        for _ in range(3):
-            w.e2e_step()
-        barrier()
-        e2e_steps = max(3, min(args.steps, 10))
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record(stream)
-        for _ in range(e2e_steps):
-            w.e2e_step()
-        stop.record(stream)
-        stop.synchronize()
-        e2e_ms = start.elapsed_time(stop)
-        barrier()
-        launches_after = k.launch_count()
-        host_launch_us = None
-        if getattr(w, "host_launch", None) is not None:
-            calls = 100
+    def maximum(*values):
+        if not distributed:
+            return list(values)
+        t = torch.tensor(values, device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def worst_parity(figures):
+        """The largest errors over the ranks (every rank checks its own shard)."""
+        rel, worst = maximum(figures["rel_l2"], figures["max_abs"])
+        return {"rel_l2": rel, "max_abs": worst, "rows": figures["rows"],
+                "ok": bool(rel <= REL_L2_BOUND and worst <= MAX_ABS_BOUND)}
+
+    w = make_workload(args.workload, device, world_obj, world, rank)
+    use_graph = not (w.no_graph or args.no_graph)
+    ms, launches, clocks = measure(w, args.steps, args.warmup, stream, device, use_graph, barrier, local_rank)
+    parity = w.check()
+    if not (args.workload.startswith("tp_mlp") and distributed):
+        parity = worst_parity(parity)       # the MLP's check already gathers over the ranks
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = end_to_end(w, e2e_steps, device)
+    barrier()
+    host_launch_us = None
+    if w.host_launch is not None:
+        calls = 100
+        with torch.cuda.stream(stream):
             t0 = time.perf_counter()
             for _ in range(calls):
                 w.host_launch()
             host_launch_us = (time.perf_counter() - t0) / calls * 1e6
-            barrier()
-    launches = launches_after - launches_before
-    if not args.no_graph:
-        launches += args.steps * w.kernels_per_step  # replays do not pass through the library
-
-    if distributed:
-        t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
+        barrier()
+    ms, e2e_ms = maximum(ms, e2e_ms)
 
     status = k.device_status()
     if status:
         raise SystemExit(f"device status word {status:#x}: a bounded in-kernel wait gave up")
 
-    pk = peaks()
     per_step_ms = ms / args.steps
-    value = world * w.work * args.steps / (ms / 1e3)
-    e2e_value = world * (getattr(w, "e2e_work", None) or w.work) * e2e_steps / (e2e_ms / 1e3)
-    scaling = "strong" if w.strong else "weak"
-    achieved = w.work / (per_step_ms / 1e3)            # per GPU, dominant kernel
-    if w.bound == "tensor":
-        long_run = ms > 1000.0
-        peak = pk["bf16_tflops_sustained"] if long_run else pk["bf16_tflops"]
-        peak_note = ("sustained" if long_run else "burst") + " cuBLAS bf16, " + pk["source"]
-        roof_unit = "TFLOP/s"
-    else:
-        peak, peak_note, roof_unit = pk["hbm_gbs"], "copy bandwidth, " + pk["source"], "GB/s"
     line = {
-        "metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": per_step_ms, "higher_is_better": True,
-        "scaling": scaling, "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
-        "config": {"workload": w.label, "l2": w.l2_note,
-                   "parallelism": (getattr(w, "parallelism", None) or
-                                   ("single GPU" if world == 1 else
-                                    f"tp{world} over NVLink peer memory" if w.strong else "replicas only")),
-                   "launch": "direct" if args.no_graph else "CUDA Graph replay"},
-        "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": roof_unit,
-                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(w.name),
-                     "algorithmic_bytes": w.alg_bytes, "peak_kind": peak_note},
-        "e2e": {"value": e2e_value, "unit": w.unit, "h2d_bytes_per_step": w.h2d,
-                "d2h_bytes_per_step": w.d2h, "steps": e2e_steps},
+        "metric": w.metric, "value": world * w.work * args.steps / (ms / 1e3), "unit": w.unit,
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step_ms,
+        "higher_is_better": True, "scaling": "strong" if w.strong else "weak", "vs_baseline": None,
+        "dtype": w.dtype, "data": "synthetic", "config": config_of(w, use_graph),
+        "roofline": roofline_of(w, per_step_ms, ms > 1000.0),
+        "e2e": {"value": world * (w.e2e_work or w.work) * e2e_steps / (e2e_ms / 1e3), "unit": w.unit,
+                "h2d_bytes_per_step": w.h2d, "d2h_bytes_per_step": w.d2h, "steps": e2e_steps,
+                "overlap": "copies of neighbouring steps overlap the kernels (three streams, two buffer sets)"},
+        "parity": parity,
         "gpu_launches": launches,
-        "clocks": clocks.summary(),
+        "clocks": clocks,
     }
     if host_launch_us is not None:
         line["host_launch_us"] = host_launch_us   # public-API launch, host side only
+
+    # The other benchmark configurations, each device-timed and checked the same way.
+    if args.workload == "tp_mlp" and not args.no_configs:
+        del w
+        torch.cuda.empty_cache()
+        names = (["gemm_bias_1024", "gemm_relu", "rmsnorm", "softmax", "mla"] if world == 1
+                 else ["mla", "mla_batch_sharded"])
+        block = {}
+        for name in names:
+            other = make_workload(name, device, None, world, rank)
+            steps = 100 if name == "gemm_relu" else 30
+            other_ms, other_launches, _ = measure(other, steps, 5, stream, device, True, barrier)
+            figures = worst_parity(other.check())
+            (other_ms,) = maximum(other_ms)
+            roof = roofline_of(other, other_ms / steps, False)
+            block[name] = {"workload": other.label, "parallelism": other.parallelism, "steps": steps,
+                           "ms_per_step": other_ms / steps,
+                           "value": world * other.work * steps / (other_ms / 1e3), "unit": other.unit,
+                           "roofline": roof, "parity": figures, "gpu_launches": other_launches}
+            line["gpu_launches"] += other_launches
+            del other
+            torch.cuda.empty_cache()
+        line["configs"] = block
+        status = k.device_status()
+        if status:
+            raise SystemExit(f"device status word {status:#x}: a bounded in-kernel wait gave up")
+
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        v, sample, _ = w.cpu_sample(threads, budget_s=10.0)
-        line["cpu_baseline"] = {"value": v, "unit": w.unit, "cores": threads, "kind": "port",
+        w_cpu = make_workload(args.workload, torch.device("cpu"))
+        v, sample, _ = w_cpu.cpu_sample(threads, budget_s=10.0)
+        line["cpu_baseline"] = {"value": v, "unit": line["unit"], "cores": threads, "kind": "port",
                                 "sample": sample}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if distributed:
         dist.destroy_process_group()
+    checks = [line["parity"]] + [c["parity"] for c in line.get("configs", {}).values()]
+    if not all(c["ok"] for c in checks):
+        print("bench.py: a result is outside the stated tolerance (see \"parity\")", file=sys.stderr)
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -260,10 +260,14 @@ TRINITY_SM100_API int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* arg
  * calls no cudaMalloc, cudaFree or other allocating routine.  args->scratch and
  * args->scratch_bytes are ignored.
  *
- * Limit: trinity_sm100_mla_scratch_bytes(batch, heads, d_v, splits) must not exceed the array;
- * larger requests return TRINITY_SM100_E_UNSUPPORTED with an explanation.
- * First use on a device looks up the array's device address (one cudaGetSymbolAddress with
- * that device current); make that first call outside any stream capture.
+ * Limit: trinity_sm100_mla_scratch_bytes(batch, heads, d_v, splits) must not exceed the array.
+ * With kv_splits == 0 (schedule left to the library) a first choice that does not fit is
+ * replaced by the most equal splits that do; with kv_splits != 0 (schedule fixed by the caller)
+ * a request that does not fit returns TRINITY_SM100_E_UNSUPPORTED with an explanation.
+ * The array's device address is looked up once per device (one cudaGetSymbolAddress with that
+ * device current): by trinity_sm100_prepare_device(), which every program.so calls from
+ * trinity_prepare, or else by the first call of this entry point on the device, which should
+ * then come before any stream capture.
  * All calls on one GPU share the array: calls that overlap in time on the GPU race on it.
  * Nothing in the array needs clearing between calls.
  *
@@ -279,7 +283,8 @@ TRINITY_SM100_API int trinity_sm100_mla_decode_bf16_noalloc(const trinity_sm100_
  *   peers[r]  this buffer on rank r, mapped into the calling process (peers[rank] is local)
  *   flags[r]  rank r's flag pad (uint32, at least trinity_sm100_allreduce_flag_words() words,
  *             zeroed once before first use)
- *   epoch     strictly increasing per call on every rank (flags are never reset)
+ *   epoch     strictly increasing per call on every rank, starting at 1 (flags are never reset
+ *             and a zeroed pad reads as epoch 0, which is refused)
  *
  * Two-shot: rank r reduces row block r of every peer into its own buffer in FP32, then every
  * rank pulls the reduced blocks.  All waits are bounded; a wait that gives up sets the device
@@ -307,7 +312,9 @@ TRINITY_SM100_API int trinity_sm100_allreduce_bf16(const trinity_sm100_allreduce
  * Every rank calls this with its own shard (`gemm`: no bias, no activation, BF16 out) and the
  * same peer tables (`reduce`: peers[r] = rank r's [m,n] output buffer, peers[rank] == gemm->out;
  * flags[r] = rank r's flag pad of at least trinity_sm100_gemm_allreduce_flag_words() zeroed
- * words; epoch strictly increasing per call; world is 1, 2, 4 or 8).  Inside one persistent
+ * words, whose first trinity_sm100_allreduce_flag_words() words are left to
+ * trinity_sm100_allreduce_bf16 so one pad serves both; epoch strictly increasing per call,
+ * starting at 1; world is 1, 2, 4 or 8).  Inside one persistent
  * kernel the epilogue warps store their partial tile, tell every rank, and - one tile behind,
  * so the wait is short and the NVLink traffic overlaps the next tile's MMAs - each rank adds
  * the partials of its own 128/world rows of that tile in rank order in FP32 and pushes the
@@ -329,6 +336,15 @@ TRINITY_SM100_API int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm
  * Counterpart of the generated trinity_status() (src/emit/native/cuda/templates/host.cu.j2:78-83).
  */
 TRINITY_SM100_API int trinity_sm100_device_status(uint32_t* status, int clear);
+
+/*
+ * Budget of every bounded in-kernel wait on the current device, in SM clock cycles (default
+ * about two seconds; 0 restores the default).  Synchronises the device.  A wait that exceeds it
+ * records its site in the device status word and the kernel returns without faulting, so the
+ * context stays usable.  The reference's artifacts have no such bound: its persistent launch only
+ * carries a stall hook for tests (delay_rank / delay_task / delay_cycles, src/native/abi.h:38-40).
+ */
+TRINITY_SM100_API int trinity_sm100_set_wait_budget(uint64_t cycles);
 
 /* Library identity and diagnostics. */
 TRINITY_SM100_API int trinity_sm100_abi_version(void);

@@ -1,43 +1,20 @@
-"""TEST INFRASTRUCTURE ONLY -- seeded inputs and oracle equations of the benchmark workloads.
+"""TEST INFRASTRUCTURE ONLY -- oracle equations of the benchmark workloads.
 
-Each workload is a synthetic, seeded stand-in with the shapes and value distributions the
-benchmark configurations state; inputs are drawn in FP32 from a torch CPU generator and cast to
-BF16.  The equations are written in the vocabulary of ``oracle.evaluator`` and therefore carry
-the reference's precision rules (FP32 elementwise math, float64 matrix products, one rounding
-at the store).
+The equations are written in the vocabulary of ``oracle.evaluator`` and therefore carry the
+reference's precision rules (FP32 elementwise math, float64 matrix products, one rounding at
+the store).  The seeded input generators live in ``trinity_lowering.synthetic`` (the product
+and the benchmark draw from there without touching this package); they are re-exported here so
+a parity test names inputs and expected results through one module.
 """
-import math
-
 import torch
+
+from trinity_lowering.synthetic import (_gen, _normal, dyadic_gemm_inputs, ffn_block_inputs, ffn_ir_inputs,  # noqa: F401
+                                        gemm_inputs, mla_inputs, mlp_inputs, rownorm_inputs)
 
 from . import evaluator as ev
 
 
-def _gen(seed):
-    g = torch.Generator(device="cpu")
-    g.manual_seed(seed)
-    return g
-
-
-def _normal(shape, std, g, mean=0.0):
-    return (torch.randn(shape, generator=g, dtype=torch.float32) * std + mean).bfloat16()
-
-
-def _uniform(shape, g):
-    return (torch.rand(shape, generator=g, dtype=torch.float32) * 2 - 1).bfloat16()
-
-
 # ---------------------------------------------------------------- GEMM + epilogue
-def gemm_inputs(m, n, k, seed, distribution="normal"):
-    """A[m,k], W[k,n], bias[n].  'uniform': all U(-1,1) (streamed example shape class);
-    'normal': A~N(0,1), W~N(0,1/k), bias~N(0,0.1) (graph-replay configuration)."""
-    g = _gen(seed)
-    if distribution == "uniform":
-        return _uniform((m, k), g), _uniform((k, n), g), _uniform((n,), g)
-    return (_normal((m, k), 1.0, g), _normal((k, n), 1.0 / math.sqrt(k), g),
-            _normal((n,), 0.1, g))
-
-
 def gemm_equation(activation=None, bias="col"):
     """act(A @ W + bcast(bias)) over value ids 'A', 'W', 'bias'."""
     e = ev.op("matmul", ev.load("A"), ev.load("W"))
@@ -76,23 +53,7 @@ def gated_oracle(a, w_up, w_gate, rows=None):
     return ev.run(gated_equation(), env, [env["A"].shape[0], w_up.shape[1]], "bf16")
 
 
-def dyadic_gemm_inputs(m, n, k):
-    """The exactly-representable operand pattern of the reference's GEMM harness
-    (src/emit/provider/cute/operator/gemm/tests/reference.cu:17-19): every product and FP32
-    partial sum is exact, so any correct kernel must match bit for bit."""
-    i = torch.arange(m * k, dtype=torch.int64)
-    a = (((i * 13 + (i // k) * 7) % 17 - 8).float() / 8.0).reshape(m, k).bfloat16()
-    j = torch.arange(k * n, dtype=torch.int64)
-    b = (((j * 11 + (j // n) * 3) % 19 - 9).float() / 8.0).reshape(k, n).bfloat16()
-    return a, b
-
-
 # ---------------------------------------------------------------- row kernels
-def rownorm_inputs(rows, cols, seed):
-    g = _gen(seed)
-    return _normal((rows, cols), 1.0, g), _normal((cols,), 0.02, g, mean=1.0)
-
-
 def rmsnorm_equation(cols, eps, gain=True):
     x = ev.load("X")
     mean = ev.op("div", ev.op("sum", ev.op("sqr", x), axis=1), ev.const(float(cols)))
@@ -121,11 +82,6 @@ def softmax_oracle(x):
 
 
 # ---------------------------------------------------------------- MLA decode
-def mla_inputs(batch, heads, seq, d_qk, seed):
-    g = _gen(seed)
-    return _normal((batch, heads, d_qk), 1.0, g), _normal((batch, seq, d_qk), 1.0, g)
-
-
 def mla_oracle(q, cache, scale, d_v, batches=None):
     """softmax_s(scale * q.cache^T) @ cache[..., :d_v] per batch, with the evaluator's rules:
     float64 matrix products narrowed to FP32, FP32 softmax, one BF16 rounding of the output.
@@ -145,13 +101,6 @@ def mla_oracle(q, cache, scale, d_v, batches=None):
 
 
 # ---------------------------------------------------------------- TP MLP
-def mlp_inputs(m, d_model, d_ff, seed):
-    g = _gen(seed)
-    return (_normal((m, d_model), 1.0, g), _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
-            _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
-            _normal((d_ff, d_model), 1.0 / math.sqrt(d_ff), g))
-
-
 def mlp_oracle(x, w_gate, w_up, w_down, rows=None):
     """Y = (silu(X@Wg) * (X@Wu)) @ Wd with the hidden activation stored once in BF16."""
     xs = x if rows is None else x[rows]
@@ -159,20 +108,6 @@ def mlp_oracle(x, w_gate, w_up, w_down, rows=None):
     env = {"H": hidden, "Wd": w_down}
     return ev.run(ev.op("matmul", ev.load("H"), ev.load("Wd")), env,
                   [xs.shape[0], w_down.shape[1]], "bf16")
-
-
-def ffn_block_inputs(m, d_model, d_ff, seed):
-    """attn, Wo, residual, gain, Wg, Wu, Wd for the decode-time feed-forward block."""
-    g = _gen(seed)
-    return {
-        "attn": _normal((m, d_model), 1.0, g),
-        "Wo": _normal((d_model, d_model), 1.0 / math.sqrt(d_model), g),
-        "R": _normal((m, d_model), 1.0, g),
-        "g": _normal((d_model,), 0.02, g, mean=1.0),
-        "Wg": _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
-        "Wu": _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
-        "Wd": _normal((d_ff, d_model), 1.0 / math.sqrt(d_ff), g),
-    }
 
 
 def ffn_block_oracle(t, eps):
@@ -183,18 +118,6 @@ def ffn_block_oracle(t, eps):
     xn = rmsnorm_oracle(x1, t["g"], eps)
     hidden = gated_oracle(xn, t["Wu"], t["Wg"])
     return gemm_oracle(hidden, t["Wd"], x1, None, "matrix")
-
-
-def ffn_ir_inputs(m, d_model, d_ff, seed):
-    g = _gen(seed)
-    return {
-        "attn": _normal((m, d_model), 1.0, g),
-        "Wo": _normal((d_model, d_model), 1.0 / math.sqrt(d_model), g),
-        "X": _normal((m, d_model), 1.0, g),
-        "Wa": _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
-        "Wb": _normal((d_model, d_ff), 1.0 / math.sqrt(d_model), g),
-        "Wd": _normal((d_ff, d_model), 1.0 / math.sqrt(d_ff), g),
-    }
 
 
 def ffn_ir_oracle(t):

@@ -1,0 +1,105 @@
+"""Parity at the benchmark's own sizes (B200 only): the 8192^3 GEMM + bias + ReLU through the
+CUDA-Graph path of the public API, the two per-GPU GEMMs of the eight-way tensor-parallel MLP,
+and the whole MLP on one GPU, each compared with the CPU oracle on strided sample rows.
+
+Tolerances: one BF16 ulp against the oracle rounded to BF16 for a single GEMM + epilogue; the
+path's rel-L2 <= 1e-2 / max-abs <= 2e-2 for the chained MLP (a one-ulp flip in the BF16 hidden
+activation moves small outputs by more than one ulp)."""
+import pytest
+import torch
+
+import trinity_lowering as tl
+from oracle import workloads as wl
+from parity import assert_close_bf16
+from trinity_lowering import plans, synthetic
+from trinity_lowering.tp_mlp import TensorParallelMLP
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _library():
+    from trinity_lowering import kernels as k
+    k.library()
+    yield
+    torch.cuda.synchronize()
+    assert k.device_status() == 0
+    torch.cuda.empty_cache()
+
+
+@torch.inference_mode()
+def test_gemm_bias_relu_8192_cubed_through_a_graph():
+    m = n = k = 8192
+    artifact = tl.compile(tl.emit(plans.gemm_bias(m, n, k, "relu")))
+    module = tl.load(artifact, DEV)
+    artifact.close()
+    a, w, bias = wl.gemm_inputs(m, n, k, 1235, "normal")
+    io = module.allocate_io()
+    io.inputs["A"].copy_(a)
+    io.inputs["W"].copy_(w)
+    io.inputs["bias"].copy_(bias)
+    execution = module.prepare(io.inputs, out=io.output)
+    stream = torch.cuda.Stream(device=module.device)
+    stream.wait_stream(torch.cuda.current_stream(module.device))
+    graph = tl.Graph.capture(execution.run, executions=[execution], stream=stream)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            graph.replay()
+    graph.wait(timeout=60)
+    # 64 strided rows plus the last one: every row tile of the rasterisation groups is sampled
+    rows = torch.cat([torch.arange(0, m, 128) + torch.arange(64) % 128, torch.tensor([m - 1])])
+    expected = wl.gemm_oracle(a, w, bias, "relu", rows=rows)
+    assert_close_bf16(graph.output[rows.to(DEV)].cpu(), expected, max_ulp=1, max_abs=2e-2)
+    del graph
+    stream.synchronize()
+    tl.runtime.native().collect_local()
+    execution.close()
+    module.close()
+
+
+@pytest.fixture(scope="module")
+def mlp_operands():
+    """X[16384,8192] and one rank's shards of the eight-way split (3584 of 28672 columns)."""
+    m, d_model, d_ff, ranks = 16384, 8192, 28672, 8
+    x = synthetic.mlp_activations_on_device(m, d_model, DEV)
+    wg, wu, wd = synthetic.mlp_shard_on_device(3, d_model, d_ff // ranks, d_ff, DEV)
+    return x, wg, wu, wd
+
+
+def test_gated_gemm_at_the_per_gpu_shape(mlp_operands):
+    from trinity_lowering import kernels as k
+    x, wg, wu, _ = mlp_operands
+    hidden = k.gemm(x, wu, b2=wg, activation=k.ACT_SILU_GATE)
+    rows = torch.arange(5, x.shape[0], 257)
+    expected = wl.gated_oracle(x[rows.to(DEV)].cpu(), wu.cpu(), wg.cpu())
+    assert_close_bf16(hidden[rows.to(DEV)].cpu(), expected, max_ulp=1, max_abs=2e-2)
+
+
+def test_down_gemm_at_the_per_gpu_shape(mlp_operands):
+    from trinity_lowering import kernels as k
+    x, wg, wu, wd = mlp_operands
+    hidden = k.gemm(x, wu, b2=wg, activation=k.ACT_SILU_GATE)
+    out = k.gemm(hidden, wd)
+    rows = torch.arange(11, x.shape[0], 257)
+    expected = wl.gemm_oracle(hidden[rows.to(DEV)].cpu(), wd.cpu(), None)
+    assert_close_bf16(out[rows.to(DEV)].cpu(), expected, max_ulp=1, max_abs=2e-2)
+
+
+def test_whole_mlp_on_one_gpu():
+    m, d_model, d_ff = 16384, 8192, 28672
+    x = synthetic.mlp_activations_on_device(m, d_model, DEV)
+    wg, wu, wd = synthetic.mlp_shard_on_device(0, d_model, d_ff, d_ff, DEV)
+    mlp = TensorParallelMLP(None, m, d_model, d_ff, wg, wu, wd)
+    out = mlp.forward(x)
+    torch.cuda.synchronize()
+    rows = torch.arange(3, m, 1024)
+    xs = x[rows.to(DEV)].cpu()
+    # the gated product is separable by columns: the oracle runs on 4096-column blocks so the
+    # host never holds a float64 copy of a whole weight
+    blocks = [wl.gated_oracle(xs, wu[:, c:c + 4096].cpu(), wg[:, c:c + 4096].cpu())
+              for c in range(0, d_ff, 4096)]
+    hidden = torch.cat(blocks, dim=1)
+    assert_close_bf16(mlp.hidden[rows.to(DEV)].cpu(), hidden, max_ulp=1, max_abs=2e-2)
+    expected = wl.gemm_oracle(hidden, wd.cpu(), None)
+    assert_close_bf16(out[rows.to(DEV)].cpu(), expected, max_ulp=None, max_abs=2e-2)

@@ -437,8 +437,9 @@ def test_text_reader_rejects_hazards_where_the_reference_does():
                         "(keyed_index (slot a fulltile))")
     dtypes = {"X": "bf16", "Y": "bf16", "T": "fp32"}
 
-    def produce(index, stop=256):
-        return f"(ploop 0 {stop} 128 c (store {view('tensor', 'T')} (sqr (load {view('input', 'X')} {index})) {index}))"
+    def produce(index, stop=256, start=0):
+        return (f"(ploop {start} {stop} 128 c (store {view('tensor', 'T')} "
+                f"(sqr (load {view('input', 'X')} {index})) {index}))")
     consume = f"(ploop 0 256 128 c (store {view('output', 'Y')} (relu (load {view('tensor', 'T')} {tile})) {tile}))"
     (plan,) = tl.lower_ir(f"(seq {produce(tile)} {consume})", {}, dtypes)
     assert [v["storage"] for v in json.loads(plan.metadata_json())["values"]] == ["external", "global", "external"]
@@ -450,5 +451,8 @@ def test_text_reader_rejects_hazards_where_the_reference_does():
             (f"(sloop 0 256 128 k {consume.replace('tensor', 'input').replace(' T)', ' X)')})", "parallel work inside")):
         with pytest.raises(ValueError, match=fragment + ".* at byte [1-9]"):
             tl.lower_ir(text, {}, dtypes)
+    # two kernels that write one half each cover a later read of the whole tensor
+    halves = f"(seq (seq {produce(tile, stop=128)} {produce(tile, start=128)}) {consume})"
+    assert len(tl.lower_ir(halves, {}, dtypes)) == 1
     invariant = f"(ploop 0 256 128 c (store {view('output', 'Y')} (relu (load {view('input', 'X')} {full})) {full}))"
     assert len(tl.lower_ir(invariant, {}, dtypes)) == 1

@@ -8,8 +8,10 @@
 //   4. gather:   for each peer q, wait for q's `reduced`, copy slice q from q's buffer
 //   5. retire:   last CTA writes `done` on every peer and waits for every peer's `done`, so no
 //                rank can start overwriting its buffer while another still reads it
-// Flags carry the call's epoch and are never reset.  Every wait is bounded; on expiry the
-// device status word is set and the CTA returns.
+// Flags carry the call's epoch (never 0: a zeroed pad reads as epoch 0) and are never reset.
+// Every wait is bounded; on expiry the device status word is set, the CTA stops moving data
+// and the call publishes nothing further.  The pad's first 64 words belong to this kernel; the
+// fused GEMM epilogue keeps its flags behind them, so one pad serves both.
 //
 // NVLink traffic per rank: (world-1)/world * bytes pulled in the reduce step and the same again
 // in the gather step.
@@ -20,9 +22,10 @@ namespace trinity_sm100 {
 namespace {
 
 constexpr int kMaxWorld = 8;
-constexpr int kFlagWords = 64;  // ready[8] reduced[8] done[8] counters[2] + padding
-constexpr int kOffReady = 0, kOffReduced = 8, kOffDone = 16, kOffCounter = 24;
+constexpr int kFlagWords = 64;  // ready[8] reduced[8] done[8] counters[2] failed + padding
+constexpr int kOffReady = 0, kOffReduced = 8, kOffDone = 16, kOffCounter = 24, kOffFailed = 26;
 constexpr int kArThreads = 512;
+static_assert(kGemmFlagOffset == kFlagWords, "the fused GEMM epilogue's flags start behind this kernel's");
 
 struct AllReduceParams {
   uint4* buffers[kMaxWorld];
@@ -45,6 +48,10 @@ allreduce_two_shot_kernel(const AllReduceParams p) {
   __shared__ int s_last;
   uint32_t* my_flags = p.flags[p.rank];
   const int tid = threadIdx.x;
+  // A CTA whose wait gave up moves no more data but still takes part in both counters, so the
+  // counters are back at zero for the next call on this pad; it marks the call as failed
+  // (kOffFailed = epoch) and the last CTA then publishes nothing, so the peers' waits run out as
+  // well and every rank's status word reports the failure.
 
   // 1. announce
   if (blockIdx.x == 0 && tid < p.world) {
@@ -58,42 +65,50 @@ allreduce_two_shot_kernel(const AllReduceParams p) {
     if (!wait_flag(my_flags + kOffReady + tid, p.epoch, 0x701)) s_ok = 0;
   }
   __syncthreads();
-  if (!s_ok) return;
+  bool ok = s_ok != 0;
   long long lo, hi;
-  slice_range(p.vectors, p.world, p.rank, lo, hi);
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = lo + static_cast<long long>(blockIdx.x) * blockDim.x + tid; i < hi;
-       i += stride) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    uint4 v[kMaxWorld];
+  if (ok) {
+    slice_range(p.vectors, p.world, p.rank, lo, hi);
+    for (long long i = lo + static_cast<long long>(blockIdx.x) * blockDim.x + tid; i < hi;
+         i += stride) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      uint4 v[kMaxWorld];
 #pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r)
-      if (r < p.world) v[r] = peer_load(p.buffers[r] + i);
+      for (int r = 0; r < kMaxWorld; ++r)
+        if (r < p.world) v[r] = peer_load(p.buffers[r] + i);
 #pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r) {
-      if (r < p.world) {
-        const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+      for (int r = 0; r < kMaxWorld; ++r) {
+        if (r < p.world) {
+          const uint32_t w[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          acc[2 * e] += bf16_lo(w[e]);
-          acc[2 * e + 1] += bf16_hi(w[e]);
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] += bf16_lo(w[e]);
+            acc[2 * e + 1] += bf16_hi(w[e]);
+          }
         }
       }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      p.buffers[p.rank][i] = o;
     }
-    uint4 o;
-    o.x = pack_bf16x2(acc[0], acc[1]);
-    o.y = pack_bf16x2(acc[2], acc[3]);
-    o.z = pack_bf16x2(acc[4], acc[5]);
-    o.w = pack_bf16x2(acc[6], acc[7]);
-    p.buffers[p.rank][i] = o;
   }
   // 3. publish once every CTA of this rank has stored its part of the slice
   __threadfence_system();
   __syncthreads();
   if (tid == 0) {
+    if (!ok) atomicExch(my_flags + kOffFailed, p.epoch);
+    __threadfence();
     const unsigned prev = atomicAdd(my_flags + kOffCounter, 1u);
     s_last = (prev == gridDim.x - 1);
-    if (s_last) my_flags[kOffCounter] = 0;
+    if (s_last) {
+      my_flags[kOffCounter] = 0;
+      __threadfence();
+      if (*reinterpret_cast<volatile uint32_t*>(my_flags + kOffFailed) == p.epoch) s_last = 0;
+    }
   }
   __syncthreads();
   if (s_last && tid < p.world) {
@@ -101,11 +116,13 @@ allreduce_two_shot_kernel(const AllReduceParams p) {
     flag_store(p.flags[tid] + kOffReduced + p.rank, p.epoch);
   }
   // 4. gather the other slices
-  for (int step = 1; step < p.world; ++step) {
+  for (int step = 1; step < p.world && ok; ++step) {
     const int q = (p.rank + step) % p.world;
+    __syncthreads();
     if (tid == 0 && !wait_flag(my_flags + kOffReduced + q, p.epoch, 0x702)) s_ok = 0;
     __syncthreads();
-    if (!s_ok) return;
+    ok = s_ok != 0;
+    if (!ok) break;
     slice_range(p.vectors, p.world, q, lo, hi);
     for (long long i = lo + static_cast<long long>(blockIdx.x) * blockDim.x + tid; i < hi;
          i += stride)
@@ -114,10 +131,15 @@ allreduce_two_shot_kernel(const AllReduceParams p) {
   // 5. retire
   __syncthreads();
   if (tid == 0) {
+    if (!ok) atomicExch(my_flags + kOffFailed, p.epoch);
     __threadfence();
     const unsigned prev = atomicAdd(my_flags + kOffCounter + 1, 1u);
     s_last = (prev == gridDim.x - 1);
-    if (s_last) my_flags[kOffCounter + 1] = 0;
+    if (s_last) {
+      my_flags[kOffCounter + 1] = 0;
+      __threadfence();
+      if (*reinterpret_cast<volatile uint32_t*>(my_flags + kOffFailed) == p.epoch) s_last = 0;
+    }
   }
   __syncthreads();
   if (s_last && tid < p.world) {
@@ -141,6 +163,8 @@ extern "C" int trinity_sm100_allreduce_bf16(const trinity_sm100_allreduce* args,
   if (a.world < 1 || a.world > kMaxWorld || a.rank < 0 || a.rank >= a.world)
     return fail(TRINITY_SM100_E_INVALID, "allreduce: world %d / rank %d out of range", a.world,
                 a.rank);
+  if (a.epoch == 0)
+    return fail(TRINITY_SM100_E_INVALID, "allreduce: epoch 0 is what a fresh flag pad holds; start at 1");
   if (a.rows <= 0 || a.cols <= 0 || a.cols % 8)
     return fail(TRINITY_SM100_E_INVALID, "allreduce: rows > 0, cols a positive multiple of 8");
   AllReduceParams p;

@@ -32,6 +32,9 @@ constexpr int kStagingBytes = 4 * 2 * kStoreBufBytes;
 
 // Peer-mapped output buffers and flag pads for the fused all-reduce epilogue.
 constexpr int kGemmMaxWorld = 8;
+// The first words of a flag pad belong to the plain all-reduce kernel (allreduce.cu); the fused
+// epilogue's flags start behind them so that one pad can serve both kernels in turn.
+constexpr int kGemmFlagOffset = 64;
 struct GemmPeers {
   uint4* buffers[kGemmMaxWorld];   // the [M,N] BF16 output on every rank (buffers[rank] is local)
   uint32_t* flags[kGemmMaxWorld];  // flag pads: ready[tile][source rank], done[rank], counter
@@ -505,6 +508,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
+// Shared-memory opt-in of one instantiation, once per device.
+template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false>
+int opt_in_gemm() {
+  static unsigned long long configured = 0;
+  return opt_in_shared_memory(
+      reinterpret_cast<const void*>(&gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched>),
+      gemm_smem_bytes<kBN, kStages>(), &configured, "gemm");
+}
+
 template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false>
 int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, const GemmPeers* fused = nullptr,
                 const trinity_sm100_gemm_batch* batch = nullptr) {
@@ -512,16 +524,7 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
   constexpr int kSmem = gemm_smem_bytes<kBN, kStages>();
   static_assert(kSmem <= 232448, "exceeds the 227 KB shared-memory limit");
   auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched>;
-  static bool configured[64] = {};
-  int device = 0;
-  cudaGetDevice(&device);
-  if (!configured[device & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (e != cudaSuccess)
-      return fail(TRINITY_SM100_E_CUDA, "gemm: shared memory opt-in (%d B): %s", kSmem,
-                  cudaGetErrorString(e));
-    configured[device & 63] = true;
-  }
+  if (int rc = opt_in_gemm<kBN, kStages, kGated, kOutF32, kFused, kBatched>()) return rc;
   CUtensorMap map_a, map_b, map_b2, map_out;
   int rc;
   const int out_bytes = kOutF32 ? 4 : 2;
@@ -584,6 +587,22 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
 }
 
 }  // namespace
+
+int gemm_prepare_device() {
+  // every instantiation an entry point can select
+  int rc = 0;
+#define TRINITY_OPT_IN(...) if (!rc) rc = opt_in_gemm<__VA_ARGS__>();
+  TRINITY_OPT_IN(256, 4, true, true) TRINITY_OPT_IN(256, 4, true, false)
+  TRINITY_OPT_IN(256, 4, false, true) TRINITY_OPT_IN(256, 4, false, false)
+  TRINITY_OPT_IN(128, 6, false, true) TRINITY_OPT_IN(128, 6, false, false)
+  TRINITY_OPT_IN(64, 8, false, true) TRINITY_OPT_IN(64, 8, false, false)
+  TRINITY_OPT_IN(256, 4, false, true, false, true) TRINITY_OPT_IN(256, 4, false, false, false, true)
+  TRINITY_OPT_IN(128, 6, false, true, false, true) TRINITY_OPT_IN(128, 6, false, false, false, true)
+  TRINITY_OPT_IN(64, 8, false, true, false, true) TRINITY_OPT_IN(64, 8, false, false, false, true)
+  TRINITY_OPT_IN(256, 4, false, false, true)
+#undef TRINITY_OPT_IN
+  return rc;
+}
 }  // namespace trinity_sm100
 
 using namespace trinity_sm100;
@@ -697,7 +716,7 @@ extern "C" int trinity_sm100_gemm_batched_bf16(const trinity_sm100_gemm* args,
 extern "C" size_t trinity_sm100_gemm_allreduce_flag_words(int64_t m, int64_t n, int32_t world) {
   if (m <= 0 || n <= 0 || world <= 0) return 0;
   const size_t tiles = size_t((m + kBM - 1) / kBM) * size_t((n + 255) / 256);
-  return tiles * size_t(world) + kGemmMaxWorld + 8;
+  return kGemmFlagOffset + tiles * size_t(world) + kGemmMaxWorld + 8;
 }
 
 extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
@@ -725,8 +744,10 @@ extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
     if (!r.peers[i] || !r.flags[i] || !aligned16(r.peers[i]) || !aligned16(r.flags[i]))
       return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: peer %d pointer null or misaligned", i);
     peers.buffers[i] = static_cast<uint4*>(r.peers[i]);
-    peers.flags[i] = static_cast<uint32_t*>(r.flags[i]);
+    peers.flags[i] = static_cast<uint32_t*>(r.flags[i]) + kGemmFlagOffset;
   }
+  if (r.epoch == 0)
+    return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: epoch 0 is what a fresh flag pad holds; start at 1");
   if (r.peers[r.rank] != g.out)
     return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: out must be this rank's entry of the peer table");
   if (!aligned16(g.a) || !aligned16(g.b)) return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: operands must be 16-byte aligned");

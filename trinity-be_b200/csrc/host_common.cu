@@ -74,6 +74,23 @@ int require_sm100(int* sm_count) {
   return 0;
 }
 
+int opt_in_shared_memory(const void* kernel, int bytes, unsigned long long* done_mask, const char* what) {
+  static std::mutex mutex;
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= 64) return fail(TRINITY_SM100_E_DEVICE, "device index %d", device);
+  const unsigned long long bit = 1ull << device;
+  if (__atomic_load_n(done_mask, __ATOMIC_ACQUIRE) & bit) return 0;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (*done_mask & bit) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess)
+    return fail(TRINITY_SM100_E_CUDA, "%s: shared memory opt-in (%d B): %s", what, bytes, cudaGetErrorString(e));
+  __atomic_fetch_or(done_mask, bit, __ATOMIC_RELEASE);
+  return 0;
+}
+
 void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int check_launch(const char* what) {
@@ -142,6 +159,15 @@ extern "C" int trinity_sm100_device_status(uint32_t* status, int clear) {
     if (e != cudaSuccess)
       return fail(TRINITY_SM100_E_CUDA, "clearing device status: %s", cudaGetErrorString(e));
   }
+  return 0;
+}
+
+extern "C" int trinity_sm100_set_wait_budget(uint64_t cycles) {
+  long long value = cycles == 0 ? kDefaultWaitBudgetCycles
+                                : (cycles > uint64_t(INT64_MAX) ? INT64_MAX : static_cast<long long>(cycles));
+  cudaError_t e = cudaMemcpyToSymbol(g_wait_budget_cycles, &value, sizeof(value));
+  if (e != cudaSuccess)
+    return fail(TRINITY_SM100_E_CUDA, "setting the wait budget: %s", cudaGetErrorString(e));
   return 0;
 }
 

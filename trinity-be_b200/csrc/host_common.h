@@ -21,6 +21,16 @@ void count_launch(unsigned n = 1);
 // Checks cudaGetLastError() after a launch; `what` names the kernel.
 int check_launch(const char* what);
 
+// Opts `kernel` into `bytes` of dynamic shared memory on the current device, once per device:
+// bit d of `*done_mask` records that device d has it.  Safe to call from several threads.
+int opt_in_shared_memory(const void* kernel, int bytes, unsigned long long* done_mask, const char* what);
+
+// Per-device set-up that trinity_sm100_prepare_device runs so that later launches (possibly under
+// stream capture) make no attribute or symbol-address calls: the kernels' shared-memory opt-ins
+// and the device address of the built-in MLA scratch array.
+int gemm_prepare_device();
+int mla_prepare_device();
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // 2-D tiled tensor map over a row-major matrix: `inner` contiguous elements per row,

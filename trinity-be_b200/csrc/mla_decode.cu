@@ -89,33 +89,6 @@ struct MlaParams {
   int negate;         // scale < 0: the query's sign is flipped on its way into TMEM
 };
 
-// Optional per-phase cycle counters of the softmax loop: a tuning harness that defines
-// TRINITY_MLA_TIMING reads g_mla_ticks; the library build compiles the hooks away.
-#ifdef TRINITY_MLA_TIMING
-__device__ unsigned long long g_mla_ticks[40];
-__device__ __forceinline__ unsigned long long mla_now_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// wall-clock stamps (ns) of one CTA's milestones
-#define TRINITY_MLA_STAMP(i) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) g_mla_ticks[24 + (i)] = mla_now_ns();
-#define TRINITY_MLA_TICK_DECL long long tick_last = clock64(); unsigned long long tick_sum[12] = {};
-#define TRINITY_MLA_TICK(i) { const long long now = clock64(); tick_sum[i] += now - tick_last; tick_last = now; }
-#define TRINITY_MLA_TICK_FLUSH if (blockIdx.z == 0 && blockIdx.y == 0 && blockIdx.x == 0 && threadIdx.x == 64) { for (int i = 0; i < 12; ++i) g_mla_ticks[i] = tick_sum[i]; }
-#define TRINITY_MLA_ISSUER_DECL long long issuer_last = clock64(); unsigned long long issuer_sum[5] = {}; int why = 1;
-#define TRINITY_MLA_ISSUER_TICK(i) { const long long now = clock64(); issuer_sum[i] += now - issuer_last; issuer_last = now; }
-#define TRINITY_MLA_ISSUER_FLUSH if (blockIdx.z == 0 && blockIdx.y == 0 && blockIdx.x == 0) { for (int i = 0; i < 5; ++i) g_mla_ticks[16 + i] = issuer_sum[i]; }
-#else
-#define TRINITY_MLA_STAMP(i)
-#define TRINITY_MLA_ISSUER_DECL
-#define TRINITY_MLA_ISSUER_TICK(i)
-#define TRINITY_MLA_ISSUER_FLUSH
-#define TRINITY_MLA_TICK_DECL
-#define TRINITY_MLA_TICK(i)
-#define TRINITY_MLA_TICK_FLUSH
-#endif
-
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -217,7 +190,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait_cluster(bar, parity)) return true;
-    if (clock64() - start > kWaitBudgetCycles) {
+    if (clock64() - start > wait_budget()) {
       report_timeout(site);
       return false;
     }
@@ -331,7 +304,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) { TRINITY_MLA_STAMP(0) }
   const uint32_t half = cluster_rank();   // latent half and rope half owned by this CTA
   const uint32_t peer = half ^ 1u;
 
@@ -371,7 +343,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   Segment seg;
-  if (threadIdx.x == 0) { TRINITY_MLA_STAMP(1) }
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -457,20 +428,14 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     {
       constexpr uint32_t kIdescQK = umma_idesc_bf16(128, kKv, 0, 0);
       const uint32_t d_scores = tmem_base + kColS, a_query = tmem_base + kColQ;
-      TRINITY_MLA_ISSUER_DECL
       int g = 0;
       bool ok = true;
       for (int si = 0; ok && get_segment(p, si, seg); ++si) {
         ok = __all_sync(0xffffffffu, mbar_wait(q_tmem, si & 1u, 0x502));
-        if (si == 0 && lane == 0) { TRINITY_MLA_STAMP(8) }
         for (int j = 0; ok && j < seg.num_chunks; ++j, ++g) {
-          TRINITY_MLA_ISSUER_TICK(3)
           if (g > 0) ok = __all_sync(0xffffffffu, mbar_wait(s_free, (g - 1) & 1u, 0x505));
-          TRINITY_MLA_ISSUER_TICK(0)
           if (ok) ok = __all_sync(0xffffffffu, mbar_wait(kv_full(g % kKvStages), (g / kKvStages) & 1u, 0x503));
           if (!ok) break;
-          TRINITY_MLA_ISSUER_TICK(1)
-          if (g == 0 && lane == 0) { TRINITY_MLA_STAMP(2) }
           tc_fence_after();
           // 16 K-steps over the latent boxes and 2 over the rope box, the query always from TMEM
           const uint32_t stage = kv_smem + (g % kKvStages) * kStageBytes;
@@ -494,8 +459,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           __syncwarp();
         }
       }
-      TRINITY_MLA_ISSUER_TICK(3)
-      if (lane == 0) { TRINITY_MLA_ISSUER_FLUSH }
     }
   } else if (warp == 2 + kSoftmaxWarps) {
     // ------------------------------------------------------------ value MMA issuer
@@ -512,10 +475,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         for (int j = 0; ok && j < seg.num_chunks; ++j, ++g) {
           ok = __all_sync(0xffffffffu, mbar_wait(p_full, g & 1u, 0x504));
           if (!ok) break;
-          if (lane == 0) {
-            if (g == 0) { TRINITY_MLA_STAMP(3) }
-            if (j == seg.num_chunks - 1) { TRINITY_MLA_STAMP(4) }
-          }
           tc_fence_after();
           const int s = g % kKvStages;
           const uint64_t values = umma_smem_desc(kv_smem + s * kStageBytes, kBoxBytes, 1024);
@@ -545,7 +504,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
     // together at the next vote, so no barrier or collective is ever left half-attended.
     bool bad = false;
     int gbase = 0;   // chunks of earlier segments
-    TRINITY_MLA_TICK_DECL
 
     for (int si = 0; get_segment(p, si, seg); ++si) {
       const int num_chunks = seg.num_chunks;
@@ -610,7 +568,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (threadIdx.x == 64 && si == 0) { TRINITY_MLA_STAMP(9) }
         if (lane == 0) mbar_arrive(q_tmem);
       }
 
@@ -625,9 +582,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         uint4* staged = reinterpret_cast<uint4*>(send + buf * kXchgBytes);
         const uint4* received = reinterpret_cast<const uint4*>(xchg + buf * kXchgBytes);
         // ---- partial scores of this CTA's feature half: TMEM -> registers
-        TRINITY_MLA_TICK(0)
         if (!bad) bad = !mbar_wait(s_full(g), group_phase(g), 0x601);
-        TRINITY_MLA_TICK(1)
         tc_fence_after();
         float t[64];
         {
@@ -644,7 +599,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         // the scores are in registers: later score MMAs may overwrite the buffer
         tc_fence_before();
         if (__all_sync(0xffffffffu, !bad) && lane == 0) mbar_arrive(s_free);
-        TRINITY_MLA_TICK(2)
         // ---- FP16 copy for the peer: [8 groups of 8 positions][128 rows] (conflict-free), then
         //      one thread starts the bulk asynchronous copy into the peer's receive tile.
         // The buffers were last used for chunk g-2, by another group.  Once that group has read
@@ -654,7 +608,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           const unsigned target = 4u * unsigned(g >> 1);
           const long long start = clock64();
           while (read_count[buf] < target) {
-            if (clock64() - start > kWaitBudgetCycles) {
+            if (clock64() - start > wait_budget()) {
               report_timeout(0x607);
               bad = true;
               break;
@@ -662,7 +616,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           }
         }
         if (!bad) bad = !mbar_wait_cluster(x_empty(buf), phase ^ 1u, 0x604);
-        TRINITY_MLA_TICK(3)
         if (!bad) {
 #pragma unroll
           for (int q8 = 0; q8 < 8; ++q8) {
@@ -699,10 +652,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
                 "r"(kXchgBytes), "r"(map_to_peer(x_full(buf), peer))
               : "memory");
         }
-        TRINITY_MLA_TICK(4)
         // ---- the peer's half of the scores
         if (!bad) bad = !mbar_wait_cluster(x_full(buf), phase, 0x605);
-        TRINITY_MLA_TICK(5)
 #pragma unroll
         for (int q8 = 0; q8 < 8; ++q8) {
           const uint4 other = received[q8 * 128 + row];
@@ -736,7 +687,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         }
         // position 0 of a chunk is always inside seq, so the maximum is finite
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-        TRINITY_MLA_TICK(6)
         // ---- reference maximum: take it over from the group that had chunk j-1, pass it on
         float m_prev = -INFINITY;
         if (j > 0) {
@@ -776,7 +726,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           sum4[0] = tail; sum4[1] = 0.0f; sum4[2] = 0.0f; sum4[3] = 0.0f;
         }
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        TRINITY_MLA_TICK(7)
         // Neither the probability buffer nor the accumulator may be touched before the value MMAs
         // of chunk j-1 have finished with them.  (For a segment's first chunk the previous
         // segment's epilogue has waited for them.)
@@ -800,9 +749,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         tc_fence_before();
         const bool warp_good = __all_sync(0xffffffffu, !bad);
         if (lane == 0 && warp_good) mbar_arrive(p_full);
-        TRINITY_MLA_TICK(8)
       }
-      if (si == 0) { TRINITY_MLA_TICK_FLUSH }
 
       // Every softmax thread comes here, also after a failure.  The final reference maximum of
       // a head was written by the group that had the segment's last chunk.
@@ -813,7 +760,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
       if (m_l != m_final) l *= fast_exp2(m_l - m_final);   // a group without chunks holds l = 0
       l_part[group * 128 + row] = l;
       if (ready) ready = mbar_wait(pv_done(g_last), group_phase(g_last), 0x603);
-      if (threadIdx.x == 64) { TRINITY_MLA_STAMP(5) }
       asm volatile("bar.sync 4, %0;" ::"n"(kSoftmaxThreads) : "memory");
       l = 0.0f;
 #pragma unroll
@@ -864,7 +810,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
           if (live && group == 0) p.partial_lse[slot * 2 + half] = m_final + log2f(l);
         }
       }
-      if (threadIdx.x == 64) { TRINITY_MLA_STAMP(6) }
       // the accumulator has been read: the next segment's values may overwrite it
       tc_fence_before();
       __syncwarp();
@@ -879,7 +824,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();
-  if (threadIdx.x == 0) { TRINITY_MLA_STAMP(7) }
   if (warp == 2) {
     if (g_device_status != 0)
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -1039,6 +983,11 @@ Schedule choose_schedule(int batch, int seq, int kv_splits) {
   return s;
 }
 
+int opt_in_mla() {
+  static unsigned long long configured = 0;
+  return opt_in_shared_memory(reinterpret_cast<const void*>(&mla_decode_kernel), kMlaSmem, &configured, "mla");
+}
+
 }  // namespace
 }  // namespace trinity_sm100
 
@@ -1125,16 +1074,7 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   }
   if (int rc = require_sm100(nullptr)) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
-  static bool configured[64] = {};
-  int device = 0;
-  cudaGetDevice(&device);
-  if (!configured[device & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(mla_decode_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem);
-    if (e != cudaSuccess)
-      return fail(TRINITY_SM100_E_CUDA, "mla: shared memory opt-in: %s", cudaGetErrorString(e));
-    configured[device & 63] = true;
-  }
+  if (int rc = opt_in_mla()) return rc;
   // Two views of the cache: 64-feature boxes (128-byte swizzle) for the latent part and
   // 32-feature boxes (64-byte swizzle) for each CTA's half of the rope part.
   CUtensorMap map_cache, map_rope;
@@ -1241,6 +1181,12 @@ int static_scratch_address(void** address) {
 }
 }  // namespace
 
+int trinity_sm100::mla_prepare_device() {
+  if (int rc = opt_in_mla()) return rc;
+  void* scratch = nullptr;
+  return static_scratch_address(&scratch);
+}
+
 extern "C" int trinity_sm100_mla_decode_bf16_noalloc(const trinity_sm100_mla* args,
                                                      void* stream_handle) {
   if (!args) return fail(TRINITY_SM100_E_INVALID, "mla (no-alloc): null argument block");
@@ -1253,8 +1199,9 @@ extern "C" int trinity_sm100_mla_decode_bf16_noalloc(const trinity_sm100_mla* ar
   const int chunks = (call.seq + kKv - 1) / kKv;
   if (splits > chunks) splits = chunks;
   size_t need = scratch_bytes(call.batch, call.heads, call.d_v, splits);
-  if (call.kv_splits <= 0 && need > size_t(TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES)) {
-    // The automatic schedule's partials do not fit: take the most equal splits that do.
+  if (call.kv_splits == 0 && need > size_t(TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES)) {
+    // The schedule was left to the library and its first choice does not fit: take the most
+    // equal splits that do.  A caller that fixed the schedule (kv_splits != 0) is refused below.
     while (splits > 1 && scratch_bytes(call.batch, call.heads, call.d_v, splits) >
                              size_t(TRINITY_SM100_MLA_STATIC_SCRATCH_BYTES))
       --splits;

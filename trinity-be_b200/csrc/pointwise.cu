@@ -245,6 +245,8 @@ extern "C" int trinity_sm100_prepare_device(int32_t* device_index) {
   if (e == cudaSuccess) e = cudaGetDevice(&device);
   if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "prepare: %s", cudaGetErrorString(e));
   if (int rc = require_sm100(nullptr)) return rc;
+  if (int rc = gemm_prepare_device()) return rc;
+  if (int rc = mla_prepare_device()) return rc;
   if (device_index) *device_index = device;
   return 0;
 }

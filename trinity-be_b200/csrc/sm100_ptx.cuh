@@ -15,8 +15,14 @@ namespace trinity_sm100 {
 // built as one translation unit, so this header holds the single definition.
 __device__ unsigned int g_device_status = 0;
 
-// Budget for one wait, in SM clock cycles (about two seconds at 2 GHz).
-constexpr long long kWaitBudgetCycles = 4000000000LL;
+// Budget for one wait, in SM clock cycles: about two seconds at 2 GHz unless the host has set
+// another one for this device (trinity_sm100_set_wait_budget), which a test of the give-up path
+// does.  Kernels read it only after a wait has already spun for a while.
+constexpr long long kDefaultWaitBudgetCycles = 4000000000LL;
+__device__ long long g_wait_budget_cycles = kDefaultWaitBudgetCycles;
+__device__ __forceinline__ long long wait_budget() {
+  return *reinterpret_cast<volatile long long*>(&g_wait_budget_cycles);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -76,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - start > kWaitBudgetCycles) {
+    if (clock64() - start > wait_budget()) {
       report_timeout(site);
       return false;
     }
@@ -258,7 +264,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t epoch, uin
       if (reached(flag_load(p), epoch)) return true;
       __nanosleep(64);
     }
-    if (clock64() - start > kWaitBudgetCycles) {
+    if (clock64() - start > wait_budget()) {
       report_timeout(site);
       return false;
     }

@@ -15,6 +15,7 @@
 // proven disjoint"), and a read of an intermediate tensor beyond what earlier kernels wrote
 // ("not covered").  The interval reasoning is per axis over tile / elem / fulltile indices with
 // numeric loop bounds; any other index form is taken as covering.
+#include <algorithm>
 #include <functional>
 
 #include "plan.hpp"
@@ -252,6 +253,10 @@ struct Reader {
     for (auto& read : t.accesses) {
       if (read.write || !read.known) continue;
       bool produced_here = false, covered = false, any_earlier = false;
+      // Earlier exact writes as boxes; two boxes that agree on every axis but one and touch or
+      // overlap on that axis are one box (halves of a tensor, rows of tiles written by several
+      // kernels), merged until nothing changes.
+      std::vector<std::vector<std::pair<int64_t, int64_t>>> boxes;
       for (auto& w : t.accesses) {
         if (!w.write) continue;
         if (w.kernel == read.kernel) produced_here = true;
@@ -259,10 +264,32 @@ struct Reader {
         any_earlier = true;
         if (!w.known) { covered = true; break; }
         if (!w.exact || w.range.size() != read.range.size()) continue;
+        boxes.emplace_back(w.range.begin(), w.range.end());
+      }
+      for (bool merged = true; merged && !covered;) {
+        merged = false;
+        for (size_t i = 0; i < boxes.size() && !merged; ++i)
+          for (size_t j = i + 1; j < boxes.size() && !merged; ++j) {
+            int differing = -1, count = 0;
+            for (size_t axis = 0; axis < boxes[i].size(); ++axis)
+              if (boxes[i][axis] != boxes[j][axis]) { differing = int(axis); ++count; }
+            if (count == 0) { boxes.erase(boxes.begin() + j); merged = true; break; }
+            if (count != 1) continue;
+            auto& a = boxes[i][differing];
+            const auto& b = boxes[j][differing];
+            if (b.first > a.second || a.first > b.second) continue;   // a gap between them
+            a.first = std::min(a.first, b.first);
+            a.second = std::max(a.second, b.second);
+            boxes.erase(boxes.begin() + j);
+            merged = true;
+          }
+      }
+      for (auto& box : boxes) {
+        if (covered) break;
         bool inside = true;
-        for (size_t axis = 0; axis < w.range.size(); ++axis)
-          if (read.range[axis].first < w.range[axis].first || read.range[axis].second > w.range[axis].second) inside = false;
-        if (inside) { covered = true; break; }
+        for (size_t axis = 0; axis < box.size(); ++axis)
+          if (read.range[axis].first < box[axis].first || read.range[axis].second > box[axis].second) inside = false;
+        if (inside) covered = true;
       }
       if (produced_here || covered) continue;   // accumulators and in-kernel values are the planner's business
       if (any_earlier)

@@ -299,7 +299,10 @@ void Execution::run(void* stream_handle) {
   if (rc) {
     failed_ = true;
     failure_ = info;
-    if (info.submitted && !capturing) {
+    // One entry point may launch several kernels and fail after the first, so work can be in
+    // flight whatever `submitted` says: the tail is recorded on every failure outside a capture
+    // (as src/native/runtime.cpp:232-238 does) and close() then waits for it.
+    if (!capturing) {
       cudaEventRecord(tail_, stream);
       recorded_ = true;
       last_stream_ = stream;

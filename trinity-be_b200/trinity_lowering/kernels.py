@@ -38,6 +38,7 @@ EXPORTS = (
     "trinity_sm100_current_device",
     "trinity_sm100_stream_synchronize",
     "trinity_sm100_device_status",
+    "trinity_sm100_set_wait_budget",
     "trinity_sm100_abi_version",
     "trinity_sm100_last_error",
     "trinity_sm100_launch_count",
@@ -128,6 +129,7 @@ def library():
                 ctypes.POINTER(GemmArgs), ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
             lib.trinity_sm100_device_status.argtypes = [
                 ctypes.POINTER(ctypes.c_uint32), ctypes.c_int]
+            lib.trinity_sm100_set_wait_budget.argtypes = [ctypes.c_uint64]
             lib.trinity_sm100_last_error.restype = ctypes.c_char_p
             lib.trinity_sm100_launch_count.restype = ctypes.c_uint64
             _lib = lib
@@ -158,6 +160,12 @@ def device_status(clear=False):
     value = ctypes.c_uint32(0)
     _check(library().trinity_sm100_device_status(ctypes.byref(value), int(clear)))
     return value.value
+
+
+def set_wait_budget(cycles):
+    """Budget of every bounded in-kernel wait on the current device, in SM clock cycles
+    (0 restores the default of about two seconds)."""
+    _check(library().trinity_sm100_set_wait_budget(int(cycles)))
 
 
 def gemm(a, b, *, bias=None, bias_mode=None, activation=ACT_NONE, b2=None, out=None,

@@ -11,13 +11,18 @@ python/src/trinity_lowering/world.py) without NVSHMEM:
 * data plane (needs GPUs): buffers from ``torch.distributed._symmetric_memory`` mapped into every
   rank's address space; collectives are this library's own kernels over plain peer loads and
   stores with bounded flag waits (``trinity_sm100_allreduce_bf16``).  NCCL is used only by the
-  symmetric-memory rendezvous, never for the data path.  No multicast object is bound.
+  symmetric-memory rendezvous, never for the data path.  The kernels need no multicast object,
+  and none is bound: TORCH_SYMM_MEM_DISABLE_MULTICAST=1 is set before the first rendezvous (a
+  rank that died while its memory was bound to an NVLink multicast object could fault its peers).
 """
 import os
 import threading
 import time
 
 from .errors import DistributedFailure
+
+# Read by torch's symmetric-memory allocator at its first rendezvous in the process.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 
 class World:
@@ -139,6 +144,7 @@ class World:
     def allocate(self, shape, dtype=None, flag_words=None):
         """A symmetric buffer: same shape on every rank, every rank's copy mapped everywhere.
         ``flag_words`` sizes the flag pad that travels with it (default: the all-reduce kernel's)."""
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch
         import torch.distributed._symmetric_memory as symm
         from . import kernels
