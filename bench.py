@@ -126,12 +126,17 @@ class ClockSampler:
 
 # ---------------------------------------------------------------- parity (float64 on the host)
 def error_figures(actual, expected, rows):
-    """rel-L2 and max-abs of a BF16 result against a float64 expectation of the same rows."""
+    """rel-L2 and max-abs of a BF16 result against a float64 expectation of the same rows.  The
+    max-abs bound is 2e-2 for outputs of order one; where outputs exceed |y| = 4 the rounding of
+    the BF16 result alone is larger than that, and the bound is one BF16 ulp of the largest
+    output (stated in the line as max_abs_bound)."""
     a, e = actual.double(), expected.double()
     rel = ((a - e).norm() / e.norm().clamp_min(1e-300)).item()
     worst = (a - e).abs().max().item()
-    return {"rel_l2": rel, "max_abs": worst, "rows": int(rows),
-            "ok": bool(rel <= REL_L2_BOUND and worst <= MAX_ABS_BOUND)}
+    top = e.abs().max().item()
+    bound = max(MAX_ABS_BOUND, 2.0 ** (math.floor(math.log2(top)) - 7) if top > 0 else 0.0)
+    return {"rel_l2": rel, "max_abs": worst, "max_abs_bound": bound, "rows": int(rows),
+            "ok": bool(rel <= REL_L2_BOUND and worst <= bound)}
 
 
 def sampled_rows(total, count):
@@ -714,9 +719,9 @@ def main():
 
     def worst_parity(figures):
         """The largest errors over the ranks (every rank checks its own shard)."""
-        rel, worst = maximum(figures["rel_l2"], figures["max_abs"])
-        return {"rel_l2": rel, "max_abs": worst, "rows": figures["rows"],
-                "ok": bool(rel <= REL_L2_BOUND and worst <= MAX_ABS_BOUND)}
+        rel, worst, bound = maximum(figures["rel_l2"], figures["max_abs"], figures["max_abs_bound"])
+        return {"rel_l2": rel, "max_abs": worst, "max_abs_bound": bound, "rows": figures["rows"],
+                "ok": bool(rel <= REL_L2_BOUND and worst <= bound)}
 
     w = make_workload(args.workload, device, world_obj, world, rank)
     use_graph = not (w.no_graph or args.no_graph)

@@ -73,7 +73,9 @@ def test_gated_gemm_at_the_per_gpu_shape(mlp_operands):
     hidden = k.gemm(x, wu, b2=wg, activation=k.ACT_SILU_GATE)
     rows = torch.arange(5, x.shape[0], 257)
     expected = wl.gated_oracle(x[rows.to(DEV)].cpu(), wu.cpu(), wg.cpu())
-    assert_close_bf16(hidden[rows.to(DEV)].cpu(), expected, max_ulp=1, max_abs=2e-2)
+    # |up * silu(gate)| reaches ~10, where half a BF16 ulp already exceeds 2e-2: the ulp bound
+    # is the stricter statement here
+    assert_close_bf16(hidden[rows.to(DEV)].cpu(), expected, max_ulp=1)
 
 
 def test_down_gemm_at_the_per_gpu_shape(mlp_operands):
@@ -100,6 +102,6 @@ def test_whole_mlp_on_one_gpu():
     blocks = [wl.gated_oracle(xs, wu[:, c:c + 4096].cpu(), wg[:, c:c + 4096].cpu())
               for c in range(0, d_ff, 4096)]
     hidden = torch.cat(blocks, dim=1)
-    assert_close_bf16(mlp.hidden[rows.to(DEV)].cpu(), hidden, max_ulp=1, max_abs=2e-2)
+    assert_close_bf16(mlp.hidden[rows.to(DEV)].cpu(), hidden, max_ulp=1)
     expected = wl.gemm_oracle(hidden, wd.cpu(), None)
     assert_close_bf16(out[rows.to(DEV)].cpu(), expected, max_ulp=None, max_abs=2e-2)

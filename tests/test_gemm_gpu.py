@@ -42,6 +42,28 @@ def test_dyadic_inputs_are_bit_exact(m, n, k, out_dtype):
         assert torch.equal(out, exact)
 
 
+@pytest.mark.parametrize("m,n,k", [(2309, 2312, 328), (4096, 2560, 64), (2432, 4104, 200)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_dyadic_inputs_on_cta_pairs(m, n, k, out_dtype):
+    """Shapes with at least as many 256 x 256 tiles as SM pairs run on two-CTA clusters (one MMA
+    over both CTAs' shared memory); an odd count of 128-row tiles leaves the last pair with one
+    empty half, ragged edges clip.  Exact operands: any correct kernel matches bit for bit."""
+    a, b = wl.dyadic_gemm_inputs(m, n, k)
+    exact = (a.double() @ b.double()).float().to(out_dtype)
+    for _ in range(2):
+        out = run_gemm(a, b, out_dtype=out_dtype)
+        assert torch.equal(out, exact)
+
+
+def test_gated_form_on_cta_pairs():
+    """In the gated form one CTA of the pair stages the up weight and the other the gate weight."""
+    a, wg, wu, _ = wl.mlp_inputs(2000, 256, 1304, 31)
+    dev = torch.device("cuda:0")
+    out = kernels.gemm(a.to(dev), wu.to(dev), b2=wg.to(dev), activation=kernels.ACT_SILU_GATE)
+    torch.cuda.synchronize()
+    assert_close_bf16(out.cpu(), wl.gated_oracle(a, wu, wg), max_ulp=1)
+
+
 def test_output_outside_the_matrix_is_untouched():
     """Sentinel fill (reference.cu:16,39): only [m,n] of a wider allocation may change."""
     dev = torch.device("cuda:0")

@@ -14,6 +14,14 @@
 //   warps 6-9 only in the row-parallel form with the cross-GPU sum (320 threads): reducers that
 //             add the ranks' partial tiles over NVLink peer memory while the MMAs go on
 //
+//
+// Large problems run on CTA pairs (a cluster of two CTAs, tcgen05 cta_group::2): a pair owns a
+// 256 x 256 output tile, each CTA loads its own 128 rows of A and its own 128 of the 256 B
+// columns (in the gated form one CTA loads the up weight and the other the gate weight), the
+// even CTA issues M=256 MMAs that read both CTAs' shared memory and write each CTA's 128
+// accumulator rows into its own TMEM, and both CTAs run their own epilogue.  A stage is 32 KB
+// per CTA instead of 48, so every SM reads and writes a third less shared memory per FLOP.
+//
 // Algorithmic traffic per launch: (M*K + K*N [+K*N]) * 2 + bias + M*N*out_bytes.
 #include "host_common.h"
 #include "sm100_ptx.cuh"
@@ -31,6 +39,7 @@ constexpr int kStoreBufBytes = 32 * 128;  // 32 rows x 128 B per epilogue warp
 constexpr int kStagingBytes = 4 * 2 * kStoreBufBytes;
 
 // Peer-mapped output buffers and flag pads for the fused all-reduce epilogue.
+constexpr int kPairStages = 6;        // 32 KB stages of a CTA pair
 constexpr int kGemmMaxWorld = 8;
 // The first words of a flag pad belong to the plain all-reduce kernel (allreduce.cu); the fused
 // epilogue's flags start behind them so that one pad can serve both kernels in turn.
@@ -50,6 +59,7 @@ struct GemmParams {
   int activation;
   int m, n, k;
   int tiles_m, tiles_n, num_tiles, num_kb;
+  int flag_tiles;          // 128-row tiles the cross-GPU flags are numbered over (tiles_m rounded up to even)
   // batched form: num_tiles = batch * tiles_per_batch, batch z = tile / tiles_per_batch
   int tiles_per_batch;
   int b_shared;            // one right operand for every batch entry (its map has no batch axis)
@@ -60,23 +70,43 @@ struct GemmParams {
   long long stride_bias;   // elements between the side operands of consecutive batch entries
 };
 
-template <int kBN>
+// In a CTA pair each CTA stages only half of the tile's B columns.
+template <int kBN, bool kPair = false>
 __host__ __device__ constexpr int stage_bytes() {
-  return kStageBytesA + kBK * kBN * 2;
+  return kStageBytesA + kBK * (kPair ? kBN / 2 : kBN) * 2;
 }
-template <int kBN, int kStages>
+template <int kBN, int kStages, bool kPair = false>
 __host__ __device__ constexpr int gemm_smem_bytes() {
-  return 1024 + kStages * stage_bytes<kBN>() + kStagingBytes + 256;
+  return 1024 + kStages * stage_bytes<kBN, kPair>() + kStagingBytes + 256;
 }
 
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m_blk, int& n_blk) {
-  const int group_size = kGroupM * p.tiles_n;
+// Rasterisation: groups of `group_rows` tile rows are walked column by column so that the
+// tiles in flight share B columns in L2.
+__device__ __forceinline__ void tile_coords(int tiles_m, int tiles_n, int group_rows, int tile, int& m_blk,
+                                            int& n_blk) {
+  const int group_size = group_rows * tiles_n;
   const int group = tile / group_size;
-  const int first_m = group * kGroupM;
-  const int rows_in_group = min(kGroupM, p.tiles_m - first_m);
+  const int first_m = group * group_rows;
+  const int rows_in_group = min(group_rows, tiles_m - first_m);
   const int local = tile - group * group_size;
   m_blk = first_m + local % rows_in_group;
   n_blk = local / rows_in_group;
+}
+
+// Where unit `unit` of the persistent loop lies: a 128-row tile, or in pair mode a pair of
+// vertically adjacent 128-row tiles of which CTA `rank` takes the `rank`-th.  `flag_tile` numbers
+// the 128-row tiles for the cross-GPU flags (the same on every GPU).
+template <bool kPair>
+__device__ __forceinline__ void locate_tile(const GemmParams& p, int unit, uint32_t rank, int& m_blk, int& n_blk,
+                                            int& flag_tile) {
+  if (kPair) {
+    tile_coords((p.tiles_m + 1) / 2, p.tiles_n, kGroupM / 2, unit, m_blk, n_blk);
+    m_blk = m_blk * 2 + int(rank);
+    flag_tile = unit * 2 + int(rank);
+  } else {
+    tile_coords(p.tiles_m, p.tiles_n, kGroupM, unit, m_blk, n_blk);
+    flag_tile = unit;
+  }
 }
 
 __device__ __forceinline__ float apply_activation(float x, int activation) {
@@ -166,7 +196,8 @@ __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const Gem
   return true;
 }
 
-template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false>
+template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false,
+          bool kPair = false>
 __global__ void __launch_bounds__(kFused ? kGemmFusedThreads : kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b,
@@ -174,13 +205,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_out, const GemmParams p,
                          const GemmPeers peers) {
   constexpr int kOutN = kGated ? kBN / 2 : kBN;      // output columns per tile
-  constexpr int kStage = stage_bytes<kBN>();
-  constexpr int kChunksB = kBN / 64;                 // 64-column TMA boxes per stage
+  constexpr int kStage = stage_bytes<kBN, kPair>();
+  constexpr int kChunksB = (kPair ? kBN / 2 : kBN) / 64;   // 64-column TMA boxes this CTA loads per stage
   constexpr uint32_t kTmemCols = 2 * kBN;            // double-buffered accumulator
-  constexpr uint32_t kIdesc = umma_idesc_bf16(kBM, kBN, 0, 1);
+  constexpr uint32_t kIdesc = umma_idesc_bf16(kPair ? 2 * kBM : kBM, kBN, 0, 1);
   static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512,
                 "TMEM allocation must be a power of two");
   static_assert(!(kBatched && (kFused || kGated)), "the batched form is the plain GEMM + epilogue");
+  static_assert(!(kPair && kBatched) && (!kPair || kBN == 256), "pairs work on 256 x 256 tiles of one matrix");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -198,6 +230,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // Pair mode: CTA 0 of the cluster issues the MMAs; its `full` barriers count the bytes of both
+  // CTAs' loads and its `tmem_empty` barriers the epilogue warps of both CTAs.
+  const uint32_t rank = kPair ? cluster_rank() : 0u;
+  const int first_unit = kPair ? int(blockIdx.x >> 1) : int(blockIdx.x);
+  const int unit_stride = kPair ? int(gridDim.x >> 1) : int(gridDim.x);
+  const int num_units = kPair ? ((p.tiles_m + 1) / 2) * p.tiles_n : p.num_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -206,7 +244,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 4);
+      mbar_init(tmem_empty_bar(a), kPair ? 8 : 4);
     }
     mbar_fence_init();
     tma_prefetch_desc(&map_a);
@@ -215,11 +253,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     tma_prefetch_desc(&map_out);
   }
   if (warp == 2) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
-    tmem_relinquish();
+    if (kPair) {
+      tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();   // the other CTA's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -228,19 +272,32 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-        int m_blk, n_blk;
+      for (int tile = first_unit; tile < num_units && ok; tile += unit_stride) {
+        int m_blk, n_blk, flag_tile;
         const int z = kBatched ? tile / p.tiles_per_batch : 0;   // batch entry (tensor maps are 3-D)
-        tile_coords(p, kBatched ? tile - z * p.tiles_per_batch : tile, m_blk, n_blk);
+        locate_tile<kPair>(p, kBatched ? tile - z * p.tiles_per_batch : tile, rank, m_blk, n_blk, flag_tile);
         const int m0 = m_blk * kBM;
         const int n0 = n_blk * kOutN;
         for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
           if (!mbar_wait(empty_bar(s), phase ^ 1u, 0x101)) { ok = false; break; }
-          mbar_arrive_expect_tx(full_bar(s), kStage);
           const uint32_t a_dst = smem_base + s * kStage;
           const uint32_t b_dst = a_dst + kStageBytesA;
+          if (kPair) {
+            // the issuing CTA expects the bytes of both CTAs on its barrier
+            if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * kStage);
+            const uint32_t bar = map_to_peer(full_bar(s), 0);
+            tma_load_2d_pair(a_dst, &map_a, bar, kb * kBK, m0);
+            // plain: this CTA's half of the 256 columns; gated: CTA 0 the up weight (accumulator
+            // columns 0-127), CTA 1 the gate weight (columns 128-255), same 128 output columns
+#pragma unroll
+            for (int j = 0; j < kChunksB; ++j)
+              tma_load_2d_pair(b_dst + j * 8192, (kGated && rank) ? &map_b2 : &map_b, bar,
+                               n0 + (kGated ? 0 : int(rank) * (kBN / 2)) + j * 64, kb * kBK);
+            continue;
+          }
+          mbar_arrive_expect_tx(full_bar(s), kStage);
           if (kBatched) {
             tma_load_3d(a_dst, &map_a, full_bar(s), kb * kBK, p.a_batch_inside ? z : m0,
                         p.a_batch_inside ? m0 : z);
@@ -263,11 +320,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       uint32_t it = 0;
       uint32_t local_tile = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      for (int tile = first_unit; tile < num_units && ok; tile += unit_stride, ++local_tile) {
         const uint32_t acc = local_tile & 1u;
         const uint32_t acc_phase = (local_tile >> 1) & 1u;
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, 0x201)) { ok = false; break; }
@@ -286,11 +343,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint64_t a_desc = umma_smem_desc(a_addr + k4 * 32, 16, 1024);
             // B: N-major, 64-column chunks 8192 B apart, 8-row K groups 1024 B apart.
             const uint64_t b_desc = umma_smem_desc(b_addr + k4 * 2048, 8192, 1024);
-            umma_bf16_ss(d_tmem, a_desc, b_desc, kIdesc, (kb | k4) != 0 ? 1u : 0u);
+            if (kPair)
+              umma_bf16_ss_pair(d_tmem, a_desc, b_desc, kIdesc, (kb | k4) != 0 ? 1u : 0u);
+            else
+              umma_bf16_ss(d_tmem, a_desc, b_desc, kIdesc, (kb | k4) != 0 ? 1u : 0u);
           }
-          umma_commit(empty_bar(s));
+          if (kPair) umma_commit_pair(empty_bar(s)); else umma_commit(empty_bar(s));
         }
-        if (ok) umma_commit(tmem_full_bar(acc));
+        if (ok) {
+          if (kPair) umma_commit_pair(tmem_full_bar(acc)); else umma_commit(tmem_full_bar(acc));
+        }
       }
     }
   } else if (warp < 6) {
@@ -304,10 +366,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t store_buf = 0;
     bool ok = true;
     const int etid = threadIdx.x - 64;      // 0..127 within the epilogue group
-    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++local_tile) {
-      int m_blk, n_blk;
-      const int z = kBatched ? tile / p.tiles_per_batch : 0;
-      tile_coords(p, kBatched ? tile - z * p.tiles_per_batch : tile, m_blk, n_blk);
+    for (int unit = first_unit; unit < num_units && ok; unit += unit_stride, ++local_tile) {
+      int m_blk, n_blk, tile;
+      const int z = kBatched ? unit / p.tiles_per_batch : 0;
+      locate_tile<kPair>(p, kBatched ? unit - z * p.tiles_per_batch : unit, rank, m_blk, n_blk, tile);
       const __nv_bfloat16* bias_base = p.bias + (kBatched ? z * p.stride_bias : 0);
       const int m0 = m_blk * kBM;
       const int n0 = n_blk * kOutN;
@@ -449,7 +511,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+      if (lane == 0) {
+        if (kPair) mbar_arrive_cluster(map_to_peer(tmem_empty_bar(acc), 0));
+        else mbar_arrive(tmem_empty_bar(acc));
+      }
       if (kFused) {
         // This rank's partial of the tile is complete in memory -> tell every rank's reducer
         // warps (this CTA's own included), which own a slice of the tile's rows each.
@@ -470,9 +535,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     // tile at about the same time, so the partials of a tile arrive together.
     const int rtid = threadIdx.x - kGemmThreads;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-      int m_blk, n_blk;
-      tile_coords(p, tile, m_blk, n_blk);
+    for (int unit = first_unit; unit < num_units && ok; unit += unit_stride) {
+      int m_blk, n_blk, tile;
+      locate_tile<kPair>(p, unit, rank, m_blk, n_blk, tile);
       ok = reduce_owned_tile<kBN>(p, peers, tile, m_blk * kBM, n_blk * kBN, rtid, 2);
     }
     {
@@ -481,13 +546,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       __threadfence_system();
       asm volatile("bar.sync 2, 128;" ::: "memory");
       if (rtid == 0) {
-        uint32_t* mine = peers.flags[peers.rank] + static_cast<long long>(p.num_tiles) * peers.world;
+        uint32_t* mine = peers.flags[peers.rank] + static_cast<long long>(p.flag_tiles) * peers.world;
         const unsigned prev = atomicAdd(mine + kGemmMaxWorld, 1u);
         if (prev == gridDim.x - 1) {
           mine[kGemmMaxWorld] = 0;
           __threadfence_system();
           for (int r = 0; r < peers.world; ++r)
-            flag_store(peers.flags[r] + static_cast<long long>(p.num_tiles) * peers.world + peers.rank, peers.epoch);
+            flag_store(peers.flags[r] + static_cast<long long>(p.flag_tiles) * peers.world + peers.rank, peers.epoch);
           for (int r = 0; r < peers.world; ++r)
             if (!wait_flag(mine + r, peers.epoch, 0x802)) break;
         }
@@ -496,35 +561,75 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 
   // Common exit: every role leaves its loop (normally or after a wait gave up) and meets here.
+  // In pair mode neither CTA leaves while the other may still arrive on its barriers or its MMAs
+  // read this CTA's shared memory.
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();
   if (warp == 2) {
     if (g_device_status != 0) {
       // A wait gave up somewhere: give copies still in flight time to land before the
       // shared memory and TMEM of this CTA are released.
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     }
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (kPair) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
 // Shared-memory opt-in of one instantiation, once per device.
-template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false>
+template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false,
+          bool kPair = false>
 int opt_in_gemm() {
   static unsigned long long configured = 0;
   return opt_in_shared_memory(
-      reinterpret_cast<const void*>(&gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched>),
-      gemm_smem_bytes<kBN, kStages>(), &configured, "gemm");
+      reinterpret_cast<const void*>(&gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched, kPair>),
+      gemm_smem_bytes<kBN, kStages, kPair>(), &configured, "gemm");
 }
 
-template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false>
+// How many two-CTA clusters of a pair-mode instantiation the current device keeps resident at
+// once (one CTA per SM; a GPC with an odd number of SMs leaves one unpaired).  Cached per device.
+template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused>
+int resident_pairs(int* pairs) {
+  static std::mutex mutex;
+  static int cached[64] = {};
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= 64)
+    return fail(TRINITY_SM100_E_CUDA, "gemm: cudaGetDevice: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(mutex);
+  if (!cached[device]) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * 148);
+    config.blockDim = dim3(kFused ? kGemmFusedThreads : kGemmThreads);
+    config.dynamicSmemBytes = gemm_smem_bytes<kBN, kStages, true>();
+    cudaLaunchAttribute cluster;
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.x = 2;
+    cluster.val.clusterDim.y = 1;
+    cluster.val.clusterDim.z = 1;
+    config.attrs = &cluster;
+    config.numAttrs = 1;
+    int count = 0;
+    e = cudaOccupancyMaxActiveClusters(
+        &count, gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, false, true>, &config);
+    if (e != cudaSuccess || count < 1)
+      return fail(TRINITY_SM100_E_CUDA, "gemm: cluster occupancy query: %s (%d clusters)", cudaGetErrorString(e),
+                  count);
+    cached[device] = count;
+  }
+  *pairs = cached[device];
+  return 0;
+}
+
+template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false,
+          bool kPair = false>
 int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, const GemmPeers* fused = nullptr,
                 const trinity_sm100_gemm_batch* batch = nullptr) {
   constexpr int kOutN = kGated ? kBN / 2 : kBN;
-  constexpr int kSmem = gemm_smem_bytes<kBN, kStages>();
+  constexpr int kSmem = gemm_smem_bytes<kBN, kStages, kPair>();
   static_assert(kSmem <= 232448, "exceeds the 227 KB shared-memory limit");
-  auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched>;
-  if (int rc = opt_in_gemm<kBN, kStages, kGated, kOutF32, kFused, kBatched>()) return rc;
+  auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched, kPair>;
+  if (int rc = opt_in_gemm<kBN, kStages, kGated, kOutF32, kFused, kBatched, kPair>()) return rc;
   CUtensorMap map_a, map_b, map_b2, map_out;
   int rc;
   const int out_bytes = kOutF32 ? 4 : 2;
@@ -577,9 +682,33 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
   p.out_batch_inside = kBatched && batch->stride_out < g.ldo ? 1 : 0;
   p.stride_bias = kBatched ? batch->stride_bias : 0;
   p.num_kb = int((g.k + kBK - 1) / kBK);
-  const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
+  p.flag_tiles = (p.tiles_m + 1) / 2 * 2 * p.tiles_n;
   GemmPeers peers = {};
   if (fused) peers = *fused;
+  if constexpr (kPair) {
+    // a persistent grid of as many CTA pairs as are resident together
+    int pairs = 0;
+    if ((rc = resident_pairs<kBN, kStages, kGated, kOutF32, kFused>(&pairs))) return rc;
+    const int units = (p.tiles_m + 1) / 2 * p.tiles_n;
+    if (units < pairs) pairs = units;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * pairs);
+    config.blockDim = dim3(kFused ? kGemmFusedThreads : kGemmThreads);
+    config.dynamicSmemBytes = kSmem;
+    config.stream = stream;
+    cudaLaunchAttribute cluster;
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.x = 2;
+    cluster.val.clusterDim.y = 1;
+    cluster.val.clusterDim.z = 1;
+    config.attrs = &cluster;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_b2, map_out, p, peers);
+    if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "gemm_bf16_tcgen05 (pairs) launch: %s", cudaGetErrorString(e));
+    count_launch();
+    return check_launch("gemm_bf16_tcgen05");
+  }
+  const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
   kernel<<<grid, kFused ? kGemmFusedThreads : kGemmThreads, kSmem, stream>>>(map_a, map_b, map_b2,
                                                                             map_out, p, peers);
   count_launch();
@@ -600,6 +729,9 @@ int gemm_prepare_device() {
   TRINITY_OPT_IN(128, 6, false, true, false, true) TRINITY_OPT_IN(128, 6, false, false, false, true)
   TRINITY_OPT_IN(64, 8, false, true, false, true) TRINITY_OPT_IN(64, 8, false, false, false, true)
   TRINITY_OPT_IN(256, 4, false, false, true)
+  TRINITY_OPT_IN(256, kPairStages, true, true, false, false, true) TRINITY_OPT_IN(256, kPairStages, true, false, false, false, true)
+  TRINITY_OPT_IN(256, kPairStages, false, true, false, false, true) TRINITY_OPT_IN(256, kPairStages, false, false, false, false, true)
+  TRINITY_OPT_IN(256, kPairStages, false, false, true, false, true)
 #undef TRINITY_OPT_IN
   return rc;
 }
@@ -652,16 +784,26 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
   if (int rc = require_sm100(&sm_count)) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
   const bool f32 = g.out_dtype == TRINITY_SM100_FP32;
+  const long long row_tiles = (g.m + kBM - 1) / kBM;
+  // CTA pairs once there are at least as many 256-row x 256-column (gated: x 128) pair tiles as
+  // SM pairs; an odd last row tile costs its pair half a tile of zero work.
+  const long long pair_units = (row_tiles + 1) / 2 * ((g.n + (gated ? 127 : 255)) / (gated ? 128 : 256));
+  const bool pairs = row_tiles >= 2 && pair_units >= sm_count / 2;
   if (gated) {
+    if (pairs)
+      return f32 ? launch_gemm<256, kPairStages, true, true, false, false, true>(g, sm_count, stream)
+                 : launch_gemm<256, kPairStages, true, false, false, false, true>(g, sm_count, stream);
     return f32 ? launch_gemm<256, 4, true, true>(g, sm_count, stream)
                : launch_gemm<256, 4, true, false>(g, sm_count, stream);
   }
+  if (pairs)
+    return f32 ? launch_gemm<256, kPairStages, false, true, false, false, true>(g, sm_count, stream)
+               : launch_gemm<256, kPairStages, false, false, false, false, true>(g, sm_count, stream);
   // Wide tiles once there are enough of them to fill the machine.  Otherwise the tile width
   // that finishes in the fewest column-steps: a persistent CTA works through
   // ceil(tiles / SMs) tiles of that width.  With few output rows (decode-time GEMMs) the kernel
   // streams the weight matrix, and 64-column tiles are what spreads an [K, 8192] weight over
   // 128 SMs instead of 64, each with an eight-stage ring in flight.
-  const long long row_tiles = (g.m + kBM - 1) / kBM;
   const long long wide_tiles = row_tiles * ((g.n + 255) / 256);
   if (wide_tiles >= sm_count) {
     return f32 ? launch_gemm<256, 4, false, true>(g, sm_count, stream)
@@ -715,7 +857,8 @@ extern "C" int trinity_sm100_gemm_batched_bf16(const trinity_sm100_gemm* args,
 
 extern "C" size_t trinity_sm100_gemm_allreduce_flag_words(int64_t m, int64_t n, int32_t world) {
   if (m <= 0 || n <= 0 || world <= 0) return 0;
-  const size_t tiles = size_t((m + kBM - 1) / kBM) * size_t((n + 255) / 256);
+  // numbered over 128-row tiles with the row-tile count rounded up to even (CTA pairs)
+  const size_t tiles = (size_t((m + kBM - 1) / kBM) + 1) / 2 * 2 * size_t((n + 255) / 256);
   return kGemmFlagOffset + tiles * size_t(world) + kGemmMaxWorld + 8;
 }
 
@@ -758,5 +901,8 @@ extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
   int sm_count = 0;
   if (int rc = require_sm100(&sm_count)) return rc;
   // every CTA of the persistent grid is resident (one per SM), which the flag waits rely on
+  const long long row_tiles = (g.m + kBM - 1) / kBM;
+  if (row_tiles >= 2 && (row_tiles + 1) / 2 * ((g.n + 255) / 256) >= sm_count / 2)
+    return launch_gemm<256, kPairStages, false, false, true, false, true>(g, sm_count, static_cast<cudaStream_t>(stream_handle), &peers);
   return launch_gemm<256, 4, false, false, true>(g, sm_count, static_cast<cudaStream_t>(stream_handle), &peers);
 }

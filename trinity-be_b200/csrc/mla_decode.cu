@@ -146,18 +146,7 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// ---- thread-block-cluster helpers (two CTAs per cluster)
-__device__ __forceinline__ uint32_t cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-// Address of the same shared-memory offset in CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t map_to_peer(uint32_t local_addr, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  return remote;
-}
+// ---- more thread-block-cluster helpers (the basic ones are in sm100_ptx.cuh)
 __device__ __forceinline__ void st_peer_v4(uint32_t remote_addr, float a, float b, float c, float d) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
                ::"r"(remote_addr), "f"(a), "f"(b), "f"(c), "f"(d)
@@ -196,11 +185,6 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     }
   }
 }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n"
-               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
 // Chunk range [first, first + count) of split `s` when `chunks` are dealt out evenly.
 __host__ __device__ inline void split_range(int chunks, int splits, int s, int& first, int& count) {
   const int base = chunks / splits, extra = chunks % splits;
