@@ -11,7 +11,8 @@ Total work is fixed, so the scaling is strong.  Inputs are synthetic and seeded.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--workload tp_mlp|tp_mlp_unfused|tp_mlp_noreduce|gemm_relu|gemm_bias_1024|
                                 rmsnorm|softmax|mla|mla_batch_sharded|
-                                gemm_decode_square|gemm_decode_up|gemm_decode_down]
+                                gemm_decode_square|gemm_decode_up|gemm_decode_down|
+                                gemm_shape --shape M,N,K --epilogue none|relu|gated]
                     [--no-configs] [--no-cpu-baseline] [--no-graph]
 
 Prints one JSON line (rank 0).  With the default workload the line also carries a "configs" block:
@@ -37,6 +38,7 @@ sys.path.insert(0, str(REPO / "trinity-be_b200"))
 import torch  # noqa: E402
 
 L2_BYTES = 126 * 1024 * 1024
+SHAPE, EPILOGUE = (4096, 4096, 4096), "none"   # of the gemm_shape workload (--shape, --epilogue)
 REL_L2_BOUND, MAX_ABS_BOUND = 1e-2, 2e-2   # the path's stated floating-point bar
 
 # DRAM bytes per launch of the dominant kernel from an ncu capture (profiles/), per workload.
@@ -188,6 +190,7 @@ def workload_label(name):
         "gemm_decode_down": "gemm A[16,28672]@W[28672,8192] bf16 (decode-time shape)",
         "mla": "mla_decode batch 64 x 128 heads, cache[64,4096,576] bf16, heads sharded over the GPUs",
         "mla_batch_sharded": "mla_decode batch 64 x 128 heads, cache[64,4096,576] bf16, sequences sharded over the GPUs",
+        "gemm_shape": "gemm A[%d,%d]@W[%d,%d] bf16, epilogue %s" % (SHAPE[0], SHAPE[2], SHAPE[2], SHAPE[1], EPILOGUE),
         "tp_mlp": mlp + ", all-reduce fused into the down GEMM",
         "tp_mlp_unfused": mlp + ", separate all-reduce kernel",
         "tp_mlp_noreduce": mlp + ", NO all-reduce (timing baseline, result incomplete)",
@@ -358,6 +361,68 @@ def make_workload(name, device, world=None, ranks=1, rank=0):
                 wl.softmax_oracle(sample)
             dt = time.perf_counter() - t0
             return sample.numel() * 4 / 1e9 / dt, "4096 of 32768 rows, CPU oracle (FP32 torch)", dt
+
+    elif name == "gemm_shape":
+        # One GEMM of a free shape (profiler captures of small cases, tile-shape sweeps):
+        # --shape M,N,K --epilogue none|relu|gated.  Operands are drawn on the device.
+        m, n, kk = SHAPE
+        w.metric, w.unit, w.bound, w.dtype = "bf16_gemm_epilogue_tflops", "TFLOP/s", "tensor", "bf16"
+        gated = EPILOGUE == "gated"
+        w.work = (4.0 if gated else 2.0) * m * n * kk / 1e12
+        w.alg_bytes = (m * kk + (2 if gated else 1) * kk * n + m * n) * 2
+        w.kernels_per_step = 1
+        w.l2_note = "inputs larger than L2" if w.alg_bytes > L2_BYTES else "inputs fit in L2"
+        if on_gpu:
+            g = torch.Generator(device=device)
+            g.manual_seed(1241)
+            ad = torch.randn((m, kk), generator=g, device=device).bfloat16()
+            wd = (torch.randn((kk, n), generator=g, device=device) / math.sqrt(kk)).bfloat16()
+            w2 = (torch.randn((kk, n), generator=g, device=device) / math.sqrt(kk)).bfloat16() if gated else None
+            bias = (torch.randn((n,), generator=g, device=device) * 0.1).bfloat16()
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+            host_a = ad.cpu().pin_memory()
+
+            def run(a_s, o_s):
+                if gated:
+                    k.gemm(a_s, wd, b2=w2, activation=k.ACT_SILU_GATE, out=o_s)
+                elif EPILOGUE == "relu":
+                    k.gemm(a_s, wd, bias=bias, bias_mode=k.BIAS_COL_VECTOR, activation=k.ACT_RELU, out=o_s)
+                else:
+                    k.gemm(a_s, wd, out=o_s)
+
+            def make_slot(index):
+                a_s = ad if index == 0 else torch.empty_like(ad)
+                o_s = out if index == 0 else torch.empty_like(out)
+                host_out = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+                return (lambda: a_s.copy_(host_a, non_blocking=True), lambda: run(a_s, o_s),
+                        lambda: host_out.copy_(o_s, non_blocking=True))
+
+            w.make_slot = make_slot
+            w.device_step = lambda: run(ad, out)
+            w.h2d, w.d2h = m * kk * 2, m * n * 2
+
+            def check():
+                rows = sampled_rows(m, 32)
+                xs = host_a[rows].double()
+                up = xs @ wd.cpu().double()
+                if gated:
+                    gate = xs @ w2.cpu().double()
+                    expected = up * (gate * torch.sigmoid(gate))
+                elif EPILOGUE == "relu":
+                    expected = torch.relu(up + bias.cpu().double())
+                else:
+                    expected = up
+                return error_figures(out[rows.to(device)].cpu(), expected, len(rows))
+            w.check = check
+
+        def cpu_sample(threads, budget_s):
+            torch.set_num_threads(threads)
+            rows = min(m, 256)
+            xs, ws = torch.randn(rows, kk), torch.randn(kk, n)
+            t0 = time.perf_counter()
+            (xs @ ws).bfloat16()
+            dt = time.perf_counter() - t0
+            return 2.0 * rows * n * kk / 1e12 / dt, f"{rows} of {m} rows, torch CPU FP32 matmul", dt
 
     elif name in ("gemm_decode_square", "gemm_decode_up", "gemm_decode_down"):
         # Decode-time GEMMs: 16 tokens against a large weight, which the kernel streams once.
@@ -666,6 +731,9 @@ def main():
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="tp_mlp")
+    parser.add_argument("--shape", default=None, help="M,N,K of --workload gemm_shape")
+    parser.add_argument("--epilogue", default="none", choices=["none", "relu", "gated"],
+                        help="epilogue of --workload gemm_shape")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-configs", action="store_true",
                         help="skip the block with the other benchmark configurations")
@@ -673,6 +741,10 @@ def main():
                         help="launch directly instead of replaying a CUDA Graph (for profilers)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
+    global SHAPE, EPILOGUE
+    if args.shape:
+        SHAPE = tuple(int(v) for v in args.shape.split(","))
+    EPILOGUE = args.epilogue
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -91,6 +91,13 @@ typedef struct trinity_sm100_gemm {
 TRINITY_SM100_API int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* stream);
 
 /*
+ * Large problems run on pairs of thread blocks that share one tensor-core instruction (two SMs
+ * of one TPC).  This reports how many such pairs the current device keeps resident at once
+ * (the size of the persistent grid in that mode).  For tools and tests.
+ */
+TRINITY_SM100_API int trinity_sm100_gemm_pair_capacity(int32_t* pairs);
+
+/*
  * Batched form: `batch` GEMMs of one shape in one launch.  Entry z reads a + z*stride_a and
  * b + z*stride_b, adds bias + z*stride_bias and writes out + z*stride_out (strides in elements,
  * multiples of 16 bytes).  stride_b == 0 shares one right operand, stride_bias == 0 one side

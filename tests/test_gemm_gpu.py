@@ -56,7 +56,8 @@ def test_dyadic_inputs_on_cta_pairs(m, n, k, out_dtype):
 
 
 def test_gated_form_on_cta_pairs():
-    """In the gated form one CTA of the pair stages the up weight and the other the gate weight."""
+    """In the gated form each CTA of the pair stages 64 up-weight and the matching 64 gate-weight
+    columns of the tile."""
     a, wg, wu, _ = wl.mlp_inputs(2000, 256, 1304, 31)
     dev = torch.device("cuda:0")
     out = kernels.gemm(a.to(dev), wu.to(dev), b2=wg.to(dev), activation=kernels.ACT_SILU_GATE)

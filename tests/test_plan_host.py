@@ -256,6 +256,35 @@ def test_hazards_are_errors():
     assert tl.emit(tiled(16, 64)).launch_count == 1
 
 
+def test_kernel_candidates_list_per_operation_offers_and_rejections():
+    """Candidate discovery (src/emit/candidate.rs:107-207 there): nothing is selected; each
+    operation carries the launches that would cover it and, per recogniser that declined, the
+    reason.  An operation nothing covers keeps an empty candidate list with its diagnostics."""
+    found = tl.kernel_candidates(plans.gemm_bias(256, 256, 128, "relu"))
+    assert sorted(found) == ["0", "1"]                      # the K-loop product and its epilogue
+    for entry in found.values():
+        assert entry["scope"] == {"statement": 0}
+        assert entry["candidates"] == [{"provider": "sm100.gemm", "kind": "native",
+                                        "kernel": "trinity_sm100_gemm_bf16", "operations": [0, 1]}]
+        declined = {r["provider"]: r["reason"] for r in entry["rejections"]}
+        assert declined["sm100.pointwise"] == "no applicable implementations"
+        assert "not part of" in declined["triton"] and "not part of" in declined["quack"]
+    norm = tl.kernel_candidates(plans.rmsnorm(64, 4096))
+    assert {c["provider"] for c in norm["0"]["candidates"]} == {"sm100.rmsnorm"}
+    assert {"provider": "sm100.gemm", "reason": "sm100.gemm: not load(acc) + matmul"} in norm["0"]["rejections"]
+
+    def overlapping():
+        b, x, y = copy_builder()
+        op = b.add_operation([x], [y], expression=expression("(clipped_tile i 16)"))
+        return b.build([b.add_loop("parallel", "i", 0, 64, 8, [op])], "Y", y)
+    bad = tl.kernel_candidates(overlapping())
+    assert bad["0"]["candidates"] == []
+    reasons = {r["provider"]: r["reason"] for r in bad["0"]["rejections"]}
+    assert "overlap between CTAs" in reasons["sm100.pointwise"]
+    # plan-level refusals stay plan-level, as the reference's prepare step fails the whole call
+    assert "Persistent" in tl.kernel_candidates(plans.gemm_bias(256, 256, 128, world_size=2))["error"]
+
+
 def test_unsupported_operations_report_no_provider():
     b = tl.PhysicalPlanBuilder()
     x = b.add_value("fp16", [64], "external", name="X")

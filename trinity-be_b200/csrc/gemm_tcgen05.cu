@@ -17,12 +17,14 @@
 //
 // Large problems run on CTA pairs (a cluster of two CTAs, tcgen05 cta_group::2): a pair owns a
 // 256 x 256 output tile, each CTA loads its own 128 rows of A and its own 128 of the 256 B
-// columns (in the gated form one CTA loads the up weight and the other the gate weight), the
+// columns (in the gated form 64 up-weight and the matching 64 gate-weight columns), the
 // even CTA issues M=256 MMAs that read both CTAs' shared memory and write each CTA's 128
 // accumulator rows into its own TMEM, and both CTAs run their own epilogue.  A stage is 32 KB
 // per CTA instead of 48, so every SM reads and writes a third less shared memory per FLOP.
 //
 // Algorithmic traffic per launch: (M*K + K*N [+K*N]) * 2 + bias + M*N*out_bytes.
+#include <cstdlib>
+
 #include "host_common.h"
 #include "sm100_ptx.cuh"
 
@@ -289,12 +291,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * kStage);
             const uint32_t bar = map_to_peer(full_bar(s), 0);
             tma_load_2d_pair(a_dst, &map_a, bar, kb * kBK, m0);
-            // plain: this CTA's half of the 256 columns; gated: CTA 0 the up weight (accumulator
-            // columns 0-127), CTA 1 the gate weight (columns 128-255), same 128 output columns
+            // plain: this CTA's half of the 256 columns.  gated: this CTA's 64 of the tile's 128
+            // output columns from the up weight, then the same 64 from the gate weight, so the
+            // accumulator columns read [up 0-63 | gate 0-63 | up 64-127 | gate 64-127] and both
+            // CTAs stream both weights.
 #pragma unroll
-            for (int j = 0; j < kChunksB; ++j)
-              tma_load_2d_pair(b_dst + j * 8192, (kGated && rank) ? &map_b2 : &map_b, bar,
-                               n0 + (kGated ? 0 : int(rank) * (kBN / 2)) + j * 64, kb * kBK);
+            for (int j = 0; j < kChunksB; ++j) {
+              if (kGated)
+                tma_load_2d_pair(b_dst + j * 8192, j ? &map_b2 : &map_b, bar, n0 + int(rank) * 64, kb * kBK);
+              else
+                tma_load_2d_pair(b_dst + j * 8192, &map_b, bar, n0 + int(rank) * (kBN / 2) + j * 64, kb * kBK);
+            }
             continue;
           }
           mbar_arrive_expect_tx(full_bar(s), kStage);
@@ -404,12 +411,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int sub = 0; sub < kSubPerStore; ++sub) {
           const int col = c0 + sub * 32;
+          // accumulator columns of this sub-chunk's values and (gated form) of its gates
+          const int acc_col = (kPair && kGated) ? (col / 64) * 128 + col % 64 : col;
+          const int gate_col = (kPair && kGated) ? acc_col + 64 : kOutN + col;
           uint32_t v[32];
-          tmem_ld_32x32b_x32(t_row + col, v);
+          tmem_ld_32x32b_x32(t_row + acc_col, v);
           float x[32];
           if (kGated) {
             uint32_t g[32];
-            tmem_ld_32x32b_x32(t_row + kOutN + col, g);
+            tmem_ld_32x32b_x32(t_row + gate_col, g);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -775,6 +785,29 @@ int check_gemm_arguments(const trinity_sm100_gemm& g) {
 }
 }  // namespace
 
+namespace {
+// TRINITY_SM100_GEMM_PAIRS=0 keeps every GEMM on single CTAs; =1 (default) lets large plain and
+// all-reduce-fused problems run on CTA pairs; =2 also the gated form, which measures slower on
+// pairs than on single CTAs (B200, 16384 x 8192 x 28672) and therefore stays on single CTAs by
+// default.  Read at every call; a tuning override, not part of the ABI.
+int pairs_mode() {
+  const char* v = getenv("TRINITY_SM100_GEMM_PAIRS");
+  return v && v[0] >= '0' && v[0] <= '2' ? v[0] - '0' : 1;
+}
+bool pairs_allowed() { return pairs_mode() != 0; }
+}  // namespace
+
+// CTA pairs of the plain pair-mode GEMM that the current device keeps resident at once.
+extern "C" int trinity_sm100_gemm_pair_capacity(int32_t* pairs) {
+  if (!pairs) return fail(TRINITY_SM100_E_INVALID, "gemm_pair_capacity: null pointer");
+  if (int rc = require_sm100(nullptr)) return rc;
+  if (int rc = opt_in_gemm<256, kPairStages, false, false, false, false, true>()) return rc;
+  int count = 0;
+  if (int rc = resident_pairs<256, kPairStages, false, false, false>(&count)) return rc;
+  *pairs = count;
+  return 0;
+}
+
 extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* stream_handle) {
   if (!args) return fail(TRINITY_SM100_E_INVALID, "gemm: null argument block");
   const trinity_sm100_gemm& g = *args;
@@ -788,9 +821,9 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
   // CTA pairs once there are at least as many 256-row x 256-column (gated: x 128) pair tiles as
   // SM pairs; an odd last row tile costs its pair half a tile of zero work.
   const long long pair_units = (row_tiles + 1) / 2 * ((g.n + (gated ? 127 : 255)) / (gated ? 128 : 256));
-  const bool pairs = row_tiles >= 2 && pair_units >= sm_count / 2;
+  const bool pairs = pairs_allowed() && row_tiles >= 2 && pair_units >= sm_count / 2;
   if (gated) {
-    if (pairs)
+    if (pairs && pairs_mode() == 2)
       return f32 ? launch_gemm<256, kPairStages, true, true, false, false, true>(g, sm_count, stream)
                  : launch_gemm<256, kPairStages, true, false, false, false, true>(g, sm_count, stream);
     return f32 ? launch_gemm<256, 4, true, true>(g, sm_count, stream)
@@ -902,7 +935,7 @@ extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
   if (int rc = require_sm100(&sm_count)) return rc;
   // every CTA of the persistent grid is resident (one per SM), which the flag waits rely on
   const long long row_tiles = (g.m + kBM - 1) / kBM;
-  if (row_tiles >= 2 && (row_tiles + 1) / 2 * ((g.n + 255) / 256) >= sm_count / 2)
+  if (pairs_allowed() && row_tiles >= 2 && (row_tiles + 1) / 2 * ((g.n + 255) / 256) >= sm_count / 2)
     return launch_gemm<256, kPairStages, false, false, true, false, true>(g, sm_count, static_cast<cudaStream_t>(stream_handle), &peers);
   return launch_gemm<256, 4, false, false, true>(g, sm_count, static_cast<cudaStream_t>(stream_handle), &peers);
 }

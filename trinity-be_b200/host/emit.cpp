@@ -812,13 +812,7 @@ struct Emitter {
   }
 
   void run() {
-    if (plan.world_size != 1)
-      unsupported("UnsupportedExecution: Persistent emission is not implemented");
-    if (!plan.symbols().empty())
-      throw PlanError(ErrorKind::Value, "InvalidExecution: plan has unbound symbols; call bind_symbols first");
-    for (auto& v : plan.values)
-      if (v.dtype == DType::Fp16) unsupported("UnsupportedExecution: fp16 values are not supported by the native provider");
-    if (plan.outputs.size() != 1) unsupported("UnsupportedExecution: native CUDA ABI requires one output");
+    check_plan();
     build_buffers();
     for (auto& s : plan.statements) {
       rejections.clear();
@@ -830,6 +824,54 @@ struct Emitter {
       unsupported("NoProvider: no sm100 kernel for operation " + std::to_string(ops.empty() ? -1 : ops[0]) +
                   (reasons.empty() ? "" : " (" + reasons + ")"));
     }
+  }
+
+  // Candidate discovery (src/emit/candidate.rs:107-207): every recogniser is offered every
+  // top-level statement, nothing is selected.  An operation gets, per recogniser, either the
+  // launch that would cover it or the recogniser's reason for declining.
+  struct Offer {
+    std::string provider;
+    bool matched = false;
+    std::vector<Launch> launches;   // when matched
+    std::string reason;             // when not
+  };
+  void check_plan() {
+    if (plan.world_size != 1)
+      unsupported("UnsupportedExecution: Persistent emission is not implemented");
+    if (!plan.symbols().empty())
+      throw PlanError(ErrorKind::Value, "InvalidExecution: plan has unbound symbols; call bind_symbols first");
+    for (auto& v : plan.values)
+      if (v.dtype == DType::Fp16) unsupported("UnsupportedExecution: fp16 values are not supported by the native provider");
+    if (plan.outputs.size() != 1) unsupported("UnsupportedExecution: native CUDA ABI requires one output");
+  }
+  std::vector<Offer> offers(const Statement& s) {
+    using Recogniser = bool (Emitter::*)(const Statement&);
+    const std::pair<const char*, Recogniser> recognisers[] = {
+        {"sm100.gemm", &Emitter::try_gemm},         {"sm100.rmsnorm", &Emitter::try_rmsnorm},
+        {"sm100.softmax", &Emitter::try_softmax},   {"sm100.mla_decode", &Emitter::try_mla},
+        {"sm100.row_reduce", &Emitter::try_row_reduce}, {"sm100.pointwise", &Emitter::try_pointwise}};
+    std::vector<Offer> result;
+    for (auto& [name, recogniser] : recognisers) {
+      Offer offer;
+      offer.provider = name;
+      const size_t before = launches.size();
+      rejections.clear();
+      try {
+        offer.matched = (this->*recogniser)(s);
+      } catch (const PlanError& declined) {
+        offer.matched = false;
+        offer.reason = declined.what();
+      }
+      if (offer.matched) {
+        offer.launches.assign(launches.begin() + before, launches.end());
+      } else if (offer.reason.empty()) {
+        for (auto& r : rejections) offer.reason += (offer.reason.empty() ? "" : "; ") + r;
+        if (offer.reason.empty()) offer.reason = "no applicable implementations";
+      }
+      launches.resize(before);
+      result.push_back(std::move(offer));
+    }
+    return result;
   }
 };
 
@@ -929,14 +971,45 @@ std::string kernel_candidates_json(const PhysicalPlan& plan) {
   out << "{";
   try {
     Emitter e(plan);
-    e.run();
+    e.check_plan();
+    e.build_buffers();
     bool first = true;
-    for (auto& l : e.launches)
-      for (int op : l.operations) {
-        out << (first ? "" : ",") << "\"" << op << "\":{\"candidates\":[{\"provider\":\"sm100\",\"kind\":\"native\",\"kernel\":\""
-            << l.kernel << "\"}],\"rejections\":[]}";
+    for (size_t index = 0; index < plan.statements.size(); ++index) {
+      const Statement& statement = plan.statements[index];
+      std::vector<int> ops;
+      statement.operations(ops);
+      const std::vector<Emitter::Offer> offers = e.offers(statement);
+      for (int op : ops) {
+        out << (first ? "" : ",") << "\"" << op << "\":{\"scope\":{\"statement\":" << index << "},\"candidates\":[";
         first = false;
+        bool first_candidate = true;
+        for (auto& offer : offers) {
+          if (!offer.matched) continue;
+          for (auto& launch : offer.launches) {
+            if (std::find(launch.operations.begin(), launch.operations.end(), op) == launch.operations.end()) continue;
+            out << (first_candidate ? "" : ",") << "{\"provider\":\"" << offer.provider
+                << "\",\"kind\":\"native\",\"kernel\":\"" << json_escape(launch.kernel) << "\",\"operations\":[";
+            for (size_t i = 0; i < launch.operations.size(); ++i) out << (i ? "," : "") << launch.operations[i];
+            out << "]}";
+            first_candidate = false;
+          }
+        }
+        out << "],\"rejections\":[";
+        bool first_rejection = true;
+        for (auto& offer : offers) {
+          if (offer.matched) continue;
+          out << (first_rejection ? "" : ",") << "{\"provider\":\"" << offer.provider << "\",\"reason\":\""
+              << json_escape(offer.reason) << "\"}";
+          first_rejection = false;
+        }
+        // the reference's other providers produce opaque Python candidates; they are not part of
+        // this library, which is recorded the way a provider records an unsupported operation
+        for (const char* absent : {"triton", "quack"})
+          out << (first_rejection ? "" : ",") << "{\"provider\":\"" << absent
+              << "\",\"reason\":\"provider is not part of the sm_100a library\"}", first_rejection = false;
+        out << "]}";
       }
+    }
   } catch (const PlanError& err) {
     out << "\"error\":\"" << json_escape(err.what()) << "\"";
   }

@@ -19,6 +19,7 @@ DT_BF16, DT_FP32 = 0, 1
 EXPORTS = (
     "trinity_sm100_gemm_bf16",
     "trinity_sm100_gemm_batched_bf16",
+    "trinity_sm100_gemm_pair_capacity",
     "trinity_sm100_rmsnorm_bf16",
     "trinity_sm100_softmax_bf16",
     "trinity_sm100_mla_scratch_bytes",
@@ -159,6 +160,13 @@ def launch_count():
 def device_status(clear=False):
     value = ctypes.c_uint32(0)
     _check(library().trinity_sm100_device_status(ctypes.byref(value), int(clear)))
+    return value.value
+
+
+def gemm_pair_capacity():
+    """CTA pairs the current device keeps resident at once in the GEMM's pair mode."""
+    value = ctypes.c_int32(0)
+    _check(library().trinity_sm100_gemm_pair_capacity(ctypes.byref(value)))
     return value.value
 
 
