@@ -836,6 +836,15 @@ def main():
     }
     if host_launch_us is not None:
         line["host_launch_us"] = host_launch_us   # public-API launch, host side only
+    if distributed and args.workload == "tp_mlp":
+        # milestones of the last fused down-projection launch on every rank (its first thread block),
+        # microseconds after its start: last MMA committed, last partial tile handed over, last
+        # owned rows reduced, all ranks retired
+        t = k.gemm_allreduce_stamps()
+        mine = [round((v - t[0]) / 1e3, 1) for v in t[1:]]
+        every = [None] * world
+        dist.all_gather_object(every, mine)
+        line["fused_gemm_milestones_us"] = every      # one list per rank
 
     # The other benchmark configurations, each device-timed and checked the same way.
     if args.workload == "tp_mlp" and not args.no_configs:

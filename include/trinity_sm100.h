@@ -337,6 +337,13 @@ TRINITY_SM100_API int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm
                                       const trinity_sm100_allreduce* reduce, void* stream);
 
 /*
+ * Diagnostic: five milestones of thread block 0 of the most recent fused launch on the current
+ * device, in nanoseconds of the device's global timer: kernel start, last MMA committed, last
+ * partial tile handed over, last owned rows reduced, every rank retired.  Synchronises the device.
+ */
+TRINITY_SM100_API int trinity_sm100_gemm_allreduce_stamps(uint64_t* stamps);
+
+/*
  * Device status word: 0 while every bounded in-kernel wait has completed; otherwise the code
  * of the first wait that gave up (site id in the low 16 bits).  Reading synchronises the
  * device.  `clear` != 0 resets it afterwards.

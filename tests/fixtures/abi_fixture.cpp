@@ -3,6 +3,10 @@
 //   -DBAD_VERSION   descriptor.version is wrong
 //   -DBAD_OFFSET    one launch-field offset is wrong
 //   -DNO_STATUS     trinity_status is not exported
+// A run-time switch makes one entry point fail on the host, with the codes of the reference's
+// fixture (python/tests/fixtures/cuda_library.cu:16-19, :33-52 there):
+//   TRINITY_FIXTURE_FAILURE=prepare | launch | release  ->  code 17 | 719 (submitted) | 19
+#include <cstdlib>
 #include <cstring>
 
 #include "trinity_abi.h"
@@ -18,6 +22,11 @@ static const char kRequirements[] =
 
 static int launches = 0;
 
+static bool fault(const char* mode) {
+  const char* value = std::getenv("TRINITY_FIXTURE_FAILURE");
+  return value && std::strcmp(value, mode) == 0;
+}
+
 #define EXPORT extern "C" __attribute__((visibility("default")))
 
 EXPORT Descriptor const* trinity_abi() {
@@ -32,14 +41,14 @@ EXPORT Descriptor const* trinity_abi() {
 }
 EXPORT int trinity_prepare(unsigned* workers, ErrorInfo* e) {
   *workers = 1;
-  return report(e, none, 0, prepare);
+  return report(e, driver, fault("prepare") ? 17 : 0, prepare);
 }
 EXPORT int trinity_launch(StreamedLaunch const*, ErrorInfo* e) {
   ++launches;
-  return report(e, none, 0, launch, true);
+  return report(e, runtime, fault("launch") ? 719 : 0, launch, true);
 }
 #ifndef NO_STATUS
 EXPORT int trinity_status(void*, ErrorInfo* e) { return report(e, none, 0, completion); }
 #endif
-EXPORT int trinity_release(ErrorInfo* e) { return report(e, none, 0, release); }
+EXPORT int trinity_release(ErrorInfo* e) { return report(e, driver, fault("release") ? 19 : 0, release); }
 EXPORT int fixture_launches() { return launches; }

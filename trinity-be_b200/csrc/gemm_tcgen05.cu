@@ -51,8 +51,19 @@ struct GemmPeers {
   uint32_t* flags[kGemmMaxWorld];  // flag pads: ready[tile][source rank], done[rank], counter
   int world, rank;
   uint32_t epoch;
+  int signal_from_epilogue;        // 1: the epilogue warps fence and flag (older scheme, kept for comparison)
   long long ld_vectors;            // output row pitch in 16-byte vectors
 };
+
+// Milestones of CTA 0 of the most recent fused launch on this device, in nanoseconds of the
+// global timer: kernel start, last MMA committed, last partial tile flagged, last owned rows
+// reduced, kernel end.  Read by trinity_sm100_gemm_allreduce_stamps (a diagnostic).
+__device__ unsigned long long g_fused_stamps[8];
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 struct GemmParams {
   const __nv_bfloat16* bias;
@@ -229,6 +240,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
   volatile uint32_t* tmem_holder =
       reinterpret_cast<volatile uint32_t*>(staging + kStagingBytes + 8 * (2 * kStages + 4));
+  // fused form: counts epilogue warps whose stores of a tile have landed (four per tile); a
+  // counter and not an mbarrier because the epilogue may run several tiles ahead of the reducers
+  const uint32_t stored_count = bar_base + 8u * (2 * kStages + 4) + 8u;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -248,6 +262,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), kPair ? 8 : 4);
     }
+    asm volatile("st.shared::cta.u32 [%0], %1;" ::"r"(stored_count), "r"(0u) : "memory");
+    if (kFused && blockIdx.x == 0) g_fused_stamps[0] = global_ns();
     mbar_fence_init();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
@@ -360,6 +376,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (ok) {
           if (kPair) umma_commit_pair(tmem_full_bar(acc)); else umma_commit(tmem_full_bar(acc));
         }
+        if (kFused && blockIdx.x == 0) g_fused_stamps[1] = global_ns();
       }
     }
   } else if (warp < 6) {
@@ -526,15 +543,22 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         else mbar_arrive(tmem_empty_bar(acc));
       }
       if (kFused) {
-        // This rank's partial of the tile is complete in memory -> tell every rank's reducer
-        // warps (this CTA's own included), which own a slice of the tile's rows each.
-        if (lane == 0) {
+        if (peers.signal_from_epilogue) {
+          if (lane == 0) {
+            tma_store_wait_all();
+            __threadfence_system();
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (etid < peers.world)
+            flag_store(peers.flags[etid] + static_cast<long long>(tile) * peers.world + peers.rank, peers.epoch);
+        } else if (lane == 0) {
+          // Once this warp's part of the partial tile has landed in memory the warp is free for
+          // the next tile; telling the other GPUs (a system-scope release, which waits for
+          // writes in flight) is left to the reducer warps, which wait for this tile anyway.
           tma_store_wait_all();
-          __threadfence_system();
+          asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(stored_count) : "memory");
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (etid < peers.world)
-          flag_store(peers.flags[etid] + static_cast<long long>(tile) * peers.world + peers.rank, peers.epoch);
+        if (blockIdx.x == 0 && etid == 0) g_fused_stamps[2] = global_ns();
       }
     }
     if (lane == 0) tma_store_wait_all();
@@ -545,11 +569,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     // tile at about the same time, so the partials of a tile arrive together.
     const int rtid = threadIdx.x - kGemmThreads;
     bool ok = true;
-    for (int unit = first_unit; unit < num_units && ok; unit += unit_stride) {
+    uint32_t local_tile = 0;
+    for (int unit = first_unit; unit < num_units && ok; unit += unit_stride, ++local_tile) {
       int m_blk, n_blk, tile;
       locate_tile<kPair>(p, unit, rank, m_blk, n_blk, tile);
+      if (!peers.signal_from_epilogue && rtid < peers.world) {
+        // This rank's partial of the tile is complete in memory (the epilogue warps' stores have
+        // landed) -> tell every rank's reducer warps, this CTA's own included.  The give-up case
+        // is caught by the flag wait that follows: nobody will have flagged the tile.
+        const uint32_t target = 4u * (local_tile + 1u);
+        const long long start = clock64();
+        bool landed = false;
+        for (;;) {
+          uint32_t seen;
+          asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(stored_count) : "memory");
+          if (static_cast<int32_t>(seen - target) >= 0) { landed = true; break; }
+          if (clock64() - start > wait_budget()) { report_timeout(0x803); break; }
+          __nanosleep(100);
+        }
+        if (landed)
+          flag_store(peers.flags[rtid] + static_cast<long long>(tile) * peers.world + peers.rank, peers.epoch);
+      }
       ok = reduce_owned_tile<kBN>(p, peers, tile, m_blk * kBM, n_blk * kBN, rtid, 2);
     }
+    if (blockIdx.x == 0 && rtid == 0) g_fused_stamps[3] = global_ns();
     {
       // Retire: once every CTA of this rank has pushed its tiles, tell the peers; the last CTA
       // stays until every peer has said the same, so the output is complete when the kernel ends.
@@ -566,6 +609,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           for (int r = 0; r < peers.world; ++r)
             if (!wait_flag(mine + r, peers.epoch, 0x802)) break;
         }
+        if (blockIdx.x == 0) g_fused_stamps[4] = global_ns();
       }
     }
   }
@@ -895,6 +939,18 @@ extern "C" size_t trinity_sm100_gemm_allreduce_flag_words(int64_t m, int64_t n, 
   return kGemmFlagOffset + tiles * size_t(world) + kGemmMaxWorld + 8;
 }
 
+// stamps[0..4]: kernel start, last MMA committed, last partial tile handed over, last owned rows
+// reduced, all ranks retired - nanoseconds of the device's global timer, written by CTA 0 of the
+// most recent fused launch on the current device.  Synchronises the device.
+extern "C" int trinity_sm100_gemm_allreduce_stamps(uint64_t* stamps) {
+  if (!stamps) return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce_stamps: null pointer");
+  unsigned long long host[8];
+  cudaError_t e = cudaMemcpyFromSymbol(host, g_fused_stamps, sizeof(host));
+  if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "gemm_allreduce_stamps: %s", cudaGetErrorString(e));
+  for (int i = 0; i < 5; ++i) stamps[i] = host[i];
+  return 0;
+}
+
 extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
                                                  const trinity_sm100_allreduce* reduce, void* stream_handle) {
   if (!args || !reduce) return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: null argument block");
@@ -930,6 +986,10 @@ extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
   peers.world = r.world;
   peers.rank = r.rank;
   peers.epoch = r.epoch;
+  {
+    const char* v = getenv("TRINITY_SM100_FUSED_SIGNAL");
+    peers.signal_from_epilogue = v && v[0] == 'e' ? 1 : 0;
+  }
   peers.ld_vectors = g.ldo / 8;
   int sm_count = 0;
   if (int rc = require_sm100(&sm_count)) return rc;

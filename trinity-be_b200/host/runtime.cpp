@@ -356,7 +356,22 @@ void Execution::wait(double timeout_seconds) {
 void Execution::close(bool wait_first) {
   if (closed_) return;
   if (graph_owner_) throw ResourceBusy("execution is owned by a graph");
-  if (wait_first) wait(-1);
+  if (wait_first) {
+    // An execution whose launch or completion failed still closes (its resources are released or
+    // handed to the retire queue) and then reports the failure, as src/native/runtime.cpp:285-293
+    // does: the caller learns that its results are not valid, and nothing stays pinned.
+    try {
+      wait(-1);
+      if (failed_) throw RuntimeFailure("execution failed earlier", failure_);
+    } catch (...) {
+      reclaim();
+      throw;
+    }
+  }
+  reclaim();
+}
+
+void Execution::reclaim() {
   std::lock_guard<std::recursive_mutex> lock(module_->mutex_);
   if (closed_) return;
   DeviceGuard guard(module_->device_);

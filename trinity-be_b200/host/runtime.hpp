@@ -86,6 +86,7 @@ class Execution {
   void run(void* stream);
   void wait(double timeout_seconds);  // negative = no limit
   void close(bool wait_first);
+  void reclaim();   // the closing part of close(): events destroyed or deferred, module released
   bool closed() const { return closed_; }
   bool failed() const { return failed_; }
   const abi::ErrorInfo& failure() const { return failure_; }

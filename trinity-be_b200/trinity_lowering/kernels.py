@@ -33,6 +33,7 @@ EXPORTS = (
     "trinity_sm100_allreduce_bf16",
     "trinity_sm100_gemm_allreduce_flag_words",
     "trinity_sm100_gemm_allreduce_bf16",
+    "trinity_sm100_gemm_allreduce_stamps",
     "trinity_sm100_pointwise",
     "trinity_sm100_row_reduce_sum",
     "trinity_sm100_prepare_device",
@@ -370,6 +371,14 @@ def allreduce(peer_ptrs, flag_ptrs, rows, cols, rank, epoch, stream=None):
     args.flags = ctypes.cast(flags, ctypes.POINTER(ctypes.c_void_p))
     args.rows, args.cols, args.world, args.rank, args.epoch = rows, cols, world, rank, epoch
     _check(library().trinity_sm100_allreduce_bf16(ctypes.byref(args), _stream(stream)))
+
+
+def gemm_allreduce_stamps():
+    """Milestones (ns of the device timer) of the most recent fused launch's first thread block:
+    start, last MMA committed, last partial tile handed over, last owned rows reduced, retired."""
+    values = (ctypes.c_uint64 * 5)()
+    _check(library().trinity_sm100_gemm_allreduce_stamps(values))
+    return list(values)
 
 
 def gemm_allreduce_flag_words(m, n, world):

@@ -271,10 +271,13 @@ class PreparedExecution:
     def close(self, wait=True):
         if self._closed:
             return
-        if h.library().th_execution_close(self._handle, 1 if wait else 0) != 0:
+        failed = h.library().th_execution_close(self._handle, 1 if wait else 0) != 0
+        if not failed or h.library().th_execution_closed(self._handle):
+            # an execution that failed earlier closes all the same and then reports the failure
+            self._closed = True
+            self._inputs = MappingProxyType({})
+        if failed:
             h.raise_last()
-        self._closed = True
-        self._inputs = MappingProxyType({})
 
 
 def load(artifact_or_directory, device, world=None):
