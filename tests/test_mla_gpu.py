@@ -88,6 +88,34 @@ def test_rescale_path_with_growing_scores(kernels):
     assert_close_bf16(out, expected, max_ulp=None, max_abs=2.0 ** (math.floor(math.log2(top)) - 7))
 
 
+@pytest.mark.parametrize("gain", [16.0, 64.0])
+def test_large_logits(kernels, gain):
+    """Queries scaled by 16 and 64 and a cache whose positions carry different gains: scaled
+    logits reach several hundred, the softmax is sharply peaked, and an error of the score
+    exchange between the two CTAs that is relative to the partial scores' magnitude would show
+    directly in the weights.  Checked at the path's stated bar without loosening it."""
+    q, cache = wl.mla_inputs(2, 128, 1024, 576, 555)
+    q = (q.float() * gain).bfloat16()
+    # gains below one keep the outputs (values of the few positions the softmax picks) of order
+    # one, where the max-abs bound of 2e-2 is meaningful for BF16 results
+    position_gain = torch.linspace(0.2, 0.8, 1024).view(1, 1024, 1)
+    cache = (cache.float() * position_gain).bfloat16()
+    for splits in (1, 2):
+        out = kernels.mla_decode(q.to(DEV), cache.to(DEV), SCALE, kv_splits=splits).cpu()
+        expected = wl.mla_oracle(q, cache, SCALE, 512)
+        assert_close_bf16(out, expected, max_ulp=None, max_abs=2e-2)
+
+
+def test_heads_of_very_different_magnitude(kernels):
+    """Rows of very different magnitude in one tile: the exchange between the two CTAs scales
+    every head's partial scores by that head's own largest magnitude."""
+    q, cache = wl.mla_inputs(1, 128, 512, 576, 556)
+    head_gain = torch.cat([torch.full((64,), 1.0), torch.linspace(2.0, 12.0, 64)]).view(1, 128, 1)
+    q = (q.float() * head_gain).bfloat16()
+    out = kernels.mla_decode(q.to(DEV), cache.to(DEV), SCALE, kv_splits=1).cpu()
+    assert_close_bf16(out, wl.mla_oracle(q, cache, SCALE, 512), max_ulp=None, max_abs=2e-2)
+
+
 def test_full_size_properties(kernels):
     """batch 64 x 128 heads x 4096 positions: oracle on two batches, and the convexity
     property: with a cache whose value part is constant per batch, the output is that constant."""

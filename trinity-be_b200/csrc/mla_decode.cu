@@ -10,13 +10,21 @@
 //
 //   CTA c owns latent columns [256c, 256c+256) and rope features [32c, 32c+32).
 //   scores:  each CTA contracts only its 288 features (18 K-steps, N = 64 positions) into a
-//            partial score tile.  The partial tiles are rounded to FP16 and exchanged through
-//            distributed shared memory with a bulk asynchronous copy (16 KB per chunk and
-//            direction); each CTA adds the peer's rounded tile to its own exact FP32 tile.
-//            FP16 halves the exchange, which measures ~18 B/clk per SM and would otherwise
-//            bound the kernel; it costs 2^-11 relative precision on the peer's half of a logit.
-//            The two CTAs therefore hold logits that differ in the last bits; each normalises
-//            its own columns with its own sums, so every output column is a consistent softmax.
+//            partial score tile.  The partial tiles are exchanged through distributed shared
+//            memory with a bulk asynchronous copy in 16 bits per score (16.5 KB per chunk and
+//            direction); each CTA adds the peer's tile to its own exact FP32 tile.  Sixteen bits
+//            halve the exchange, which measures ~18 B/clk per SM and would otherwise bound the
+//            kernel.  The format is chosen per head and chunk from the largest magnitude `top` of
+//            the row's partials: FP16 values while top * |scale| * log2(e) <= 8 (their error,
+//            2^-11 of each partial, then stays below 2^-8 in the scaled log2 logit, 0.3 % in a
+//            weight); beyond that 16-bit integers in units of top / 32767, whose error is the same
+//            for every position of the row, 2^-16 of top (an error relative to each element, as
+//            FP16 has, would be 32 times larger on exactly the large partials that decide the
+//            weights).  Stated bound for the peer's half of a scaled log2 logit:
+//            max(2^-8, 2^-16 * top * |scale| * log2(e)), i.e. below 2^-7 up to scaled partials
+//            of 512.
+//            The two CTAs hold logits that differ in the last bits; each normalises its own
+//            columns with its own sums, so every output column is a consistent softmax.
 //   values:  each CTA multiplies its probabilities with its own 256 latent columns, which
 //            are exactly the cache bytes it already loaded for the scores
 //
@@ -64,7 +72,8 @@ constexpr int kPrefetchAhead = 4;              // chunks requested into L2 beyon
 constexpr int kBoxBytes = kKv * 128;           // 8192: one [64 positions x 64 features] box
 constexpr int kRopeBoxBytes = kKv * 64;        // 4096: [64 positions x 32 rope features]
 constexpr int kStageBytes = 4 * kBoxBytes + kRopeBoxBytes;  // 36864
-constexpr int kXchgBytes = 128 * kKv * 2;      // one partial score tile in FP16: 16384
+constexpr int kXchgTileBytes = 128 * kKv * 2;  // one partial score tile as 16-bit integers: 16384
+constexpr int kXchgBytes = kXchgTileBytes + 128 * 4;   // ... and one FP32 unit per row
 constexpr int kQueryBoxBytes = 128 * 64;       // [128 heads x 32 features] of the query
 constexpr int kQueryLandingBytes = 9 * kQueryBoxBytes;   // eight latent boxes and the rope box
 static_assert(kQueryLandingBytes <= 2 * kStageBytes && kKvStages >= 4, "the query lands in cache stages 2 and 3");
@@ -583,8 +592,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         // the scores are in registers: later score MMAs may overwrite the buffer
         tc_fence_before();
         if (__all_sync(0xffffffffu, !bad) && lane == 0) mbar_arrive(s_free);
-        // ---- FP16 copy for the peer: [8 groups of 8 positions][128 rows] (conflict-free), then
-        //      one thread starts the bulk asynchronous copy into the peer's receive tile.
+        // ---- 16-bit copy for the peer: [8 groups of 8 positions][128 rows] (conflict-free), FP16
+        //      or integers in units of 1/32767 of the row's largest magnitude, with the unit (0
+        //      for FP16) behind the tile; then one thread starts the bulk asynchronous copy into
+        //      the peer's receive tile.
         // The buffers were last used for chunk g-2, by another group.  Once that group has read
         // its receive tile, the exchange barriers of this buffer are in the phase this chunk
         // expects.
@@ -601,15 +612,43 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         }
         if (!bad) bad = !mbar_wait_cluster(x_empty(buf), phase ^ 1u, 0x604);
         if (!bad) {
+          // largest magnitude of the row: four chains of three-input maxima
+          float top4[4] = {fabsf(t[0]), fabsf(t[1]), fabsf(t[2]), fabsf(t[3])};
 #pragma unroll
-          for (int q8 = 0; q8 < 8; ++q8) {
-            uint32_t h[4];
+          for (int i = 4; i + 8 <= kKv; i += 8) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const __half2 v = __floats2half2_rn(t[q8 * 8 + 2 * e], t[q8 * 8 + 2 * e + 1]);
-              h[e] = *reinterpret_cast<const uint32_t*>(&v);
+            for (int e = 0; e < 4; ++e) top4[e] = fmaxf(fmaxf(top4[e], fabsf(t[i + e])), fabsf(t[i + 4 + e]));
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) top4[e] = fmaxf(top4[e], fabsf(t[kKv - 4 + e]));
+          const float top = fmaxf(fmaxf(top4[0], top4[1]), fmaxf(top4[2], top4[3]));
+          if (top * p.scale_log2 <= 8.0f) {
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+              uint32_t h[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __half2 v = __floats2half2_rn(t[q8 * 8 + 2 * e], t[q8 * 8 + 2 * e + 1]);
+                h[e] = *reinterpret_cast<const uint32_t*>(&v);
+              }
+              staged[q8 * 128 + row] = make_uint4(h[0], h[1], h[2], h[3]);
             }
-            staged[q8 * 128 + row] = make_uint4(h[0], h[1], h[2], h[3]);
+            reinterpret_cast<float*>(staged + kXchgTileBytes / 16)[row] = 0.0f;
+          } else {
+            // round(t * 32767 / top) lands in the low 16 bits of t * encode + 1.5 * 2^23
+            const float encode = 32767.0f / top;
+#pragma unroll
+            for (int q8 = 0; q8 < 8; ++q8) {
+              uint32_t h[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const uint32_t lo = __float_as_uint(fmaf(t[q8 * 8 + 2 * e], encode, 12582912.0f));
+                const uint32_t hi = __float_as_uint(fmaf(t[q8 * 8 + 2 * e + 1], encode, 12582912.0f));
+                h[e] = __byte_perm(lo, hi, 0x5410);
+              }
+              staged[q8 * 128 + row] = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+            reinterpret_cast<float*>(staged + kXchgTileBytes / 16)[row] = top * (1.0f / 32767.0f);
           }
         }
         fence_async_smem();
@@ -638,15 +677,30 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         }
         // ---- the peer's half of the scores
         if (!bad) bad = !mbar_wait_cluster(x_full(buf), phase, 0x605);
+        const float unit = reinterpret_cast<const float*>(received + kXchgTileBytes / 16)[row];
+        if (unit == 0.0f) {
 #pragma unroll
-        for (int q8 = 0; q8 < 8; ++q8) {
-          const uint4 other = received[q8 * 128 + row];
-          const uint32_t theirs[4] = {other.x, other.y, other.z, other.w};
+          for (int q8 = 0; q8 < 8; ++q8) {
+            const uint4 other = received[q8 * 128 + row];
+            const uint32_t theirs[4] = {other.x, other.y, other.z, other.w};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 c2 = __half22float2(*reinterpret_cast<const __half2*>(&theirs[e]));
-            t[q8 * 8 + 2 * e] += c2.x;
-            t[q8 * 8 + 2 * e + 1] += c2.y;
+            for (int e = 0; e < 4; ++e) {
+              const float2 c2 = __half22float2(*reinterpret_cast<const __half2*>(&theirs[e]));
+              t[q8 * 8 + 2 * e] += c2.x;
+              t[q8 * 8 + 2 * e + 1] += c2.y;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int q8 = 0; q8 < 8; ++q8) {
+            const uint4 other = received[q8 * 128 + row];
+            const uint32_t theirs[4] = {other.x, other.y, other.z, other.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const short lo = static_cast<short>(theirs[e] & 0xFFFFu), hi = static_cast<short>(theirs[e] >> 16);
+              t[q8 * 8 + 2 * e] = fmaf(static_cast<float>(lo), unit, t[q8 * 8 + 2 * e]);
+              t[q8 * 8 + 2 * e + 1] = fmaf(static_cast<float>(hi), unit, t[q8 * 8 + 2 * e + 1]);
+            }
           }
         }
         // This warp has read (and used) its part of the receive tile: tell the peer, whose next
@@ -665,10 +719,13 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
         }
         float mx4[4] = {t[0], t[1], t[2], t[3]};
 #pragma unroll
-        for (int i = 4; i < kKv; i += 4) {
+        for (int i = 4; i + 8 <= kKv; i += 8) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], t[i + e]);
+          for (int e = 0; e < 4; ++e)
+            asm("max.f32 %0, %0, %1, %2;" : "+f"(mx4[e]) : "f"(t[i + e]), "f"(t[i + 4 + e]));
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], t[kKv - 4 + e]);
         // position 0 of a chunk is always inside seq, so the maximum is finite
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
         // ---- reference maximum: take it over from the group that had chunk j-1, pass it on

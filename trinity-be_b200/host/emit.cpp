@@ -805,7 +805,7 @@ struct Emitter {
     launch.code = code.str();
     for (int i = 0; i < 5; ++i) launch.operations.push_back(top.body[i].operation);
     launch.operations.push_back(vloop.body[0].operation);
-    launch.shared_memory_bytes = 214528;   // four cache stages, four exchange tiles, barriers
+    launch.shared_memory_bytes = 216576;   // four cache stages, four exchange tiles, barriers
     launch.block_threads = 480;            // producer, two MMA issuers, twelve softmax warps
     launches.push_back(std::move(launch));
     return true;
