@@ -109,6 +109,11 @@ TRINITY_HOST_API int th_module_close(th_module*);
 TRINITY_HOST_API int th_module_live_executions(th_module*);
 TRINITY_HOST_API th_execution* th_execution_create(th_module*, void* const* bindings, size_t count,
                                                    void* ready_stream);
+/* Persistent (mode 2, multi-GPU) modules: the execution also owns the artifact's workspace, whose
+ * first bytes hold the peer table (src/native/abi.h:27-40, src/native/runtime.cpp:215-221). */
+TRINITY_HOST_API th_execution* th_execution_create_persistent(th_module*, void* const* bindings, size_t count,
+                                                              void* workspace, size_t workspace_bytes,
+                                                              unsigned workers, void* ready_stream);
 TRINITY_HOST_API void th_execution_free(th_execution*);
 TRINITY_HOST_API int th_execution_run(th_execution*, void* stream);
 TRINITY_HOST_API int th_execution_wait(th_execution*, double timeout_seconds);

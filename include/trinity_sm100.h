@@ -314,6 +314,44 @@ TRINITY_SM100_API size_t trinity_sm100_allreduce_flag_words(void);
 TRINITY_SM100_API int trinity_sm100_allreduce_bf16(const trinity_sm100_allreduce* args, void* stream);
 
 /*
+ * Peer table of a persistent (multi-GPU) artifact.  It occupies the first
+ * TRINITY_SM100_PEER_TABLE_BYTES of the artifact's workspace, in device memory, and is filled
+ * once by the runtime when an execution is prepared: the persistent launch block of the artifact
+ * ABI (src/native/abi.h:27-40) carries only the plan's bindings and the workspace pointer, so
+ * everything a kernel needs to reach the other GPUs is read from here on the device.  `epoch`
+ * and `counter` are advanced by the kernels themselves, which keeps a captured launch
+ * replayable; `flags` are written by the peers.  The workspace is symmetric memory: every
+ * rank's copy is mapped into every process.
+ */
+#define TRINITY_SM100_PEER_BUFFERS 4
+#define TRINITY_SM100_PEER_TABLE_BYTES 1024
+typedef struct trinity_sm100_peer_table {
+  int32_t world, rank;
+  uint32_t epoch;    /* collective launches completed on this rank (starts at 0) */
+  uint32_t counter;  /* thread blocks of the running launch that have finished   */
+  uint32_t failed;   /* epoch of the last launch in which a wait gave up         */
+  uint32_t reserved[3];
+  uint64_t workspace[8];                             /* every rank's workspace, as mapped here     */
+  uint64_t buffers[TRINITY_SM100_PEER_BUFFERS][8];   /* symmetric plan buffers, every rank's copy  */
+  uint32_t flags[64];                                /* written by the peers                        */
+} trinity_sm100_peer_table;
+
+/*
+ * Rank-major all-gather along axis 0 or 1 of a BF16 [rows, cols] shard (cols % 8 == 0):
+ *   out[q * rows + r, c] = shard_q[r, c]   (axis 0)      out[r, q * cols + c] = shard_q[r, c]   (axis 1)
+ * `workspace` is this rank's workspace with a filled peer table; the shards are symmetric buffer
+ * `source` of the table; `out` is local memory.  Pulls with plain 128-bit peer loads, bounded
+ * waits, no multicast; replayable inside a CUDA Graph (the call number lives in the table).
+ *
+ * Takes the place of the NVSHMEM all-gather the reference's plan language declares
+ * (src/analysis/plan/expression.rs:227-231, python/examples/plans.py:61-73,
+ *  src/emit/implementation/definitions/peer.rs:9-11), whose emission is unimplemented there
+ * (src/emit/native/mod.rs:161-165).
+ */
+TRINITY_SM100_API int trinity_sm100_allgather_bf16(void* workspace, int32_t source, void* out, int64_t rows,
+                                                   int64_t cols, int32_t axis, int32_t world, void* stream);
+
+/*
  * Row-parallel GEMM with the sum all-reduce fused into its epilogue:
  *   out (on every rank) = sum over ranks of A_rank[m,k] @ B_rank[k,n]        BF16, FP32 accumulate
  * Every rank calls this with its own shard (`gemm`: no bias, no activation, BF16 out) and the

@@ -242,6 +242,34 @@ def test_world_size_other_than_one_is_refused_like_the_reference():
         tl.emit(plans.gemm_bias(256, 256, 128, world_size=2))
 
 
+def test_all_gather_plans_become_persistent_artifacts():
+    """A multi-GPU plan whose statements are rank-major all-gathers (python/examples/plans.py:61-73
+    there) is emitted as a persistent artifact: mode 2 in the descriptor, PersistentLaunch in
+    trinity_launch, the shard a symmetric buffer, a workspace that starts with the peer table."""
+    for axis in (0, 1):
+        source = tl.emit(plans.gather(axis=axis, world_size=4))
+        assert source.launch_count == 1 and "trinity_sm100_allgather_bf16(workspace, 0, bindings[1], 128, 128, "\
+            f"{axis}, 4, stream)" in source.code
+        assert "PersistentLaunch const* launch_args" in source.code and "describe(2," in source.code
+        needs = json.loads(source._native.requirements_json())
+        assert needs["world_size"] == 4 and needs["workspace_bytes"] == 1024 and needs["workspace_symmetric"]
+        assert [b["symmetric"] for b in needs["buffers"]] == [True, False]
+        assert needs["buffers"][1]["shape"] == ([512, 128] if axis == 0 else [128, 512])
+    artifact = tl.compile(tl.emit(plans.gather(axis=1, world_size=2)))
+    try:
+        manifest = json.loads((artifact.directory / "manifest.json").read_text())
+        assert manifest["execution"] == "persistent" and manifest["requirements"]["nvshmem"] is True
+        exported = subprocess.run(["nm", "-D", "--defined-only", str(artifact.directory / "program.so")],
+                                  capture_output=True, text=True, check=True).stdout.split()
+        assert sorted(n for n in exported if n.startswith("trinity_")) == [
+            "trinity_abi", "trinity_launch", "trinity_prepare", "trinity_release", "trinity_status"]
+    finally:
+        artifact.close()
+    # a shard whose rows are not multiples of 16 bytes, or a destination of the wrong extent, is declined
+    with pytest.raises(NotImplementedError, match="all_gather"):
+        tl.emit(plans.gather(axis=0, world_size=2, rows=64, cols=68))
+
+
 def test_hazards_are_errors():
     # tests/plan_access.rs:213-249: overlapping tiles and partial coverage
     def tiled(step, stop):
@@ -281,8 +309,16 @@ def test_kernel_candidates_list_per_operation_offers_and_rejections():
     assert bad["0"]["candidates"] == []
     reasons = {r["provider"]: r["reason"] for r in bad["0"]["rejections"]}
     assert "overlap between CTAs" in reasons["sm100.pointwise"]
+    # single-GPU kernels are not offered to multi-GPU plans, whose collective has its own recogniser
+    multi = tl.kernel_candidates(plans.gemm_bias(256, 256, 128, world_size=2))
+    assert multi["0"]["candidates"] == [] and any("Persistent" in r["reason"] for r in multi["0"]["rejections"])
+    gathered = tl.kernel_candidates(plans.gather(axis=0, world_size=2))
+    assert [c["provider"] for c in gathered["0"]["candidates"]] == ["sm100.all_gather"]
     # plan-level refusals stay plan-level, as the reference's prepare step fails the whole call
-    assert "Persistent" in tl.kernel_candidates(plans.gemm_bias(256, 256, 128, world_size=2))["error"]
+    b = tl.PhysicalPlanBuilder()
+    x = b.add_value("fp16", [64], "external", name="X")
+    b.bind_input("X", x)
+    assert "fp16" in tl.kernel_candidates(b.build([], "Y", x))["error"]
 
 
 def test_unsupported_operations_report_no_provider():
@@ -453,6 +489,46 @@ def test_text_reader_grammar_and_located_errors():
             tl.lower_ir(text, {}, dtypes)
     with pytest.raises(ValueError, match="missing dtype"):
         tl.lower_ir(base, {}, {"X": "bf16"})
+
+
+def test_split_loops_and_view_operators_of_the_attention_fixtures():
+    """`mloop` is normalised to a parallel loop over the split around a sequential loop over the
+    split's share (src/analysis/plan/ir.rs:527-599 there); `permute`, `bcast`, `unsqueeze` and
+    `elem` accesses are read in the spelling of the reference's batched-MLA fixtures
+    (tests/fixtures/batched_mla/batched_mla_postprocessed_stage14.txt:27-56 there)."""
+    def view(kind, name):
+        return f"(view ({kind} {name}) (layout (axis a 256)))"
+    tile = "(keyed_index (slot a (tile c 64)))"
+    body = f"(store {view('output', 'Y')} (relu (load {view('input', 'X')} {tile})) {tile})"
+    dtypes = {"X": "bf16", "Y": "bf16"}
+    (split,) = tl.lower_ir(f"(mloop 0 256 64 c s 2 {body})", {}, dtypes)
+    (nest,) = tl.lower_ir(f"(ploop 0 2 1 s (sloop (+ 0 (* s 128)) (+ (+ 0 (* s 128)) 128) 64 c {body}))", {}, dtypes)
+    assert split.same_body(nest)
+    loops = json.loads(split.metadata_json())["statements"][0]["loop"]
+    assert loops["kind"] == "parallel" and loops["domain"]["stop"] == {"Constant": 2}
+    assert loops["body"][0]["loop"]["kind"] == "sequential"
+    for text, fragment in ((f"(mloop 0 256 64 c s 3 {body})", "mloop split must exactly divide"),
+                           (f"(mloop 0 256 96 c s 2 {body})", "mloop split must exactly divide"),
+                           (f"(ploop 0 4 1 s (mloop 0 256 64 c s 2 {body}))", "split variable shadows an active loop"),
+                           (f"(sloop 0 4 1 k (mloop 0 256 64 c s 2 {body}))", "parallel work inside")):
+        with pytest.raises(ValueError, match=fragment):
+            tl.lower_ir(text, {}, dtypes)
+
+    def projection(axes):
+        q = "(view (input Q) (layout (axis b 4) (axis h 16) (axis k 128)))"
+        w = "(view (input W) (layout (axis k 128) (axis m 512)))"
+        t = "(view (output T) (layout (axis b 4) (axis h 16) (axis m 512)))"
+        at = "(keyed_index (slot b (tile b 2)) (slot h (elem n)) (slot m (tile m 128)))"
+        return (f"(ploop 0 4 2 b (ploop 0 16 1 n (ploop 0 512 128 m (store {t} (@ (load {q} (keyed_index (slot b (tile b 2)) "
+                f"(slot h (elem n)) (slot k fulltile))) (permute (bcast (load {w} (keyed_index (slot k fulltile) "
+                f"(slot m (tile m 128)))) 0) {axes})) {at}))))")
+    dtypes = {"Q": "bf16", "W": "bf16", "T": "bf16"}
+    (plan,) = tl.lower_ir(projection("0 2 1"), {}, dtypes)
+    assert not plan.same_body(tl.lower_ir(projection("0 1 2"), {}, dtypes)[0])
+    with pytest.raises(ValueError, match="permute axes must be a permutation"):
+        tl.lower_ir(projection("0 2 2"), {}, dtypes)
+    found = tl.kernel_candidates(plan)["0"]       # no kernel region has this form yet: recorded, not hidden
+    assert found["candidates"] == [] and found["rejections"]
 
 
 def test_text_reader_rejects_hazards_where_the_reference_does():

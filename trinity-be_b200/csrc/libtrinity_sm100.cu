@@ -7,3 +7,4 @@
 #include "pointwise.cu"
 #include "mla_decode.cu"
 #include "allreduce.cu"
+#include "allgather.cu"

@@ -126,7 +126,8 @@ Artifact compile(const CudaSource& source, const CompileConfig& config) {
     throw CompileFailure(kind, "host compiler exited with " + std::to_string(r.exit_code), artifact.diagnostics_json);
   }
   std::ostringstream manifest;
-  manifest << "{\"schema_version\":1,\"host_abi_version\":1,\"execution\":\"streamed\",\"library\":\"program.so\","
+  manifest << "{\"schema_version\":1,\"host_abi_version\":1,\"execution\":\"" << (source.persistent ? "persistent" : "streamed")
+           << "\",\"library\":\"program.so\","
            << "\"source\":\"source.cu\",\"requirements\":" << source.requirements_json << ",\"toolchain\":{\"nvcc\":null,"
            << "\"cuda_major\":12,\"kernel_library\":\"" << json_escape(library_dir + "/libtrinity_sm100.so")
            << "\",\"cutlass\":null,\"nvshmem\":null,\"nvshmem_library_directory\":null,\"host_compiler\":\""

@@ -222,6 +222,13 @@ th_execution* th_execution_create(th_module* m, void* const* bindings, size_t co
     return new th_execution{std::make_shared<Execution>(m->module, std::vector<void*>(bindings, bindings + count), ready_stream)};
   }, nullptr);
 }
+th_execution* th_execution_create_persistent(th_module* m, void* const* bindings, size_t count, void* workspace,
+                                             size_t workspace_bytes, unsigned workers, void* ready_stream) {
+  return guarded([&]() -> th_execution* {
+    return new th_execution{std::make_shared<Execution>(m->module, std::vector<void*>(bindings, bindings + count),
+                                                        ready_stream, workspace, workspace_bytes, workers)};
+  }, nullptr);
+}
 void th_execution_free(th_execution* e) { delete e; }
 int th_execution_run(th_execution* e, void* stream) { return guarded([&] { e->execution->run(stream); return 0; }, -1); }
 int th_execution_wait(th_execution* e, double timeout) { return guarded([&] { e->execution->wait(timeout); return 0; }, -1); }

@@ -811,9 +811,76 @@ struct Emitter {
     return true;
   }
 
+  // ------------------------------------------------------------------ all-gather (multi-GPU plans)
+  // ploop row { ploop col { (all_gather X[tile row, tile col] Y[tile row, tile col] axis) } } with
+  // X [R, C] on every rank and Y [R * world, C] (axis 0) or [R, C * world] (axis 1): one launch
+  // of the peer-memory all-gather.  X becomes a symmetric buffer (every rank's copy mapped
+  // everywhere) and the artifact a persistent one whose workspace holds the peer table.
+  bool try_all_gather(const Statement& top) {
+    std::vector<LoopInfo> loops;
+    const Statement* leaf = &top;
+    if (top.is_loop) {
+      const std::vector<Statement>* body = strip_parallel(top, loops);
+      if (!body || body->size() != 1 || (*body)[0].is_loop) return false;
+      leaf = &(*body)[0];
+    }
+    const Operation& op = plan.operations[leaf->operation];
+    const Expression& e = *op.expression;
+    if (e.kind != Expression::AllGather) return false;
+    const Value &x = value(e.source.value), &y = value(e.access.value);
+    auto decline = [&](const std::string& why) { rejections.push_back("sm100.all_gather: " + why); return false; };
+    if (x.dtype != DType::Bf16 || y.dtype != DType::Bf16) return decline("shards must be bf16");
+    if (x.shape.size() != 2 || y.shape.size() != 2 || (e.axis != 0 && e.axis != 1)) return decline("rank-2 shards along axis 0 or 1");
+    const int64_t rows = x.shape[0], cols = x.shape[1];
+    if (y.shape[e.axis] != x.shape[e.axis] * plan.world_size || y.shape[1 - e.axis] != x.shape[1 - e.axis])
+      return decline("destination must be the shard extent times the world size along the axis");
+    if (cols % 8) return decline("shard rows must be multiples of 16 bytes");
+    if (x.storage != Storage::External) return decline("the shard must be an external (bound) value");
+    if (!e.source.view_shape.empty() || !e.access.view_shape.empty()) return decline("views are not gathered");
+    // the tile loops must walk the whole shard exactly once
+    for (int axis = 0; axis < 2; ++axis) {
+      const AccessIndex& index = e.source.indices[axis];
+      if (index != e.access.indices[axis]) return decline("source and destination must be indexed alike");
+      if (index.kind == AccessIndex::FullTile) continue;
+      const LoopInfo* loop = find_loop(loops, index.variable);
+      if (!loop) return decline("index variable " + index.variable + " is not a parallel loop of the region");
+      check_parallel_axis(index, *loop, x.shape[axis], "all_gather");
+    }
+    buffers[slot(e.source.value)].symmetric = true;
+    need_alignment(e.source.value, 16);
+    need_alignment(e.access.value, 16);
+    int symmetric_index = 0;
+    for (int b = 0; b < slot(e.source.value); ++b)
+      if (buffers[b].symmetric) ++symmetric_index;
+    Launch launch;
+    launch.kernel = "trinity_sm100_allgather_bf16";
+    std::ostringstream c;
+    c << "  rc = trinity_sm100_allgather_bf16(workspace, " << symmetric_index << ", " << slot_ptr(slot(e.access.value)) << ", "
+      << rows << ", " << cols << ", " << e.axis << ", " << plan.world_size << ", stream);\n";
+    launch.code = c.str();
+    launch.operations.push_back(leaf->operation);
+    launch.block_threads = 512;
+    launches.push_back(std::move(launch));
+    return true;
+  }
+
   void run() {
     check_plan();
     build_buffers();
+    if (plan.world_size != 1) {
+      // A multi-GPU plan becomes a persistent artifact; what it may contain today is the
+      // rank-major all-gather (the reference's own emitter refuses every multi-GPU plan,
+      // src/emit/native/mod.rs:161-165).
+      for (auto& s : plan.statements) {
+        rejections.clear();
+        if (try_all_gather(s)) continue;
+        std::string reasons;
+        for (auto& r : rejections) reasons += (reasons.empty() ? "" : "; ") + r;
+        unsupported("UnsupportedExecution: Persistent emission covers all_gather plans only" +
+                    (reasons.empty() ? std::string() : " (" + reasons + ")"));
+      }
+      return;
+    }
     for (auto& s : plan.statements) {
       rejections.clear();
       if (try_gemm(s) || try_rmsnorm(s) || try_softmax(s) || try_mla(s) || try_row_reduce(s) || try_pointwise(s)) continue;
@@ -836,8 +903,8 @@ struct Emitter {
     std::string reason;             // when not
   };
   void check_plan() {
-    if (plan.world_size != 1)
-      unsupported("UnsupportedExecution: Persistent emission is not implemented");
+    if (plan.world_size < 1 || plan.world_size > 8)
+      unsupported("UnsupportedExecution: Persistent emission serves worlds of up to 8 GPUs in one NVLink domain");
     if (!plan.symbols().empty())
       throw PlanError(ErrorKind::Value, "InvalidExecution: plan has unbound symbols; call bind_symbols first");
     for (auto& v : plan.values)
@@ -849,13 +916,22 @@ struct Emitter {
     const std::pair<const char*, Recogniser> recognisers[] = {
         {"sm100.gemm", &Emitter::try_gemm},         {"sm100.rmsnorm", &Emitter::try_rmsnorm},
         {"sm100.softmax", &Emitter::try_softmax},   {"sm100.mla_decode", &Emitter::try_mla},
-        {"sm100.row_reduce", &Emitter::try_row_reduce}, {"sm100.pointwise", &Emitter::try_pointwise}};
+        {"sm100.row_reduce", &Emitter::try_row_reduce}, {"sm100.pointwise", &Emitter::try_pointwise},
+        {"sm100.all_gather", &Emitter::try_all_gather}};
     std::vector<Offer> result;
     for (auto& [name, recogniser] : recognisers) {
       Offer offer;
       offer.provider = name;
       const size_t before = launches.size();
       rejections.clear();
+      const bool collective = recogniser == &Emitter::try_all_gather;
+      if (collective != (plan.world_size != 1)) {
+        // single-GPU kernels serve streamed plans, the collective serves multi-GPU plans
+        offer.reason = collective ? "all_gather needs a multi-GPU plan"
+                                  : "UnsupportedExecution: Persistent emission covers all_gather plans only";
+        result.push_back(std::move(offer));
+        continue;
+      }
       try {
         offer.matched = (this->*recogniser)(s);
       } catch (const PlanError& declined) {
@@ -900,20 +976,27 @@ std::string requirements_json(const PhysicalPlan& plan, const std::vector<Buffer
     out << "],\"dtype\":\"" << dtype_name(b.dtype) << "\",\"strides\":[";
     for (size_t k = 0; k < b.strides.size(); ++k) out << (k ? "," : "") << b.strides[k];
     out << "],\"bytes\":" << b.bytes << ",\"alignment\":" << b.alignment << ",\"external\":" << (b.external ? "true" : "false")
-        << ",\"symmetric\":false}";
+        << ",\"symmetric\":" << (b.symmetric ? "true" : "false") << "}";
   }
   int smem = 0, threads = 128;
   for (auto& l : launches) {
     smem = std::max(smem, l.shared_memory_bytes);
     threads = std::max(threads, l.block_threads);
   }
-  out << "],\"workspace_bytes\":0,\"workspace_alignment\":1,\"workspace_symmetric\":false,\"cooperative_launch\":false,"
-      << "\"shared_memory_bytes\":" << smem << ",\"block_threads\":" << threads << ",\"nvshmem\":false,\"nvls\":false}";
+  // A multi-GPU artifact is persistent: its workspace (symmetric memory) starts with the peer
+  // table the kernels read.  The manifest keeps the reference's field names: `nvshmem` says that
+  // the artifact needs a World (here: peer-mapped symmetric memory, not NVSHMEM) and
+  // `cooperative_launch` that the ranks' grids must be running at the same time.
+  const bool multi = plan.world_size > 1;
+  out << "],\"workspace_bytes\":" << (multi ? 1024 : 0) << ",\"workspace_alignment\":" << (multi ? 256 : 1)
+      << ",\"workspace_symmetric\":" << (multi ? "true" : "false") << ",\"cooperative_launch\":" << (multi ? "true" : "false")
+      << ",\"shared_memory_bytes\":" << smem << ",\"block_threads\":" << threads << ",\"nvshmem\":"
+      << (multi ? "true" : "false") << ",\"nvls\":false}";
   return out.str();
 }
 
 std::string render(const std::string& requirements, const std::vector<BufferRequirement>& buffers,
-                   const std::vector<Launch>& launches) {
+                   const std::vector<Launch>& launches, bool persistent) {
   std::ostringstream c;
   c << "// Generated by the sm_100a provider: host shim over libtrinity_sm100.so (no device code here).\n"
     << "#include <cstdint>\n#include <cstring>\n\n";
@@ -923,13 +1006,15 @@ std::string render(const std::string& requirements, const std::vector<BufferRequ
   for (auto& b : buffers) c << b.alignment << ", ";
   c << "1};\nint prepared_device = -1;\n}  // namespace\n\n";
   c << "#define TRINITY_EXPORT extern \"C\" __attribute__((visibility(\"default\")))\n\n";
-  c << "TRINITY_EXPORT Descriptor const* trinity_abi() {\n  static const Descriptor d = describe(1, kRequirements, sizeof(kRequirements) - 1);\n  return &d;\n}\n\n";
+  c << "TRINITY_EXPORT Descriptor const* trinity_abi() {\n  static const Descriptor d = describe(" << (persistent ? 2 : 1)
+    << ", kRequirements, sizeof(kRequirements) - 1);\n  return &d;\n}\n\n";
   c << "TRINITY_EXPORT int trinity_prepare(unsigned* maximum_workers, ErrorInfo* error) {\n"
     << "  if (!maximum_workers) return report(error, generated, -1, validate);\n"
     << "  std::int32_t device = -1;\n  const int rc = trinity_sm100_prepare_device(&device);\n"
     << "  if (rc) return report(error, runtime, rc, prepare);\n"
     << "  prepared_device = device;\n  *maximum_workers = 1;\n  return report(error, none, 0, prepare);\n}\n\n";
-  c << "TRINITY_EXPORT int trinity_launch(StreamedLaunch const* launch_args, ErrorInfo* error) {\n"
+  c << "TRINITY_EXPORT int trinity_launch(" << (persistent ? "PersistentLaunch" : "StreamedLaunch")
+    << " const* launch_args, ErrorInfo* error) {\n"
     << "  if (!launch_args || prepared_device < 0) return report(error, generated, -1, validate);\n"
     << "  std::int32_t device = -1;\n"
     << "  if (trinity_sm100_current_device(&device) || device != prepared_device) return report(error, generated, -2, validate);\n"
@@ -938,12 +1023,19 @@ std::string render(const std::string& requirements, const std::vector<BufferRequ
     << "  for (std::size_t i = 0; i < kBindingCount; ++i)\n"
     << "    if (!bindings[i] || reinterpret_cast<std::uintptr_t>(bindings[i]) % kAlignment[i]) return report(error, generated, -4, validate);\n"
     << "  void* stream = launch_args->stream;\n  int rc = 0;\n  (void)stream; (void)bindings;\n";
+  if (persistent)
+    c << "  // the workspace starts with the peer table the kernels read on the device\n"
+      << "  void* workspace = launch_args->workspace;\n"
+      << "  if (!workspace || launch_args->workspace_bytes < TRINITY_SM100_PEER_TABLE_BYTES ||\n"
+      << "      reinterpret_cast<std::uintptr_t>(workspace) % 256 || launch_args->worker_count != 1)\n"
+      << "    return report(error, generated, -4, validate);\n";
   for (size_t i = 0; i < launches.size(); ++i) {
     c << "  // launch " << i << ": " << launches[i].kernel << "\n" << launches[i].code
       << "  if (rc) return report(error, runtime, rc, launch, " << (i > 0 ? "true" : "false") << ");\n";
   }
   c << "  return report(error, none, 0, launch, " << (launches.empty() ? "false" : "true") << ");\n}\n\n";
-  c << "TRINITY_EXPORT int trinity_status(void* stream, ErrorInfo* error) {\n"
+  c << "TRINITY_EXPORT int trinity_status(" << (persistent ? "void const* workspace, " : "") << "void* stream, ErrorInfo* error) {\n"
+    << (persistent ? "  (void)workspace;\n" : "")
     << "  int rc = trinity_sm100_stream_synchronize(stream);\n  if (rc) return report(error, runtime, rc, completion, true);\n"
     << "  std::uint32_t status = 0;\n  rc = trinity_sm100_device_status(&status, 0);\n"
     << "  if (rc) return report(error, runtime, rc, completion, true);\n"
@@ -959,8 +1051,9 @@ CudaSource emit(const PhysicalPlan& plan) {
   Emitter e(plan);
   e.run();
   CudaSource source;
+  source.persistent = plan.world_size > 1;
   source.requirements_json = requirements_json(plan, e.buffers, e.launches);
-  source.code = render(source.requirements_json, e.buffers, e.launches);
+  source.code = render(source.requirements_json, e.buffers, e.launches, source.persistent);
   source.launches = std::move(e.launches);
   source.buffers = std::move(e.buffers);
   return source;

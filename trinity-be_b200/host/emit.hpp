@@ -19,6 +19,7 @@ struct BufferRequirement {
   int64_t bytes;
   int alignment;
   bool external;
+  bool symmetric = false;   // multi-GPU plans: every rank's copy is mapped into every process
 };
 
 // One kernel-library call of the generated launch list.
@@ -31,6 +32,7 @@ struct Launch {
 };
 
 struct CudaSource {
+  bool persistent = false;   // mode 2 (multi-GPU, PersistentLaunch) instead of mode 1 (streamed)
   std::string code;
   std::string requirements_json;
   std::vector<Launch> launches;

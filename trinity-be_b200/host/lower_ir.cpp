@@ -5,8 +5,10 @@
 // (src/analysis/plan/ir.rs:85-128, :494-633) and its storage rule in brief
 // (src/analysis/storage/mod.rs:127-141, :197-234): declared inputs and outputs are External; a
 // written tensor touched by one top-level kernel only and always through the same index and
-// view lives in a Register; every other tensor is Global.  mloop (split loops) are not read:
-// the native provider rejects them anyway (src/emit/native/mod.rs:174-185).
+// view lives in a Register; every other tensor is Global.  A split loop
+// (mloop start stop step var split count body) is normalised as the reference does
+// (src/analysis/plan/ir.rs:527-599): a parallel loop over `split` in [0, count) around a
+// sequential loop of `var` over the split's equal share of [start, stop).
 //
 // Three of the reference reader's rejections are restated with their message fragments
 // (src/analysis/storage/mod.rs:303-312, :352-363; tests/streamed.rs:183-190, tests/ir.rs:52-63
@@ -122,6 +124,36 @@ struct Reader {
       }
       loops.push_back(scope);
       collect(a[4], kernel, false);
+      loops.pop_back();
+      return;
+    }
+    if (n.op() == "mloop") {
+      // parallel over the split variable, sequential over the loop variable within a share
+      const auto& a = n.args(7);
+      LoopScope outer, inner;
+      outer.variable = a[4].atom();
+      outer.parallel = true;
+      for (auto& enclosing : loops)
+        if (!enclosing.parallel)
+          throw SyntaxError(n.offset, "parallel work inside a sequential loop (" + enclosing.variable + ") is not supported");
+      inner.variable = a[3].atom();
+      try {
+        outer.start = 0;
+        outer.stop = number(a[5]);
+        outer.step = 1;
+        outer.numeric = outer.stop > 0;
+        // over all splits the inner variable walks the whole range with the loop's own step
+        inner.start = number(a[0]);
+        inner.stop = number(a[1]);
+        inner.step = number(a[2]);
+        inner.numeric = inner.step > 0;
+      } catch (const SyntaxError&) {
+        outer.numeric = inner.numeric = false;
+      }
+      loops.push_back(outer);
+      loops.push_back(inner);
+      collect(a[6], kernel, false);
+      loops.pop_back();
       loops.pop_back();
       return;
     }
@@ -380,7 +412,39 @@ std::vector<PhysicalPlan> lower_ir(const std::string& text, const std::map<std::
                                             start, stop, step, body));
         return out;
       }
-      if (n.op() == "mloop") throw SyntaxError(n.offset, "split loops (mloop) are not read by the native path");
+      if (n.op() == "mloop") {
+        const auto& a = n.args(7);
+        const std::string& variable = a[3].atom();
+        const std::string& split = a[4].atom();
+        IndexExpr start = index(a[0], scope), stop = index(a[1], scope), step = index(a[2], scope);
+        auto nested = scope;
+        if (!nested.insert(variable).second) throw SyntaxError(n.offset, "shadowed loop variable " + variable);
+        if (!nested.insert(split).second) throw SyntaxError(a[4].offset, "split variable shadows an active loop");
+        const int64_t count = reader.number(a[5]);
+        const IndexExpr first = start.bind({}), last = stop.bind({}), stride = step.bind({});
+        if (!first.is_constant() || !last.is_constant())
+          throw SyntaxError(n.offset, "mloop bounds must be numbers once the symbols are bound");
+        const int64_t extent = last.value - first.value;
+        if (count <= 0 || extent <= 0 || extent % count != 0 ||
+            (stride.is_constant() && (stride.value <= 0 || (extent / count) % stride.value != 0)))
+          throw SyntaxError(n.offset, "mloop split must exactly divide the iteration range");
+        const int64_t chunk = extent / count;
+        IndexExpr share;
+        share.kind = IndexExpr::Mul;
+        share.operands = {IndexExpr::variable(split), IndexExpr::constant(chunk)};
+        IndexExpr inner_start;
+        inner_start.kind = IndexExpr::Add;
+        inner_start.operands = {IndexExpr::constant(first.value), share};
+        IndexExpr inner_stop;
+        inner_stop.kind = IndexExpr::Add;
+        inner_stop.operands = {inner_start, IndexExpr::constant(chunk)};
+        std::vector<int> body = statements(a[6], nested);
+        if (body.empty()) throw SyntaxError(n.offset, "empty loop body");
+        const int inner = builder.add_loop_expr(LoopKind::Sequential, variable, inner_start, inner_stop, step, body);
+        out.push_back(builder.add_loop_expr(LoopKind::Parallel, split, IndexExpr::constant(0), IndexExpr::constant(count),
+                                            IndexExpr::constant(1), {inner}));
+        return out;
+      }
       if (n.op() == "store") {
         ExprPtr e = decode_expression(n, builder.values(), &symbols);
         std::vector<int> reads;

@@ -178,6 +178,7 @@ static const char* op_token(Expression::Kind k) {
     case Expression::Relu: return "relu";
     case Expression::Exp: return "exp";
     case Expression::Transpose: return "transpose";
+    case Expression::Permute: return "permute";
     case Expression::ReduceSum: return "rsum";
     case Expression::ReduceMax: return "rmax";
     case Expression::Broadcast: return "bcast";
@@ -235,6 +236,11 @@ std::string Expression::text() const {
     case AllReduce: return "(all_reduce " + access_text(source) + " " + access_text(access) + ")";
     case ReduceSum: case ReduceMax: case Broadcast: case Unsqueeze:
       return std::string("(") + op_token(kind) + " " + args[0]->text() + " " + std::to_string(axis) + ")";
+    case Permute: {
+      std::string s = "(permute " + args[0]->text();
+      for (int a : axes) s += " " + std::to_string(a);
+      return s + ")";
+    }
     default: {
       std::string s = std::string("(") + op_token(kind);
       for (auto& a : args) s += " " + a->text();
@@ -340,6 +346,21 @@ struct Decoder {
     if (op == "relu") return unary(Expression::Relu, n);
     if (op == "exp") return unary(Expression::Exp, n);
     if (op == "transpose") return unary(Expression::Transpose, n);
+    if (op == "permute") {
+      // (permute value a0 a1 ...): result axis i is source axis a_i (the reference's ValueOp::Permute,
+      // src/analysis/plan/expression.rs:164-181, as its batched-MLA fixtures spell it)
+      if (n.children.size() < 3) throw SyntaxError(n.offset, "'permute' expects a value and at least two axes");
+      e->kind = Expression::Permute;
+      e->args = {expression(n.children[0])};
+      std::vector<bool> seen(n.children.size() - 1, false);
+      for (size_t i = 1; i < n.children.size(); ++i) {
+        const int a = axis(n.children[i]);
+        if (a < 0 || a >= int(seen.size()) || seen[a]) throw SyntaxError(n.children[i].offset, "permute axes must be a permutation");
+        seen[a] = true;
+        e->axes.push_back(a);
+      }
+      return e;
+    }
     if (op == "rsum") return with_axis(Expression::ReduceSum, n);
     if (op == "rmax") return with_axis(Expression::ReduceMax, n);
     if (op == "bcast") return with_axis(Expression::Broadcast, n);

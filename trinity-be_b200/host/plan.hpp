@@ -88,7 +88,7 @@ using ExprPtr = std::shared_ptr<Expression>;
 struct Expression {
   enum Kind {
     ConstInt, ConstF32, Load, Store, Add, Sub, Mul, Div, Matmul, Max, Sqr, Sqrt, Sigmoid, Relu,
-    Exp, Transpose, ReduceSum, ReduceMax, Broadcast, Unsqueeze, AllGather, AllReduce
+    Exp, Transpose, Permute, ReduceSum, ReduceMax, Broadcast, Unsqueeze, AllGather, AllReduce
   } kind = ConstInt;
   int64_t integer = 0;
   uint32_t f32_bits = 0;
@@ -96,6 +96,7 @@ struct Expression {
   TensorAccess source;        // AllGather/AllReduce source
   std::vector<ExprPtr> args;  // operands (Store: the stored value)
   int axis = 0;
+  std::vector<int> axes;      // Permute: source axis of every result axis
 
   bool is_pure() const;                       // no Store / collective inside
   void reads(std::vector<int>& out) const;    // value ids loaded, first-use order, unique

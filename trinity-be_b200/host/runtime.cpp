@@ -213,7 +213,7 @@ void Library::release() {
 
 // ------------------------------------------------------------------ Module
 Module::Module(const std::string& path, int device, unsigned mode) : device_(device), mode_(mode) {
-  if (mode != 1) throw std::invalid_argument("only streamed (mode 1) artifacts are supported by this runtime");
+  if (mode != 1 && mode != 2) throw std::invalid_argument("artifact mode must be 1 (streamed) or 2 (persistent)");
   DeviceGuard guard(device);
   cuda_check("cudaFree(0)", cudaFree(nullptr));
   int runtime = 0;
@@ -249,10 +249,14 @@ void Module::close() {
 }
 
 // ------------------------------------------------------------------ Execution
-Execution::Execution(std::shared_ptr<Module> module, std::vector<void*> bindings, void* ready_stream)
-    : module_(std::move(module)), bindings_(std::move(bindings)) {
+Execution::Execution(std::shared_ptr<Module> module, std::vector<void*> bindings, void* ready_stream,
+                     void* workspace, size_t workspace_bytes, unsigned workers)
+    : module_(std::move(module)), bindings_(std::move(bindings)), workspace_(workspace),
+      workspace_bytes_(workspace_bytes), workers_(workers) {
   std::lock_guard<std::recursive_mutex> lock(module_->mutex_);
   if (!module_->library_ || !module_->library_->prepared()) throw std::invalid_argument("module is not prepared");
+  if ((module_->mode_ == 2) != (workspace != nullptr))
+    throw std::invalid_argument("a persistent module needs a workspace, a streamed one has none");
   DeviceGuard guard(module_->device_);
   for (size_t i = 0; i < bindings_.size(); ++i)
     if (!bindings_[i]) throw std::invalid_argument("binding " + std::to_string(i) + " is null");
@@ -292,10 +296,26 @@ void Execution::run(void* stream_handle) {
   if (!capturing && pending() && stream != last_stream_)
     throw ResourceBusy("execution has pending work on another stream");
   if (!capturing) cuda_check("cudaStreamWaitEvent", cudaStreamWaitEvent(stream, ready_, 0));
-  abi::StreamedLaunch launch{bindings_.data(), bindings_.size(), stream_handle};
   abi::ErrorInfo info{};
-  auto fn = reinterpret_cast<int (*)(abi::StreamedLaunch const*, abi::ErrorInfo*)>(module_->library_->launch_symbol());
-  const int rc = fn(&launch, &info);
+  int rc;
+  if (module_->mode_ == 2) {
+    abi::PersistentLaunch launch{};
+    launch.bindings = bindings_.data();
+    launch.binding_count = bindings_.size();
+    launch.workspace = workspace_;
+    launch.workspace_bytes = workspace_bytes_;
+    launch.stream = stream_handle;
+    launch.worker_count = workers_;
+    launch.delay_rank = -1;
+    launch.delay_task = -1;
+    launch.delay_cycles = 0;
+    auto fn = reinterpret_cast<int (*)(abi::PersistentLaunch const*, abi::ErrorInfo*)>(module_->library_->launch_symbol());
+    rc = fn(&launch, &info);
+  } else {
+    abi::StreamedLaunch launch{bindings_.data(), bindings_.size(), stream_handle};
+    auto fn = reinterpret_cast<int (*)(abi::StreamedLaunch const*, abi::ErrorInfo*)>(module_->library_->launch_symbol());
+    rc = fn(&launch, &info);
+  }
   if (rc) {
     failed_ = true;
     failure_ = info;
@@ -343,8 +363,14 @@ void Execution::wait(double timeout_seconds) {
   std::lock_guard<std::recursive_mutex> lock(module_->mutex_);
   if (module_->library_) {
     abi::ErrorInfo info{};
-    auto fn = reinterpret_cast<int (*)(void*, abi::ErrorInfo*)>(module_->library_->status_symbol());
-    const int rc = fn(stream, &info);
+    int rc;
+    if (module_->mode_ == 2) {
+      auto fn = reinterpret_cast<int (*)(void const*, void*, abi::ErrorInfo*)>(module_->library_->status_symbol());
+      rc = fn(workspace_, stream, &info);
+    } else {
+      auto fn = reinterpret_cast<int (*)(void*, abi::ErrorInfo*)>(module_->library_->status_symbol());
+      rc = fn(stream, &info);
+    }
     if (rc) {
       failed_ = true;
       failure_ = info;

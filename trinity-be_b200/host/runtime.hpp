@@ -66,6 +66,7 @@ class Module {
   void close();
   bool closed() const { return !library_; }
   int device() const { return device_; }
+  unsigned mode() const { return mode_; }
   const std::string& requirements() const { return library_->requirements(); }
   int live_executions() const { return executions_; }
 
@@ -81,7 +82,9 @@ class Module {
 
 class Execution {
  public:
-  Execution(std::shared_ptr<Module> module, std::vector<void*> bindings, void* ready_stream);
+  // workspace / workspace_bytes / workers: only for persistent (mode 2) modules
+  Execution(std::shared_ptr<Module> module, std::vector<void*> bindings, void* ready_stream,
+            void* workspace = nullptr, size_t workspace_bytes = 0, unsigned workers = 1);
   ~Execution();
   void run(void* stream);
   void wait(double timeout_seconds);  // negative = no limit
@@ -97,6 +100,9 @@ class Execution {
   bool pending() const;
   std::shared_ptr<Module> module_;
   std::vector<void*> bindings_;
+  void* workspace_ = nullptr;
+  size_t workspace_bytes_ = 0;
+  unsigned workers_ = 1;
   CUevent_st* ready_ = nullptr;
   CUevent_st* tail_ = nullptr;
   CUstream_st* last_stream_ = nullptr;

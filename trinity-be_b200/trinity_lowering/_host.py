@@ -64,6 +64,8 @@ _SIGNATURES = {
     "th_module_close": (I, [P]),
     "th_module_live_executions": (I, [P]),
     "th_execution_create": (P, [P, ctypes.POINTER(P), ctypes.c_size_t, P]),
+    "th_execution_create_persistent": (P, [P, ctypes.POINTER(P), ctypes.c_size_t, P, ctypes.c_size_t,
+                                           ctypes.c_uint, P]),
     "th_execution_free": (None, [P]),
     "th_execution_run": (I, [P, P]),
     "th_execution_wait": (I, [P, ctypes.c_double]),

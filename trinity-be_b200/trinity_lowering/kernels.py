@@ -31,6 +31,7 @@ EXPORTS = (
     "trinity_sm100_mla_decode_bf16_noalloc",
     "trinity_sm100_allreduce_flag_words",
     "trinity_sm100_allreduce_bf16",
+    "trinity_sm100_allgather_bf16",
     "trinity_sm100_gemm_allreduce_flag_words",
     "trinity_sm100_gemm_allreduce_bf16",
     "trinity_sm100_gemm_allreduce_stamps",
@@ -125,6 +126,9 @@ def library():
             lib.trinity_sm100_allreduce_flag_words.restype = ctypes.c_size_t
             lib.trinity_sm100_allreduce_bf16.argtypes = [
                 ctypes.POINTER(AllReduceArgs), ctypes.c_void_p]
+            lib.trinity_sm100_allgather_bf16.argtypes = [
+                ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
             lib.trinity_sm100_gemm_allreduce_flag_words.argtypes = [ctypes.c_int64, ctypes.c_int64, ctypes.c_int32]
             lib.trinity_sm100_gemm_allreduce_flag_words.restype = ctypes.c_size_t
             lib.trinity_sm100_gemm_allreduce_bf16.argtypes = [
@@ -371,6 +375,36 @@ def allreduce(peer_ptrs, flag_ptrs, rows, cols, rank, epoch, stream=None):
     args.flags = ctypes.cast(flags, ctypes.POINTER(ctypes.c_void_p))
     args.rows, args.cols, args.world, args.rank, args.epoch = rows, cols, world, rank, epoch
     _check(library().trinity_sm100_allreduce_bf16(ctypes.byref(args), _stream(stream)))
+
+
+PEER_TABLE_BYTES = 1024
+PEER_BUFFERS = 4
+
+
+def peer_table(world, rank, workspace_ptrs, buffer_ptrs):
+    """The bytes of a ``trinity_sm100_peer_table`` (see the C header): ``workspace_ptrs[r]`` is
+    rank r's workspace as mapped into this process, ``buffer_ptrs[i][r]`` rank r's copy of the
+    i-th symmetric plan buffer."""
+    import struct
+    if len(buffer_ptrs) > PEER_BUFFERS or world > 8:
+        raise ValueError("at most %d symmetric buffers and 8 ranks" % PEER_BUFFERS)
+    words = struct.pack("<iiIIIIII", world, rank, 0, 0, 0, 0, 0, 0)
+    words += struct.pack("<8Q", *(list(workspace_ptrs) + [0] * (8 - world)))
+    for i in range(PEER_BUFFERS):
+        ptrs = list(buffer_ptrs[i]) if i < len(buffer_ptrs) else []
+        words += struct.pack("<8Q", *(ptrs + [0] * (8 - len(ptrs))))
+    words += bytes(64 * 4)
+    return words + bytes(PEER_TABLE_BYTES - len(words))
+
+
+def allgather(workspace_ptr, source, out, rows, cols, axis, world, stream=None):
+    """out = rank-major all-gather of the [rows, cols] BF16 shards held in symmetric buffer
+    ``source`` of the peer table at ``workspace_ptr`` (see ``trinity_sm100_allgather_bf16``)."""
+    _require(out, torch.bfloat16, "out")
+    with torch.cuda.device(out.device):
+        _check(library().trinity_sm100_allgather_bf16(ctypes.c_void_p(workspace_ptr), source, out.data_ptr(),
+                                                      rows, cols, axis, world, _stream(stream)))
+    return out
 
 
 def gemm_allreduce_stamps():

@@ -37,6 +37,27 @@ def all_reduce(source, source_shape, source_index, destination, destination_shap
             f"{view(destination, destination_shape)} {destination_index})")
 
 
+def all_gather(source, source_shape, source_index, destination, destination_shape, destination_index, axis):
+    return (f"(all_gather {view(source, source_shape)} {source_index} "
+            f"{view(destination, destination_shape)} {destination_index} {axis})")
+
+
+def gather(axis=0, world_size=2, rows=128, cols=128, target="sm100"):
+    """Rank-major all-gather of a BF16 [rows, cols] shard along `axis` with a source tile loop, in
+    the form of the reference's example (python/examples/plans.py:61-73 there)."""
+    shapes = [[rows, cols], [rows, cols]]
+    shapes[1][axis] *= world_size
+    b = PhysicalPlanBuilder(world_size, target)
+    x, y = [b.add_value("bf16", shape, "external") for shape in shapes]
+    b.bind_input("X", x)
+    access = index("(tile row 64)", "(tile col 64)")
+    body = all_gather(x, shapes[0], access, y, shapes[1], access, axis)
+    op = b.add_operation([x], [y], expression=body)
+    col = b.add_loop("parallel", "col", 0, cols, 64, [op])
+    row = b.add_loop("parallel", "row", 0, rows, 64, [col])
+    return b.build([row], "Y", y)
+
+
 # ---------------------------------------------------------------- GEMM + epilogue
 def gemm_bias(m, n, k, activation=None, bias="col", out_dtype="bf16", world_size=1, target="sm100"):
     """out = act(A[m,k] @ W[k,n] + bias): FP32 register accumulator, one rounding at the store.

@@ -88,7 +88,7 @@ def tensor_check(tensor, b, device, world=None):
     behind = tensor.untyped_storage().nbytes() - tensor.storage_offset() * tensor.element_size()
     if behind < b.bytes or tensor.data_ptr() % b.alignment != 0:
         raise ValueError(f"binding {b.value}: alignment/storage mismatch")
-    if world is None and b.symmetric:
+    if b.symmetric and (world is None or world.symmetric_buffer_of(tensor) is None):
         raise ValueError(f"binding {b.value} requires this world's symmetric allocation")
 
 
@@ -143,11 +143,12 @@ def outside_capture(device):
 
 
 class LoadedModule:
-    def __init__(self, handle, data, req, device, fingerprint):
+    def __init__(self, handle, data, req, device, fingerprint, world=None):
         self._handle, self._requirements, self._device = handle, req, device
         self._manifest, self._fingerprint = freeze(data), fingerprint
         self._closed = False
         self._lock = threading.RLock()
+        self._world = world
 
     def __del__(self):
         handle, self._handle = getattr(self, "_handle", None), None
@@ -160,7 +161,7 @@ class LoadedModule:
     requirements = property(lambda self: self._requirements)
     manifest = property(lambda self: self._manifest)
     device = property(lambda self: self._device)
-    world = property(lambda self: None)
+    world = property(lambda self: self._world)
     fingerprint = property(lambda self: self._fingerprint)
 
     def _open(self):
@@ -169,6 +170,9 @@ class LoadedModule:
 
     def _allocate(self, b):
         import torch
+        if b.symmetric:
+            # every rank's copy is mapped into every process (a collective step of the world)
+            return self._world.allocate(b.shape, getattr(torch, _TORCH_DTYPE[b.dtype])).tensor
         # Over-allocated byte storage supports alignments stronger than the allocator's.
         owner = torch.empty(b.bytes + b.alignment - 1, dtype=torch.uint8, device=self.device)
         offset = (-owner.data_ptr()) % b.alignment
@@ -178,7 +182,7 @@ class LoadedModule:
     def _bindings(self, inputs, out, allow_missing=False):
         self._open()
         outside_capture(self.device)
-        return resolve_bindings(self.requirements, inputs, out, self.device, None, allow_missing)
+        return resolve_bindings(self.requirements, inputs, out, self.device, self._world, allow_missing)
 
     def allocate_io(self, inputs=None):
         with self._lock:
@@ -209,11 +213,39 @@ class LoadedModule:
             tensors = [bound[b.value] for b in self.requirements.buffers]
             pointers = (ctypes.c_void_p * max(1, len(tensors)))(*[t.data_ptr() for t in tensors])
             stream = torch.cuda.current_stream(self.device)
-            handle = h.check_ptr(lib.th_execution_create(self._handle, pointers, len(tensors),
-                                                         ctypes.c_void_p(stream.cuda_stream)))
+            workspace = None
+            if self._world is None:
+                handle = h.check_ptr(lib.th_execution_create(self._handle, pointers, len(tensors),
+                                                             ctypes.c_void_p(stream.cuda_stream)))
+            else:
+                workspace = self._peer_workspace(tensors)
+                handle = h.check_ptr(lib.th_execution_create_persistent(
+                    self._handle, pointers, len(tensors), ctypes.c_void_p(workspace.tensor.data_ptr()),
+                    workspace.tensor.numel(), chosen, ctypes.c_void_p(stream.cuda_stream)))
             output = next(bound[b.value] for b in self.requirements.buffers if b.output_name is not None)
             named = {n: bound[b.value] for b in self.requirements.buffers for n in b.input_names}
-            return PreparedExecution(self, handle, named, tensors, output)
+            return PreparedExecution(self, handle, named, tensors, output, workspace)
+
+    def _peer_workspace(self, tensors):
+        """The execution's workspace in symmetric memory, its first bytes the peer table the
+        kernels read: every rank's workspace and every rank's copy of the symmetric plan buffers,
+        as mapped into this process.  All ranks finish this step before any of them launches."""
+        import torch
+        from . import kernels
+        world, req = self._world, self.requirements
+        size = max(req.workspace_bytes, kernels.PEER_TABLE_BYTES)
+        workspace = world.allocate((size,), torch.uint8)
+        peers = []
+        for b, tensor in zip(req.buffers, tensors):
+            if b.symmetric:
+                owner = world.symmetric_buffer_of(tensor)
+                peers.append(owner.peer_ptrs)
+        table = kernels.peer_table(world.size, world.rank, workspace.peer_ptrs, peers)
+        workspace.tensor.zero_()
+        workspace.tensor[:len(table)].copy_(torch.frombuffer(bytearray(table), dtype=torch.uint8))
+        torch.cuda.synchronize(self.device)
+        world.barrier()
+        return workspace
 
     def close(self, wait=True):
         with self._lock:
@@ -227,8 +259,9 @@ class PreparedExecution:
     """A module bound to concrete tensors.  The tensors are kept alive here; their addresses and
     storages must not change while the execution is open."""
 
-    def __init__(self, module, handle, inputs, tensors, output):
+    def __init__(self, module, handle, inputs, tensors, output, workspace=None):
         self._module, self._handle = module, handle
+        self._workspace = workspace      # persistent modules: the symmetric workspace with the peer table
         self._inputs = MappingProxyType(inputs)
         self._tensors, self._output = tensors, output
         self._snapshot = [(t.data_ptr(), t.untyped_storage().data_ptr()) for t in tensors]
@@ -246,7 +279,7 @@ class PreparedExecution:
     module = property(lambda self: self._module)
     inputs = property(lambda self: self._inputs)
     output = property(lambda self: self._output)
-    world = property(lambda self: None)
+    world = property(lambda self: self._module.world)
 
     def _validate(self):
         if self._closed:
@@ -282,20 +315,22 @@ class PreparedExecution:
 
 def load(artifact_or_directory, device, world=None):
     """Loads an artifact (or a persisted artifact directory) onto ``device``."""
-    if world is not None:
-        raise NotImplementedError("Persistent (multi-rank) artifacts are not loaded by this runtime")
     artifact = artifact_or_directory
     directory = artifact.directory if isinstance(artifact, CudaArtifact) else Path(artifact)
     data, req = manifest((directory / "manifest.json").read_text())
     d = device_of(device, req.target)
     outside_capture(d)
-    if req.nvshmem:
-        raise ValueError("artifact requires a matching world")
+    if req.nvshmem != (world is not None):
+        raise ValueError("artifact requires a matching world" if req.nvshmem else
+                         "a streamed artifact is loaded without a world")
+    if world is not None and (world.size != req.world_size or world.device != d):
+        raise ValueError("the world's size and device must be the artifact's")
     fingerprint = hashlib.sha256((directory / "source.cu").read_bytes()
                                  + json.dumps(data["requirements"], sort_keys=True).encode()).hexdigest()
     lib = h.library()
-    handle = h.check_ptr(lib.th_module_load(str(directory / "program.so").encode(), d.index, 1))
+    handle = h.check_ptr(lib.th_module_load(str(directory / "program.so").encode(), d.index,
+                                            2 if world is not None else 1))
     if json.loads(h.text(lib.th_module_requirements_json(handle))) != data["requirements"]:
         lib.th_module_free(handle)
         raise ValueError("artifact manifest differs from the loaded module")
-    return LoadedModule(handle, data, req, d, fingerprint)
+    return LoadedModule(handle, data, req, d, fingerprint, world)

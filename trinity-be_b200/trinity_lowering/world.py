@@ -164,6 +164,32 @@ class World:
         self._buffers.append(buffer)
         return buffer
 
+    def symmetric_buffer_of(self, tensor):
+        """The symmetric allocation of this world that `tensor` is (same address and size), or None."""
+        for buffer in self._buffers:
+            if buffer.tensor.data_ptr() == tensor.data_ptr() and buffer.tensor.numel() * buffer.tensor.element_size() >= \
+                    tensor.numel() * tensor.element_size():
+                return buffer
+        return None
+
+    def record_stream(self, tensor):
+        """Kept for the reference's surface (python/src/trinity_lowering/world.py): symmetric
+        allocations of this world are owned by the world until `collect()` or `close()`, so there
+        is no allocator stream to record."""
+        return None
+
+    def collect(self):
+        """Releases symmetric allocations that nothing outside the world refers to any more.  A
+        collective step: every rank calls it at the same point."""
+        import sys
+
+        def sweep():
+            keep = [b for b in self._buffers if sys.getrefcount(b) > 3 or sys.getrefcount(b.tensor) > 2]
+            dropped = len(self._buffers) - len(keep)
+            self._buffers[:] = keep
+            return dropped
+        return self._stage("collect", sweep)
+
     def all_reduce(self, buffer, stream=None):
         """In-place sum all-reduce of a symmetric BF16 matrix through peer memory."""
         from . import kernels
