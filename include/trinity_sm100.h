@@ -375,6 +375,21 @@ TRINITY_SM100_API int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm
                                       const trinity_sm100_allreduce* reduce, void* stream);
 
 /*
+ * The same fused GEMM for a persistent artifact's launch function, which has no host-side peer
+ * information: `workspace` is the artifact's workspace (symmetric memory) whose first bytes are a
+ * filled trinity_sm100_peer_table and whose flag pad follows the table; `output_buffer` says which
+ * symmetric buffer of the table is the [m,n] output (gemm->out must be this rank's copy).  The
+ * call number is the table's own counter, advanced by the kernel, so a captured launch replays
+ * unchanged.  The first call for a workspace reads its table from the device (one synchronous
+ * copy): make it outside any stream capture.
+ * workspace bytes needed: trinity_sm100_gemm_allreduce_workspace_bytes(m, n, world).
+ */
+TRINITY_SM100_API size_t trinity_sm100_gemm_allreduce_workspace_bytes(int64_t m, int64_t n, int32_t world);
+TRINITY_SM100_API int trinity_sm100_gemm_allreduce_workspace_bf16(const trinity_sm100_gemm* gemm, void* workspace,
+                                                                  size_t workspace_bytes, int32_t output_buffer,
+                                                                  void* stream);
+
+/*
  * Diagnostic: five milestones of thread block 0 of the most recent fused launch on the current
  * device, in nanoseconds of the device's global timer: kernel start, last MMA committed, last
  * partial tile handed over, last owned rows reduced, every rank retired.  Synchronises the device.

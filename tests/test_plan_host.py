@@ -265,6 +265,14 @@ def test_all_gather_plans_become_persistent_artifacts():
             "trinity_abi", "trinity_launch", "trinity_prepare", "trinity_release", "trinity_status"]
     finally:
         artifact.close()
+    # the down projection of a tensor-parallel MLP: one launch, the sum across GPUs in the GEMM's epilogue
+    fused = tl.emit(plans.row_parallel_gemm(512, 1024, 1024, 2))
+    assert fused.launch_count == 1 and "trinity_sm100_gemm_allreduce_workspace_bf16(&g, workspace, " in fused.code
+    needs = json.loads(fused._native.requirements_json())
+    assert [b["symmetric"] for b in needs["buffers"]] == [False, False, True]      # A, W local; Y symmetric
+    assert needs["workspace_bytes"] == 1024 + 4 * (64 + 16 * 2 + 16)                 # peer table + flag pad
+    found = tl.kernel_candidates(plans.row_parallel_gemm(512, 1024, 1024, 2))
+    assert all([c["provider"] for c in entry["candidates"]] == ["sm100.gemm_all_reduce"] for entry in found.values())
     # a shard whose rows are not multiples of 16 bytes, or a destination of the wrong extent, is declined
     with pytest.raises(NotImplementedError, match="all_gather"):
         tl.emit(plans.gather(axis=0, world_size=2, rows=64, cols=68))

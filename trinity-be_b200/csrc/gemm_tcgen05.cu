@@ -24,6 +24,8 @@
 //
 // Algorithmic traffic per launch: (M*K + K*N [+K*N]) * 2 + bias + M*N*out_bytes.
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 #include "host_common.h"
 #include "sm100_ptx.cuh"
@@ -52,6 +54,8 @@ struct GemmPeers {
   int world, rank;
   uint32_t epoch;
   int signal_from_epilogue;        // 1: the epilogue warps fence and flag (older scheme, kept for comparison)
+  uint32_t* epoch_counter;         // persistent artifacts: the call number lives on the device (peer table)
+                                   // and the kernel advances it; then `epoch` above is ignored
   long long ld_vectors;            // output row pitch in 16-byte vectors
 };
 
@@ -216,7 +220,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_b2,
                          const __grid_constant__ CUtensorMap map_out, const GemmParams p,
-                         const GemmPeers peers) {
+                         const GemmPeers launch_peers) {
+  // With a device-side call counter every thread reads it before anything of this launch can
+  // have advanced it (the last thread block to retire does that).
+  GemmPeers peers = launch_peers;
+  if (kFused && peers.epoch_counter) peers.epoch = *reinterpret_cast<volatile uint32_t*>(peers.epoch_counter) + 1u;
   constexpr int kOutN = kGated ? kBN / 2 : kBN;      // output columns per tile
   constexpr int kStage = stage_bytes<kBN, kPair>();
   constexpr int kChunksB = (kPair ? kBN / 2 : kBN) / 64;   // 64-column TMA boxes this CTA loads per stage
@@ -603,6 +611,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const unsigned prev = atomicAdd(mine + kGemmMaxWorld, 1u);
         if (prev == gridDim.x - 1) {
           mine[kGemmMaxWorld] = 0;
+          if (peers.epoch_counter) *reinterpret_cast<volatile uint32_t*>(peers.epoch_counter) = peers.epoch;
           __threadfence_system();
           for (int r = 0; r < peers.world; ++r)
             flag_store(peers.flags[r] + static_cast<long long>(p.flag_tiles) * peers.world + peers.rank, peers.epoch);
@@ -830,6 +839,8 @@ int check_gemm_arguments(const trinity_sm100_gemm& g) {
 }  // namespace
 
 namespace {
+// Set by the workspace entry point around its call of the host-epoch entry point (same thread).
+thread_local uint32_t* g_epoch_counter_for_next_launch = nullptr;
 // TRINITY_SM100_GEMM_PAIRS=0 keeps every GEMM on single CTAs; =1 (default) lets large plain and
 // all-reduce-fused problems run on CTA pairs; =2 also the gated form, which measures slower on
 // pairs than on single CTAs (B200, 16384 x 8192 x 28672) and therefore stays on single CTAs by
@@ -951,6 +962,70 @@ extern "C" int trinity_sm100_gemm_allreduce_stamps(uint64_t* stamps) {
   return 0;
 }
 
+namespace {
+// Peer tables of persistent workspaces, read from the device once per workspace and kept: the
+// table is written once, before the first launch, and only its counters change afterwards.
+struct CachedTable {
+  void* workspace;
+  trinity_sm100_peer_table table;
+};
+int cached_peer_table(void* workspace, trinity_sm100_peer_table* out) {
+  static std::mutex mutex;
+  static std::vector<CachedTable> known;
+  std::lock_guard<std::mutex> lock(mutex);
+  for (auto& entry : known)
+    if (entry.workspace == workspace) {
+      *out = entry.table;
+      return 0;
+    }
+  CachedTable entry;
+  entry.workspace = workspace;
+  cudaError_t e = cudaMemcpy(&entry.table, workspace, sizeof(entry.table), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess)
+    return fail(TRINITY_SM100_E_CUDA, "reading the workspace's peer table: %s", cudaGetErrorString(e));
+  known.push_back(entry);
+  *out = entry.table;
+  return 0;
+}
+}  // namespace
+
+extern "C" size_t trinity_sm100_gemm_allreduce_workspace_bytes(int64_t m, int64_t n, int32_t world) {
+  return TRINITY_SM100_PEER_TABLE_BYTES + 4 * trinity_sm100_gemm_allreduce_flag_words(m, n, world);
+}
+
+extern "C" int trinity_sm100_gemm_allreduce_workspace_bf16(const trinity_sm100_gemm* args, void* workspace,
+                                                           size_t workspace_bytes, int32_t output_buffer,
+                                                           void* stream_handle) {
+  if (!args || !workspace) return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce (workspace): null argument");
+  if (output_buffer < 0 || output_buffer >= TRINITY_SM100_PEER_BUFFERS)
+    return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce (workspace): symmetric buffer index %d", output_buffer);
+  trinity_sm100_peer_table table;
+  if (int rc = cached_peer_table(workspace, &table)) return rc;
+  if (table.world < 1 || table.world > kGemmMaxWorld || table.rank < 0 || table.rank >= table.world)
+    return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce (workspace): the peer table is not filled");
+  if (workspace_bytes < trinity_sm100_gemm_allreduce_workspace_bytes(args->m, args->n, table.world))
+    return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce (workspace): workspace of %zu bytes is too small", workspace_bytes);
+  void* peers[kGemmMaxWorld];
+  void* flags[kGemmMaxWorld];
+  for (int r = 0; r < table.world; ++r) {
+    peers[r] = reinterpret_cast<void*>(table.buffers[output_buffer][r]);
+    // the flag pad follows the table in every rank's workspace
+    flags[r] = reinterpret_cast<uint8_t*>(table.workspace[r]) + TRINITY_SM100_PEER_TABLE_BYTES;
+  }
+  trinity_sm100_allreduce reduce = {};
+  reduce.peers = peers;
+  reduce.flags = flags;
+  reduce.rows = args->m;
+  reduce.cols = args->n;
+  reduce.world = table.world;
+  reduce.rank = table.rank;
+  reduce.epoch = 1;   // replaced on the device by the table's own counter
+  g_epoch_counter_for_next_launch = &static_cast<trinity_sm100_peer_table*>(workspace)->epoch;
+  const int rc = trinity_sm100_gemm_allreduce_bf16(args, &reduce, stream_handle);
+  g_epoch_counter_for_next_launch = nullptr;
+  return rc;
+}
+
 extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
                                                  const trinity_sm100_allreduce* reduce, void* stream_handle) {
   if (!args || !reduce) return fail(TRINITY_SM100_E_INVALID, "gemm_allreduce: null argument block");
@@ -986,6 +1061,7 @@ extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
   peers.world = r.world;
   peers.rank = r.rank;
   peers.epoch = r.epoch;
+  peers.epoch_counter = g_epoch_counter_for_next_launch;
   {
     const char* v = getenv("TRINITY_SM100_FUSED_SIGNAL");
     peers.signal_from_epilogue = v && v[0] == 'e' ? 1 : 0;

@@ -864,6 +864,59 @@ struct Emitter {
     return true;
   }
 
+  // ------------------------------------------------------------------ row-parallel GEMM + all-reduce
+  // ploop m { ploop n { sloop k { acc += A[m,k] @ B[k,n] } ; (all_reduce acc[m,n] Y[m,n]) } } with
+  // a register accumulator: every rank multiplies its own K shard and the partial products are
+  // summed across the GPUs inside the GEMM's epilogue.  Y becomes a symmetric buffer, the flag pad
+  // of the reduction lives in the workspace behind the peer table.
+  size_t workspace_bytes = 0;
+  bool try_gemm_all_reduce(const Statement& top) {
+    std::vector<LoopInfo> parallel;
+    const std::vector<Statement>* body = strip_parallel(top, parallel);
+    if (!body || parallel.empty() || body->size() != 2 || !(*body)[0].is_loop || (*body)[1].is_loop) return false;
+    const Operation& reduce = plan.operations[(*body)[1].operation];
+    if (reduce.expression->kind != Expression::AllReduce) return false;
+    auto decline = [&](const std::string& why) { rejections.push_back("sm100.gemm_all_reduce: " + why); return false; };
+    Accumulator a;
+    std::string why;
+    if (!match_accumulate((*body)[0], parallel, a, why)) return decline(why);
+    const Expression& e = *reduce.expression;
+    if (!(e.source == a.acc_access)) return decline("the reduced value must be the accumulator at its own coordinates");
+    if (!(e.access.indices == a.acc_access.indices) || !e.access.view_shape.empty())
+      return decline("the destination must be written at the accumulator's coordinates");
+    const Value &vacc = value(a.acc), &vy = value(e.access.value);
+    if (vacc.storage != Storage::Register) return decline("the accumulator must be a register value");
+    if (vy.dtype != DType::Bf16 || vy.shape != vacc.shape) return decline("the destination must be a bf16 matrix of the accumulator's shape");
+    if (vy.storage != Storage::External) return decline("the destination must be an external (bound) value");
+    buffers[slot(e.access.value)].symmetric = true;
+    need_alignment(a.a, 16);
+    need_alignment(a.b, 16);
+    need_alignment(e.access.value, 16);
+    int symmetric_index = 0;
+    for (int b = 0; b < slot(e.access.value); ++b)
+      if (buffers[b].symmetric) ++symmetric_index;
+    // trinity_sm100_gemm_allreduce_workspace_bytes(m, n, world): table + flag pad
+    const size_t tiles = (size_t((a.m + 127) / 128) + 1) / 2 * 2 * size_t((a.n + 255) / 256);
+    workspace_bytes = std::max(workspace_bytes, size_t(1024) + 4 * (64 + tiles * size_t(plan.world_size) + 16));
+    std::ostringstream c;
+    c << "  {\n    trinity_sm100_gemm g = {};\n";
+    c << "    g.a = " << slot_ptr(slot(a.a)) << ";\n    g.b = " << slot_ptr(slot(a.b)) << ";\n";
+    c << "    g.out = " << slot_ptr(slot(e.access.value)) << ";\n";
+    c << "    g.m = " << a.m << "; g.n = " << a.n << "; g.k = " << a.k << ";\n";
+    c << "    g.lda = " << a.k << "; g.ldb = " << a.n << "; g.ldo = " << a.n << ";\n";
+    c << "    g.activation = 0;\n    g.out_dtype = TRINITY_SM100_BF16;\n";
+    c << "    rc = trinity_sm100_gemm_allreduce_workspace_bf16(&g, workspace, launch_args->workspace_bytes, " << symmetric_index
+      << ", stream);\n  }\n";
+    Launch l;
+    l.kernel = "trinity_sm100_gemm_allreduce_workspace_bf16";
+    l.code = c.str();
+    l.operations = {a.op, (*body)[1].operation};
+    l.shared_memory_bytes = 230656;
+    l.block_threads = 320;
+    launches.push_back(std::move(l));
+    return true;
+  }
+
   void run() {
     check_plan();
     build_buffers();
@@ -873,10 +926,10 @@ struct Emitter {
       // src/emit/native/mod.rs:161-165).
       for (auto& s : plan.statements) {
         rejections.clear();
-        if (try_all_gather(s)) continue;
+        if (try_all_gather(s) || try_gemm_all_reduce(s)) continue;
         std::string reasons;
         for (auto& r : rejections) reasons += (reasons.empty() ? "" : "; ") + r;
-        unsupported("UnsupportedExecution: Persistent emission covers all_gather plans only" +
+        unsupported("UnsupportedExecution: Persistent emission covers all_gather and GEMM + all_reduce plans only" +
                     (reasons.empty() ? std::string() : " (" + reasons + ")"));
       }
       return;
@@ -917,18 +970,18 @@ struct Emitter {
         {"sm100.gemm", &Emitter::try_gemm},         {"sm100.rmsnorm", &Emitter::try_rmsnorm},
         {"sm100.softmax", &Emitter::try_softmax},   {"sm100.mla_decode", &Emitter::try_mla},
         {"sm100.row_reduce", &Emitter::try_row_reduce}, {"sm100.pointwise", &Emitter::try_pointwise},
-        {"sm100.all_gather", &Emitter::try_all_gather}};
+        {"sm100.all_gather", &Emitter::try_all_gather}, {"sm100.gemm_all_reduce", &Emitter::try_gemm_all_reduce}};
     std::vector<Offer> result;
     for (auto& [name, recogniser] : recognisers) {
       Offer offer;
       offer.provider = name;
       const size_t before = launches.size();
       rejections.clear();
-      const bool collective = recogniser == &Emitter::try_all_gather;
+      const bool collective = recogniser == &Emitter::try_all_gather || recogniser == &Emitter::try_gemm_all_reduce;
       if (collective != (plan.world_size != 1)) {
-        // single-GPU kernels serve streamed plans, the collective serves multi-GPU plans
-        offer.reason = collective ? "all_gather needs a multi-GPU plan"
-                                  : "UnsupportedExecution: Persistent emission covers all_gather plans only";
+        // single-GPU kernels serve streamed plans, the collectives serve multi-GPU plans
+        offer.reason = collective ? "collectives need a multi-GPU plan"
+                                  : "UnsupportedExecution: Persistent emission covers all_gather and GEMM + all_reduce plans only";
         result.push_back(std::move(offer));
         continue;
       }
@@ -960,7 +1013,7 @@ std::string read_file(const std::string& path) {
 }
 
 std::string requirements_json(const PhysicalPlan& plan, const std::vector<BufferRequirement>& buffers,
-                              const std::vector<Launch>& launches) {
+                              const std::vector<Launch>& launches, size_t workspace_bytes = 0) {
   std::ostringstream out;
   out << "{\"target\":\"" << target_name(Target::Sm100) << "\",\"world_size\":" << plan.world_size << ",\"buffers\":[";
   for (size_t i = 0; i < buffers.size(); ++i) {
@@ -988,7 +1041,7 @@ std::string requirements_json(const PhysicalPlan& plan, const std::vector<Buffer
   // the artifact needs a World (here: peer-mapped symmetric memory, not NVSHMEM) and
   // `cooperative_launch` that the ranks' grids must be running at the same time.
   const bool multi = plan.world_size > 1;
-  out << "],\"workspace_bytes\":" << (multi ? 1024 : 0) << ",\"workspace_alignment\":" << (multi ? 256 : 1)
+  out << "],\"workspace_bytes\":" << (multi ? std::max<size_t>(1024, workspace_bytes) : 0) << ",\"workspace_alignment\":" << (multi ? 256 : 1)
       << ",\"workspace_symmetric\":" << (multi ? "true" : "false") << ",\"cooperative_launch\":" << (multi ? "true" : "false")
       << ",\"shared_memory_bytes\":" << smem << ",\"block_threads\":" << threads << ",\"nvshmem\":"
       << (multi ? "true" : "false") << ",\"nvls\":false}";
@@ -1052,7 +1105,7 @@ CudaSource emit(const PhysicalPlan& plan) {
   e.run();
   CudaSource source;
   source.persistent = plan.world_size > 1;
-  source.requirements_json = requirements_json(plan, e.buffers, e.launches);
+  source.requirements_json = requirements_json(plan, e.buffers, e.launches, e.workspace_bytes);
   source.code = render(source.requirements_json, e.buffers, e.launches, source.persistent);
   source.launches = std::move(e.launches);
   source.buffers = std::move(e.buffers);

@@ -35,6 +35,8 @@ EXPORTS = (
     "trinity_sm100_gemm_allreduce_flag_words",
     "trinity_sm100_gemm_allreduce_bf16",
     "trinity_sm100_gemm_allreduce_stamps",
+    "trinity_sm100_gemm_allreduce_workspace_bytes",
+    "trinity_sm100_gemm_allreduce_workspace_bf16",
     "trinity_sm100_pointwise",
     "trinity_sm100_row_reduce_sum",
     "trinity_sm100_prepare_device",

@@ -58,6 +58,29 @@ def gather(axis=0, world_size=2, rows=128, cols=128, target="sm100"):
     return b.build([row], "Y", y)
 
 
+def row_parallel_gemm(m, n, k_shard, world_size, target="sm100"):
+    """Y (on every GPU) = sum over GPUs of A_r[m, k_shard] @ B_r[k_shard, n]: every rank multiplies
+    its own K shard into an FP32 register accumulator and the partial products are summed across
+    the GPUs (`all_reduce` of the accumulator into Y), which the provider does inside the GEMM's
+    epilogue.  The down projection of a tensor-parallel MLP has this form."""
+    b = PhysicalPlanBuilder(world_size, target)
+    a = b.add_value("bf16", [m, k_shard], "external")
+    w = b.add_value("bf16", [k_shard, n], "external")
+    acc = b.add_value("fp32", [m, n], "register")
+    y = b.add_value("bf16", [m, n], "external")
+    b.bind_input("A", a)
+    b.bind_input("W", w)
+    tile_m, tile_n, tile_k = ("clipped_tile m 128", "clipped_tile n 128", "clipped_tile k 64")
+    ai, bi, ci = index(f"({tile_m})", f"({tile_k})"), index(f"({tile_k})", f"({tile_n})"), index(f"({tile_m})", f"({tile_n})")
+    rhs = f"(+ {load(acc, [m, n], ci)} (@ {load(a, [m, k_shard], ai)} {load(w, [k_shard, n], bi)}))"
+    mma = b.add_operation([a, w], [acc], expression=store(acc, [m, n], rhs, ci))
+    reduction = b.add_loop("sequential", "k", 0, _ceil(k_shard, 64), 64, [mma])
+    total = b.add_operation([acc], [y], expression=all_reduce(acc, [m, n], ci, y, [m, n], ci))
+    cols = b.add_loop("parallel", "n", 0, _ceil(n, 128), 128, [reduction, total])
+    rows = b.add_loop("parallel", "m", 0, _ceil(m, 128), 128, [cols])
+    return b.build([rows], "Y", y)
+
+
 # ---------------------------------------------------------------- GEMM + epilogue
 def gemm_bias(m, n, k, activation=None, bias="col", out_dtype="bf16", world_size=1, target="sm100"):
     """out = act(A[m,k] @ W[k,n] + bias): FP32 register accumulator, one rounding at the store.

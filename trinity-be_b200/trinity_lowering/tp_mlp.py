@@ -8,8 +8,10 @@ of W_down ([d_ff / n, d_model]); X is replicated.  Per step a rank launches
 all on one stream, with no host synchronisation in between.  With ``fused=True`` (the default)
 steps 2 and 3 are one kernel: the down GEMM's epilogue warps exchange and add the partial tiles
 over NVLink while the tensor cores work on the following tiles.
-The plan-level spelling of the same computation is `plans.gated_gemm` followed by a GEMM and
-`(all_reduce ...)`; this class is the launch sequence the provider emits for it.
+The plan-level spelling of the two GEMMs is `plans.gated_gemm` (a streamed, single-GPU plan per
+rank) and `plans.row_parallel_gemm` (a multi-GPU plan: `all_reduce` of the accumulator), which the
+provider emits as a persistent artifact whose one launch is the same fused kernel this class calls
+directly; this class is the hand-written launch sequence over the kernel library.
 """
 import torch
 
