@@ -55,5 +55,7 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
     assert k.device_status() == 0
     with pytest.raises(k.KernelError):
         k.allreduce([mine.data_ptr(), theirs.data_ptr()], [p.data_ptr() for p in pads], 64, 64, rank=0, epoch=0)
-    execution.close()
+    with pytest.raises(tl.RuntimeFailure):   # the execution whose completion failed closes and says so
+        execution.close()
+    assert execution._closed
     module.close()
