@@ -90,3 +90,39 @@ int main() {
                        check=True)
         out = subprocess.run([str(Path(tmp) / "layout")], capture_output=True, text=True, check=True).stdout
     assert out == "1 8 24 4 24 8 3 112|0 8 16 |0 4 8 12 16 20 |64 9 0 8 16 24 32 40 44 48 56 "
+
+
+def test_peer_table_bytes_match_the_c_struct():
+    """The runtime fills a persistent artifact's peer table from Python; its byte layout must be
+    the C struct's (include/trinity_sm100.h), which the kernels read on the device."""
+    import struct
+    import tempfile
+    from trinity_lowering import kernels
+    code = r'''
+#include <cstddef>
+#include <cstdio>
+#include "trinity_sm100.h"
+int main() {
+  printf("%zu %zu %zu %zu %zu %zu %zu %zu %d %d", sizeof(trinity_sm100_peer_table),
+         offsetof(trinity_sm100_peer_table, rank), offsetof(trinity_sm100_peer_table, epoch),
+         offsetof(trinity_sm100_peer_table, counter), offsetof(trinity_sm100_peer_table, failed),
+         offsetof(trinity_sm100_peer_table, workspace), offsetof(trinity_sm100_peer_table, buffers),
+         offsetof(trinity_sm100_peer_table, flags), TRINITY_SM100_PEER_BUFFERS, TRINITY_SM100_PEER_TABLE_BYTES);
+  return 0;
+}'''
+    with tempfile.TemporaryDirectory() as tmp:
+        src = Path(tmp) / "table.cpp"
+        src.write_text(code)
+        subprocess.run(["g++", "-std=c++17", "-I", str(ROOT / "include"), str(src), "-o", str(Path(tmp) / "table")],
+                       check=True)
+        out = subprocess.run([str(Path(tmp) / "table")], capture_output=True, text=True, check=True).stdout
+    size, rank, epoch, counter, failed, workspace, buffers, flags, slots, reserved = map(int, out.split())
+    assert (slots, reserved) == (kernels.PEER_BUFFERS, kernels.PEER_TABLE_BYTES) and size <= reserved
+    table = kernels.peer_table(4, 2, [0x1000, 0x2000, 0x3000, 0x4000], [[0x10, 0x20, 0x30, 0x40], [0x50, 0x60, 0x70, 0x80]])
+    assert len(table) == reserved
+    assert struct.unpack_from("<i", table, 0)[0] == 4 and struct.unpack_from("<i", table, rank)[0] == 2
+    assert struct.unpack_from("<III", table, epoch) == (0, 0, 0) and (counter, failed) == (epoch + 4, epoch + 8)
+    assert struct.unpack_from("<4Q", table, workspace) == (0x1000, 0x2000, 0x3000, 0x4000)
+    assert struct.unpack_from("<4Q", table, buffers) == (0x10, 0x20, 0x30, 0x40)
+    assert struct.unpack_from("<4Q", table, buffers + 64) == (0x50, 0x60, 0x70, 0x80)
+    assert not any(table[flags:])            # flags start at zero: a fresh pad reads as call number 0
