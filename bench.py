@@ -804,6 +804,9 @@ def main():
     w = make_workload(args.workload, device, world_obj, world, rank)
     use_graph = not (w.no_graph or args.no_graph)
     ms, launches, clocks = measure(w, args.steps, args.warmup, stream, device, use_graph, barrier, local_rank)
+    # milestones of the last device-timed fused launch (read before the end-to-end phase, whose
+    # launches wait for each rank's own copies and therefore start at different times)
+    stamps = k.gemm_allreduce_stamps() if distributed and args.workload == "tp_mlp" else None
     parity = w.check()
     if not (args.workload.startswith("tp_mlp") and distributed):
         parity = worst_parity(parity)       # the MLP's check already gathers over the ranks
@@ -847,7 +850,7 @@ def main():
         # milestones of the last fused down-projection launch on every rank (its first thread block),
         # microseconds after its start: last MMA committed, last partial tile handed over, last
         # owned rows reduced, all ranks retired
-        t = k.gemm_allreduce_stamps()
+        t = stamps
         mine = [round((v - t[0]) / 1e3, 1) for v in t[1:]]
         every = [None] * world
         dist.all_gather_object(every, mine)

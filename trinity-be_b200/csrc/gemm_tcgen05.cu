@@ -53,7 +53,6 @@ struct GemmPeers {
   uint32_t* flags[kGemmMaxWorld];  // flag pads: ready[tile][source rank], done[rank], counter
   int world, rank;
   uint32_t epoch;
-  int signal_from_epilogue;        // 1: the epilogue warps fence and flag (older scheme, kept for comparison)
   uint32_t* epoch_counter;         // persistent artifacts: the call number lives on the device (peer table)
                                    // and the kernel advances it; then `epoch` above is ignored
   long long ld_vectors;            // output row pitch in 16-byte vectors
@@ -559,15 +558,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         else mbar_arrive(tmem_empty_bar(acc));
       }
       if (kFused) {
-        if (peers.signal_from_epilogue) {
-          if (lane == 0) {
-            tma_store_wait_all();
-            __threadfence_system();
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (etid < peers.world)
-            flag_store(peers.flags[etid] + static_cast<long long>(tile) * peers.world + peers.rank, peers.epoch);
-        } else if (lane == 0) {
+        if (lane == 0) {
           // Once this warp's part of the partial tile has landed in memory the warp is free for
           // the next tile; telling the other GPUs (a system-scope release, which waits for
           // writes in flight) is left to the reducer warps, which wait for this tile anyway.
@@ -589,7 +580,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     for (int unit = first_unit; unit < num_units && ok; unit += unit_stride, ++local_tile) {
       int m_blk, n_blk, tile;
       locate_tile<kPair>(p, unit, rank, m_blk, n_blk, tile);
-      if (!peers.signal_from_epilogue && rtid < peers.world) {
+      if (rtid < peers.world) {
         // This rank's partial of the tile is complete in memory (the epilogue warps' stores have
         // landed) -> tell every rank's reducer warps, this CTA's own included.  The give-up case
         // is caught by the flag wait that follows: nobody will have flagged the tile.
@@ -1070,10 +1061,6 @@ extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
   peers.rank = r.rank;
   peers.epoch = r.epoch;
   peers.epoch_counter = g_epoch_counter_for_next_launch;
-  {
-    const char* v = getenv("TRINITY_SM100_FUSED_SIGNAL");
-    peers.signal_from_epilogue = v && v[0] == 'e' ? 1 : 0;
-  }
   peers.ld_vectors = g.ldo / 8;
   int sm_count = 0;
   if (int rc = require_sm100(&sm_count)) return rc;
