@@ -113,14 +113,59 @@ def test_streamed_config_1024_uniform():
 
 @pytest.mark.parametrize("m,n,k", [(16, 8192, 1024), (1, 4096, 2048), (100, 1000, 4096)])
 def test_decode_time_shapes(m, n, k):
-    """A few output rows against a large weight: the kernel streams the weight through
-    64-column tiles (one partly filled row tile, many column tiles)."""
+    """A few output rows against a large weight: the kernel streams the weight (one partly
+    filled row tile, many column tiles; up to 32 rows through the form that splits K)."""
     a, w, bias = wl.gemm_inputs(m, n, k, 77, "normal")
     out = run_gemm(a, w, bias, bias_mode=kernels.BIAS_COL_VECTOR)
     assert_close_bf16(out, wl.gemm_oracle(a, w, bias), max_ulp=1, max_abs=2e-2)
     out32 = run_gemm(a, w, None, out_dtype=torch.float32)
     exact = (a.double() @ w.double()).float()
     assert (out32 - exact).norm() / exact.norm() < 1e-5
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (16, 256, 512),      # one tile, two parts of four K blocks
+    (1, 2048, 1024),     # 16 K blocks: four parts of four
+    (16, 4096, 8192),    # eight parts (16 rows are handed over)
+    (17, 8192, 4096),    # 17..32 rows: four parts at most, 32 rows handed over
+    (32, 8200, 1000),    # ragged columns and a ragged last K block
+    (9, 1032, 4104),     # five tiles, the last 8 columns wide; K blocks not a multiple of the parts
+])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_few_rows_split_over_k_bit_exact(m, n, k, out_dtype):
+    """Up to 32 output rows with fewer 256-column tiles than half the SMs: the CTAs of a cluster
+    share a tile, each sums a part of K, and the first adds the parts in a fixed order.  Exact
+    operands, so the sum must not depend on how K was cut, and repeated launches must agree."""
+    a, b = wl.dyadic_gemm_inputs(m, n, k)
+    exact = (a.double() @ b.double()).float().to(out_dtype)
+    for _ in range(3):
+        out = run_gemm(a, b, out_dtype=out_dtype)
+        assert torch.equal(out, exact)
+
+
+def test_few_rows_split_over_k_epilogue_and_determinism():
+    """Bias, activation and row-vector bias run after the parts are added; two launches give the
+    same bits (the order of the additions is fixed, not the order of arrival)."""
+    a, w, bias = wl.gemm_inputs(16, 8192, 8192, 79, "normal")
+    first = run_gemm(a, w, bias, bias_mode=kernels.BIAS_COL_VECTOR, activation=kernels.ACT_RELU)
+    assert_close_bf16(first, wl.gemm_oracle(a, w, bias, "relu"), max_ulp=1, max_abs=2e-2)
+    for _ in range(3):
+        assert torch.equal(run_gemm(a, w, bias, bias_mode=kernels.BIAS_COL_VECTOR, activation=kernels.ACT_RELU), first)
+    rows = wl._normal((16,), 0.5, wl._gen(80))
+    out32 = run_gemm(a, w, rows, bias_mode=kernels.BIAS_ROW_VECTOR, out_dtype=torch.float32)
+    exact = (a.double() @ w.double() + rows.double()[:, None]).float()
+    assert (out32 - exact).norm() / exact.norm() < 1e-5
+
+
+def test_few_rows_output_outside_the_matrix_is_untouched():
+    dev = torch.device("cuda:0")
+    a, b = wl.dyadic_gemm_inputs(20, 1000, 2048)
+    backing = torch.full((64, 1024), -123.0, dtype=torch.bfloat16, device=dev)
+    kernels.gemm(a.to(dev), b.to(dev), out=backing[:20, :1000])
+    torch.cuda.synchronize()
+    host = backing.cpu()
+    assert torch.equal(host[:20, :1000], (a.double() @ b.double()).float().bfloat16())
+    assert (host[20:] == -123.0).all() and (host[:, 1000:] == -123.0).all()
 
 
 @pytest.mark.parametrize("m,n,k", [(2048, 2304, 1024), (4096, 4096, 512)])

@@ -22,6 +22,11 @@
 // accumulator rows into its own TMEM, and both CTAs run their own epilogue.  A stage is 32 KB
 // per CTA instead of 48, so every SM reads and writes a third less shared memory per FLOP.
 //
+// Few output rows against a large weight (at most 32 rows, fewer 256-column tiles than half the
+// SMs) run in the split form: a cluster of 2, 4 or 8 CTAs shares one tile, each CTA streams its
+// own part of K (32 rows of A per K block), and the partial sums meet in the first CTA's shared
+// memory (one bulk copy per CTA), where they are added in a fixed order before the epilogue.
+//
 // Algorithmic traffic per launch: (M*K + K*N [+K*N]) * 2 + bias + M*N*out_bytes.
 #include <cstdlib>
 #include <mutex>
@@ -39,6 +44,9 @@ constexpr int kGemmThreads = 192;        // TMA producer, MMA issuer, four epilo
 constexpr int kGemmFusedThreads = 320;   // ... plus four warps that do the cross-GPU reduction
 constexpr int kGroupM = 16;           // tile rasterisation: 16 row blocks share B columns in L2
 constexpr int kStageBytesA = kBM * kBK * 2;
+constexpr int kSplitRowsA = 32;          // rows of A the split form loads per K block
+constexpr int kSplitPitch = 256 + 4;     // floats between rows of a partial sum in shared memory (16-byte
+                                         // accesses by eight consecutive rows then fall into distinct banks)
 constexpr int kStoreBufBytes = 32 * 128;  // 32 rows x 128 B per epilogue warp
 constexpr int kStagingBytes = 4 * 2 * kStoreBufBytes;
 
@@ -84,6 +92,9 @@ struct GemmParams {
   // batch axis comes before the row axis and the two coordinates swap places.
   int a_batch_inside, out_batch_inside;
   long long stride_bias;   // elements between the side operands of consecutive batch entries
+  int split_rows;          // split form: accumulator rows a CTA hands to its cluster's first CTA (16 or 32)
+  void* out;               // split form: the output, which its epilogue stores without a tensor map
+  long long ldo;           // ... and its row pitch in elements
 };
 
 // In a CTA pair each CTA stages only half of the tile's B columns.
@@ -220,8 +231,10 @@ __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const Gem
   return true;
 }
 
+// (the split form leaves the epilogue loop of the other forms unreachable in its instantiations)
+#pragma nv_diag_suppress 128
 template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false,
-          bool kPair = false>
+          bool kPair = false, bool kSplit = false>
 __global__ void __launch_bounds__(kFused ? kGemmFusedThreads : kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_b,
@@ -241,6 +254,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 "TMEM allocation must be a power of two");
   static_assert(!(kBatched && (kFused || kGated)), "the batched form is the plain GEMM + epilogue");
   static_assert(!(kPair && kBatched) && (!kPair || kBN == 256), "pairs work on 256 x 256 tiles of one matrix");
+  // Split form (at most 32 output rows, a weight stream): the CTAs of a cluster share one
+  // 256-column tile and each walks its own part of K; see the epilogue.
+  static_assert(!kSplit || (kBN == 256 && !kGated && !kFused && !kBatched && !kPair),
+                "the split form is the plain single-matrix GEMM on 256-column tiles");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -258,15 +275,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   // fused form: counts epilogue warps whose stores of a tile have landed (four per tile); a
   // counter and not an mbarrier because the epilogue may run several tiles ahead of the reducers
   const uint32_t stored_count = bar_base + 8u * (2 * kStages + 4) + 8u;
+  // split form: partial_bar (first CTA) counts the bytes of the other CTAs' partial sums; go_bar
+  // (other CTAs) is the first CTA's word that its stage ring is free to receive them
+  const uint32_t partial_bar = stored_count + 8u;
+  const uint32_t go_bar = stored_count + 16u;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // Pair mode: CTA 0 of the cluster issues the MMAs; its `full` barriers count the bytes of both
   // CTAs' loads and its `tmem_empty` barriers the epilogue warps of both CTAs.
   const uint32_t rank = kPair ? cluster_rank() : 0u;
-  const int first_unit = kPair ? int(blockIdx.x >> 1) : int(blockIdx.x);
-  const int unit_stride = kPair ? int(gridDim.x >> 1) : int(gridDim.x);
+  const uint32_t split_rank = kSplit ? cluster_rank() : 0u;
+  const uint32_t split_size = kSplit ? cluster_size() : 1u;
+  const int first_unit = kPair ? int(blockIdx.x >> 1) : kSplit ? int(blockIdx.x / split_size) : int(blockIdx.x);
+  const int unit_stride = kPair ? int(gridDim.x >> 1) : kSplit ? int(gridDim.x / split_size) : int(gridDim.x);
   const int num_units = kPair ? ((p.tiles_m + 1) / 2) * p.tiles_n : p.num_tiles;
+  // K blocks this CTA walks (the launcher gives every CTA of a cluster at least one, and a
+  // cluster exactly one tile)
+  const int kb_begin = kSplit ? int(static_cast<long long>(split_rank) * p.num_kb / split_size) : 0;
+  const int kb_end = kSplit ? int(static_cast<long long>(split_rank + 1) * p.num_kb / split_size) : p.num_kb;
+  const uint32_t partial_bytes = kSplit ? uint32_t(p.split_rows) * kSplitPitch * 4u : 0u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -278,6 +306,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(tmem_empty_bar(a), kPair ? 8 : 4);
     }
     asm volatile("st.shared::cta.u32 [%0], %1;" ::"r"(stored_count), "r"(0u) : "memory");
+    if (kSplit) {
+      mbar_init(partial_bar, 1);
+      mbar_init(go_bar, 1);
+      if (split_rank == 0) mbar_arrive_expect_tx(partial_bar, (split_size - 1u) * partial_bytes);
+    }
     if (kFused && blockIdx.x == 0) g_fused_stamps[0] = global_ns();
     mbar_fence_init();
     tma_prefetch_desc(&map_a);
@@ -296,7 +329,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   }
   tc_fence_before();
   __syncthreads();
-  if (kPair) cluster_sync_all();   // the other CTA's barriers exist before anything arrives on them
+  if (kPair || kSplit) cluster_sync_all();   // the other CTAs' barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
@@ -311,7 +344,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         locate_tile<kPair>(p, kBatched ? tile - z * p.tiles_per_batch : tile, rank, m_blk, n_blk, flag_tile);
         const int m0 = m_blk * kBM;
         const int n0 = n_blk * kOutN;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
           if (!mbar_wait(empty_bar(s), phase ^ 1u, 0x101)) { ok = false; break; }
@@ -335,7 +368,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             }
             continue;
           }
-          mbar_arrive_expect_tx(full_bar(s), kStage);
+          // (split form: the A box holds 32 rows; the MMA reads all 128 rows of the stage, and what
+          // rows 32-127 hold only reaches accumulator rows that are never stored)
+          mbar_arrive_expect_tx(full_bar(s), kSplit ? kStage - kStageBytesA + kSplitRowsA * kBK * 2 : kStage);
           if (kBatched) {
             tma_load_3d(a_dst, &map_a, full_bar(s), kb * kBK, p.a_batch_inside ? z : m0,
                         p.a_batch_inside ? m0 : z);
@@ -368,7 +403,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, 0x201)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
           if (!mbar_wait(full_bar(s), phase, 0x202)) { ok = false; break; }
@@ -384,7 +419,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             if (kPair)
               umma_bf16_ss_pair(d_tmem, a_desc, b_desc, kIdesc, (kb | k4) != 0 ? 1u : 0u);
             else
-              umma_bf16_ss(d_tmem, a_desc, b_desc, kIdesc, (kb | k4) != 0 ? 1u : 0u);
+              umma_bf16_ss(d_tmem, a_desc, b_desc, kIdesc, (kb != kb_begin || k4 != 0) ? 1u : 0u);
           }
           if (kPair) umma_commit_pair(empty_bar(s)); else umma_commit(empty_bar(s));
         }
@@ -414,8 +449,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const int n0 = n_blk * kOutN;
       const uint32_t acc = local_tile & 1u;
       const uint32_t acc_phase = (local_tile >> 1) & 1u;
-      if (kFused) {
-        // a give-up must be uniform over the group because the fused path uses group barriers
+      if (kFused || kSplit) {
+        // a give-up must be uniform over the group because these paths use group barriers
         uint32_t good = mbar_wait(tmem_full_bar(acc), acc_phase, 0x301) ? 1u : 0u, all_good;
         asm volatile(
             "{\n"
@@ -435,6 +470,144 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       float row_bias = 0.0f;
       if (p.bias_mode == TRINITY_SM100_BIAS_ROW_VECTOR && row < p.m)
         row_bias = __bfloat162float(bias_base[row]);
+      if (kSplit) {
+        // Split form.  The output has at most 32 rows, all in the TMEM lanes of quadrant 0, which
+        // only that quadrant's warp can read.  Every CTA of the cluster holds the sum over its own
+        // part of K; that warp lays it out in the CTA's idle stage ring as [row][column] FP32.
+        // The other CTAs send theirs into the first CTA's ring with one bulk copy each, once the
+        // first CTA says its ring is idle too (its own MMAs have completed).  There all four
+        // epilogue warps add the parts in a fixed order (own, then by CTA rank), so the result
+        // does not depend on timing, apply the epilogue and store eight columns per thread.
+        const int rows = p.split_rows;
+        float* mine = reinterpret_cast<float*>(smem) +
+                      (split_rank == 0 ? (split_size - 1u) * (partial_bytes / 4u) : 0u);
+        if (quad == 0) {
+          if (split_rank == 0 && lane == 0)
+            for (uint32_t r = 1; r < split_size; ++r) mbar_arrive_cluster(map_to_peer(go_bar, r));
+#pragma unroll 1
+          for (int c0 = 0; c0 < kBN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(t_row + c0, v);
+            tmem_ld_wait();
+            if (lane < rows) {
+              float4* dst = reinterpret_cast<float4*>(mine + lane * kSplitPitch + c0);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                dst[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                     __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+            }
+          }
+        }
+        if (split_rank != 0) {
+          if (quad == 0) {
+            fence_async_smem();
+            __syncwarp();
+            if (!mbar_wait_cluster(go_bar, 0, 0x302)) { ok = false; break; }
+            if (lane == 0) {
+              asm volatile(
+                  "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                  ::"r"(map_to_peer(smem_base + (split_rank - 1u) * partial_bytes, 0)), "r"(smem_base),
+                    "r"(partial_bytes), "r"(map_to_peer(partial_bar, 0))
+                  : "memory");
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+          continue;
+        }
+        {
+          // the parts have landed and the first CTA's own part is laid out: a vote, so that a
+          // wait that gave up takes the whole group out together
+          uint32_t good = mbar_wait_cluster(partial_bar, 0, 0x303) ? 1u : 0u, all_good;
+          asm volatile(
+              "{\n"
+              ".reg .pred a, b;\n"
+              "setp.ne.u32 a, %1, 0;\n"
+              "bar.red.and.pred b, 1, 128, a;\n"
+              "selp.u32 %0, 1, 0, b;\n"
+              "}\n"
+              : "=r"(all_good)
+              : "r"(good)
+              : "memory");
+          if (!all_good) { ok = false; break; }
+        }
+        const float* parts = reinterpret_cast<const float*>(smem);
+        const uint32_t part_words = partial_bytes / 4u;
+        const int out_row = etid % rows;
+        for (int cb = etid / rows; cb < kBN / 8; cb += 128 / rows) {
+          const int col = cb * 8, gcol = n0 + col;
+          if (gcol >= p.n) break;
+          float x[8];
+          {
+            const float4* own = reinterpret_cast<const float4*>(parts + (split_size - 1u) * part_words +
+                                                                out_row * kSplitPitch + col);
+            const float4 lo = own[0], hi = own[1];
+            x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+            x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+          }
+          for (uint32_t r = 1; r < split_size; ++r) {
+            const float4* theirs = reinterpret_cast<const float4*>(parts + (r - 1u) * part_words +
+                                                                   out_row * kSplitPitch + col);
+            const float4 lo = theirs[0], hi = theirs[1];
+            x[0] += lo.x; x[1] += lo.y; x[2] += lo.z; x[3] += lo.w;
+            x[4] += hi.x; x[5] += hi.y; x[6] += hi.z; x[7] += hi.w;
+          }
+          if (out_row >= p.m) continue;
+          const bool whole = gcol + 8 <= p.n;
+          if (p.bias_mode == TRINITY_SM100_BIAS_ROW_VECTOR) {
+            const float b = __bfloat162float(bias_base[out_row]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] += b;
+          } else if (p.bias_mode != TRINITY_SM100_BIAS_NONE) {
+            const __nv_bfloat16* src = p.bias_mode == TRINITY_SM100_BIAS_COL_VECTOR
+                                           ? bias_base + gcol
+                                           : bias_base + static_cast<long long>(out_row) * p.ld_bias + gcol;
+            if (whole) {
+              const uint4 b = __ldg(reinterpret_cast<const uint4*>(src));
+              const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                x[e * 2] += bf16_lo(w[e]);
+                x[e * 2 + 1] += bf16_hi(w[e]);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (gcol + j < p.n) x[j] += __bfloat162float(src[j]);
+            }
+          }
+          if (p.activation != TRINITY_SM100_ACT_NONE) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = apply_activation(x[j], p.activation);
+          }
+          if (kOutF32) {
+            float* dst = static_cast<float*>(p.out) + static_cast<long long>(out_row) * p.ldo + gcol;
+            if (whole) {
+              reinterpret_cast<float4*>(dst)[0] = make_float4(x[0], x[1], x[2], x[3]);
+              reinterpret_cast<float4*>(dst)[1] = make_float4(x[4], x[5], x[6], x[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (gcol + j < p.n) dst[j] = x[j];
+            }
+          } else {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(out_row) * p.ldo + gcol;
+            if (whole) {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]),
+                                                          pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (gcol + j < p.n) dst[j] = __float2bfloat16(x[j]);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+        continue;
+      }
 
       for (int c0 = 0; c0 < kOutN; c0 += kColsPerStore) {
         if (lane == 0) tma_store_wait_read<1>();
@@ -624,10 +797,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   // Common exit: every role leaves its loop (normally or after a wait gave up) and meets here.
   // In pair mode neither CTA leaves while the other may still arrive on its barriers or its MMAs
-  // read this CTA's shared memory.
+  // read this CTA's shared memory; in the split form none leaves while its partial sums are
+  // still being copied out of its shared memory (the first CTA comes here after it has them).
   tc_fence_before();
   __syncthreads();
-  if (kPair) cluster_sync_all();
+  if (kPair || kSplit) cluster_sync_all();
   if (warp == 2) {
     if (g_device_status != 0) {
       // A wait gave up somewhere: give copies still in flight time to land before the
@@ -638,13 +812,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
+#pragma nv_diag_default 128
+
 // Shared-memory opt-in of one instantiation, once per device.
 template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false,
-          bool kPair = false>
+          bool kPair = false, bool kSplit = false>
 int opt_in_gemm() {
   static unsigned long long configured = 0;
   return opt_in_shared_memory(
-      reinterpret_cast<const void*>(&gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched, kPair>),
+      reinterpret_cast<const void*>(
+          &gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched, kPair, kSplit>),
       gemm_smem_bytes<kBN, kStages, kPair>(), &configured, "gemm");
 }
 
@@ -684,14 +861,14 @@ int resident_pairs(int* pairs) {
 }
 
 template <int kBN, int kStages, bool kGated, bool kOutF32, bool kFused = false, bool kBatched = false,
-          bool kPair = false>
+          bool kPair = false, bool kSplit = false>
 int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, const GemmPeers* fused = nullptr,
-                const trinity_sm100_gemm_batch* batch = nullptr) {
+                const trinity_sm100_gemm_batch* batch = nullptr, int split = 1) {
   constexpr int kOutN = kGated ? kBN / 2 : kBN;
   constexpr int kSmem = gemm_smem_bytes<kBN, kStages, kPair>();
   static_assert(kSmem <= 232448, "exceeds the 227 KB shared-memory limit");
-  auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched, kPair>;
-  if (int rc = opt_in_gemm<kBN, kStages, kGated, kOutF32, kFused, kBatched, kPair>()) return rc;
+  auto kernel = gemm_bf16_tcgen05_kernel<kBN, kStages, kGated, kOutF32, kFused, kBatched, kPair, kSplit>;
+  if (int rc = opt_in_gemm<kBN, kStages, kGated, kOutF32, kFused, kBatched, kPair, kSplit>()) return rc;
   CUtensorMap map_a, map_b, map_b2, map_out;
   int rc;
   const int out_bytes = kOutF32 ? 4 : 2;
@@ -718,7 +895,7 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
       return rc;
     }
   } else {
-    if ((rc = make_tensor_map_2d(&map_a, g.a, 2, g.k, g.m, g.lda * 2, kBK, kBM, true))) return rc;
+    if ((rc = make_tensor_map_2d(&map_a, g.a, 2, g.k, g.m, g.lda * 2, kBK, kSplit ? kSplitRowsA : kBM, true))) return rc;
     if ((rc = make_tensor_map_2d(&map_b, g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK, true))) return rc;
     if ((rc = make_tensor_map_2d(&map_b2, kGated ? g.b2 : g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK,
                                  true)))
@@ -745,8 +922,33 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
   p.stride_bias = kBatched ? batch->stride_bias : 0;
   p.num_kb = int((g.k + kBK - 1) / kBK);
   p.flag_tiles = (p.tiles_m + 1) / 2 * 2 * p.tiles_n;
+  p.split_rows = g.m <= 16 ? 16 : 32;
+  p.out = g.out;
+  p.ldo = g.ldo;
   GemmPeers peers = {};
   if (fused) peers = *fused;
+  if constexpr (kSplit) {
+    // one cluster of `split` CTAs per column tile, each CTA a part of K
+    if (p.tiles_m != 1 || g.m > 32 || split < 2 || split > 8 || p.num_kb < split ||
+        static_cast<size_t>(split) * p.split_rows * kSplitPitch * 4 > static_cast<size_t>(kStages) * stage_bytes<kBN>())
+      return fail(TRINITY_SM100_E_INVALID, "gemm (split form): %d rows, %d K blocks, %d parts", int(g.m), p.num_kb, split);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(p.num_tiles * split);
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = kSmem;
+    config.stream = stream;
+    cudaLaunchAttribute cluster;
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.x = split;
+    cluster.val.clusterDim.y = 1;
+    cluster.val.clusterDim.z = 1;
+    config.attrs = &cluster;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_b2, map_out, p, peers);
+    if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "gemm_bf16_tcgen05 (split) launch: %s", cudaGetErrorString(e));
+    count_launch();
+    return check_launch("gemm_bf16_tcgen05");
+  }
   if constexpr (kPair) {
     // a persistent grid of as many CTA pairs as are resident together
     int pairs = 0;
@@ -794,6 +996,7 @@ int gemm_prepare_device() {
   TRINITY_OPT_IN(256, kPairStages, true, true, false, false, true) TRINITY_OPT_IN(256, kPairStages, true, false, false, false, true)
   TRINITY_OPT_IN(256, kPairStages, false, true, false, false, true) TRINITY_OPT_IN(256, kPairStages, false, false, false, false, true)
   TRINITY_OPT_IN(256, kPairStages, false, false, true, false, true)
+  TRINITY_OPT_IN(256, 4, false, true, false, false, false, true) TRINITY_OPT_IN(256, 4, false, false, false, false, false, true)
 #undef TRINITY_OPT_IN
   return rc;
 }
@@ -886,12 +1089,30 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
   if (pairs)
     return f32 ? launch_gemm<256, kPairStages, false, true, false, false, true>(g, sm_count, stream)
                : launch_gemm<256, kPairStages, false, false, false, false, true>(g, sm_count, stream);
+  // One row tile (decode-time GEMMs: a few output rows against a large weight) makes the kernel
+  // a weight stream.  An MMA with both operands in shared memory takes 128 cycles or more
+  // whatever its width (measured: 128 at 256 columns, 165 at 64), so only 256-column tiles, 8 KB
+  // of weights per MMA, let an SM take in weights faster than its share of the memory
+  // bandwidth.  With fewer such tiles than half the SMs and at most 32 rows, the CTAs of a
+  // cluster share a tile and each walks a part of K (2, 4 or 8 parts, while every part keeps at
+  // least four K blocks and the parts' partial sums fit the stage ring).
+  const long long wide_tiles = row_tiles * ((g.n + 255) / 256);
+  if (row_tiles == 1) {
+    const long long k_blocks = (g.k + kBK - 1) / kBK;
+    int split = 1;
+    while (g.m <= 32 && split < (g.m <= 16 ? 8 : 4) && wide_tiles * split * 2 <= sm_count &&
+           k_blocks >= split * 2 * 4)
+      split *= 2;
+    if (split > 1)
+      return f32 ? launch_gemm<256, 4, false, true, false, false, false, true>(g, sm_count, stream, nullptr, nullptr, split)
+                 : launch_gemm<256, 4, false, false, false, false, false, true>(g, sm_count, stream, nullptr, nullptr, split);
+    if (wide_tiles * 2 > sm_count)
+      return f32 ? launch_gemm<256, 4, false, true>(g, sm_count, stream)
+                 : launch_gemm<256, 4, false, false>(g, sm_count, stream);
+  }
   // Wide tiles once there are enough of them to fill the machine.  Otherwise the tile width
   // that finishes in the fewest column-steps: a persistent CTA works through
-  // ceil(tiles / SMs) tiles of that width.  With few output rows (decode-time GEMMs) the kernel
-  // streams the weight matrix, and 64-column tiles are what spreads an [K, 8192] weight over
-  // 128 SMs instead of 64, each with an eight-stage ring in flight.
-  const long long wide_tiles = row_tiles * ((g.n + 255) / 256);
+  // ceil(tiles / SMs) tiles of that width.
   if (wide_tiles >= sm_count) {
     return f32 ? launch_gemm<256, 4, false, true>(g, sm_count, stream)
                : launch_gemm<256, 4, false, false>(g, sm_count, stream);

@@ -167,33 +167,6 @@ __device__ __forceinline__ void st_peer_v4(uint32_t remote_addr, float a, float 
 __device__ __forceinline__ void mbar_arrive_peer_relaxed(uint32_t remote_bar) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
 }
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-// Bounded wait that acquires at cluster scope (the arrivals come from the peer CTA).
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint32_t site) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const long long start = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait_cluster(bar, parity)) return true;
-    if (clock64() - start > wait_budget()) {
-      report_timeout(site);
-      return false;
-    }
-  }
-}
 // Chunk range [first, first + count) of split `s` when `chunks` are dealt out evenly.
 __host__ __device__ inline void split_range(int chunks, int splits, int s, int& first, int& count) {
   const int base = chunks / splits, extra = chunks % splits;

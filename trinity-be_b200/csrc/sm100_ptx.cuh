@@ -263,6 +263,39 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t n;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+  return n;
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait that acquires at cluster scope (the arrivals come from the peer CTA).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint32_t site) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long start = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (clock64() - start > wait_budget()) {
+      report_timeout(site);
+      return false;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- CTA pairs (cta_group::2)
 // Two CTAs of a cluster share one MMA: each holds its own 128 rows of A and its own half of B's
 // columns in shared memory and its own 128 rows of the accumulator in TMEM; the even CTA issues.
