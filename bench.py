@@ -17,8 +17,8 @@ Total work is fixed, so the scaling is strong.  Inputs are synthetic and seeded.
 
 Prints one JSON line (rank 0).  With the default workload the line also carries a "configs" block:
 on one GPU the other benchmark configurations (GEMM+bias 1024^3, GEMM+bias+ReLU 8192^3 over 100
-graph replays, RMSNorm, softmax, MLA decode), on N GPUs the head-sharded and the batch-sharded MLA
-decode.  Every workload's result is checked once, outside the timed region, on sampled rows
+graph replays, RMSNorm, softmax, MLA decode, the three decode-time GEMMs of 16 rows), on N GPUs the
+head-sharded and the batch-sharded MLA decode.  Every workload's result is checked once, outside the timed region, on sampled rows
 against a float64 evaluation on the host ("parity").  Timing is by CUDA events, the maximum over
 ranks, and `value` is the aggregate over all GPUs.
 """
@@ -860,8 +860,8 @@ def main():
     if args.workload == "tp_mlp" and not args.no_configs:
         del w
         torch.cuda.empty_cache()
-        names = (["gemm_bias_1024", "gemm_relu", "rmsnorm", "softmax", "mla"] if world == 1
-                 else ["mla", "mla_batch_sharded"])
+        names = (["gemm_bias_1024", "gemm_relu", "rmsnorm", "softmax", "mla", "gemm_decode_square",
+                  "gemm_decode_up", "gemm_decode_down"] if world == 1 else ["mla", "mla_batch_sharded"])
         block = {}
         for name in names:
             other = make_workload(name, device, None, world, rank)

@@ -157,6 +157,29 @@ def test_few_rows_split_over_k_epilogue_and_determinism():
     assert (out32 - exact).norm() / exact.norm() < 1e-5
 
 
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_few_rows_split_over_k_ragged_columns_and_matrix_bias(out_dtype):
+    """A column count that is no multiple of eight (the last eight-column store falls back to
+    single elements), operands and output as views of wider allocations, a matrix side operand
+    and SiLU, in the form that splits K."""
+    dev = torch.device("cuda:0")
+    m, n, k, pitch = 5, 1001, 2048, 1008
+    a, w, _ = wl.gemm_inputs(m, pitch, k, 81, "normal")
+    side = wl._normal((m, pitch), 0.5, wl._gen(82))
+    backing = torch.full((8, pitch), -7.0, dtype=out_dtype, device=dev)
+    kernels.gemm(a.to(dev), w.to(dev)[:, :n], bias=side.to(dev)[:, :n], bias_mode=kernels.BIAS_MATRIX,
+                 activation=kernels.ACT_SILU, out=backing[:m, :n])
+    torch.cuda.synchronize()
+    host = backing.cpu()
+    x = a.double() @ w.double()[:, :n] + side.double()[:, :n]
+    expected = x * torch.sigmoid(x)
+    if out_dtype == torch.float32:
+        torch.testing.assert_close(host[:m, :n], expected.float(), rtol=1e-4, atol=1e-4)
+    else:
+        assert_close_bf16(host[:m, :n], expected.float().bfloat16(), max_ulp=1, max_abs=2e-2)
+    assert (host[m:] == -7.0).all() and (host[:, n:] == -7.0).all()
+
+
 def test_few_rows_output_outside_the_matrix_is_untouched():
     dev = torch.device("cuda:0")
     a, b = wl.dyadic_gemm_inputs(20, 1000, 2048)
