@@ -180,6 +180,26 @@ def test_few_rows_split_over_k_ragged_columns_and_matrix_bias(out_dtype):
     assert (host[m:] == -7.0).all() and (host[:, n:] == -7.0).all()
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 3584, 8192), (24, 1000, 2048), (1, 128, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_few_rows_gated_form_split_over_k(m, n, k, out_dtype):
+    """The gated form with few rows and few tiles (a tensor-parallel shard of a SwiGLU projection
+    at decode time): each CTA of the cluster sums its part of K for the up and the gate
+    accumulator, the first CTA adds the parts and gates."""
+    a, wg, wu, _ = wl.mlp_inputs(m, k, n, 83)
+    dev = torch.device("cuda:0")
+    out = torch.empty((m, n), dtype=out_dtype, device=dev)
+    for _ in range(2):
+        kernels.gemm(a.to(dev), wu.to(dev), b2=wg.to(dev), activation=kernels.ACT_SILU_GATE, out=out)
+    torch.cuda.synchronize()
+    if out_dtype == torch.float32:
+        gate = a.double() @ wg.double()
+        expected = (a.double() @ wu.double()) * (gate * torch.sigmoid(gate))
+        torch.testing.assert_close(out.cpu(), expected.float(), rtol=1e-4, atol=1e-5)
+    else:
+        assert_close_bf16(out.cpu(), wl.gated_oracle(a, wu, wg), max_ulp=1)
+
+
 def test_few_rows_output_outside_the_matrix_is_untouched():
     dev = torch.device("cuda:0")
     a, b = wl.dyadic_gemm_inputs(20, 1000, 2048)

@@ -22,10 +22,11 @@
 // accumulator rows into its own TMEM, and both CTAs run their own epilogue.  A stage is 32 KB
 // per CTA instead of 48, so every SM reads and writes a third less shared memory per FLOP.
 //
-// Few output rows against a large weight (at most 32 rows, fewer 256-column tiles than half the
-// SMs) run in the split form: a cluster of 2, 4 or 8 CTAs shares one tile, each CTA streams its
-// own part of K (32 rows of A per K block), and the partial sums meet in the first CTA's shared
-// memory (one bulk copy per CTA), where they are added in a fixed order before the epilogue.
+// Few output rows against a large weight (at most 32 rows, fewer tiles of 256 accumulator columns
+// than half the SMs; plain or gated) run in the split form: a cluster of 2, 4 or 8 CTAs shares
+// one tile, each CTA streams its own part of K (32 rows of A per K block), and the partial sums
+// meet in the first CTA's shared memory (one bulk copy per CTA), where they are added in a fixed
+// order before the epilogue.
 //
 // Algorithmic traffic per launch: (M*K + K*N [+K*N]) * 2 + bias + M*N*out_bytes.
 #include <cstdlib>
@@ -256,8 +257,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   static_assert(!(kPair && kBatched) && (!kPair || kBN == 256), "pairs work on 256 x 256 tiles of one matrix");
   // Split form (at most 32 output rows, a weight stream): the CTAs of a cluster share one
   // 256-column tile and each walks its own part of K; see the epilogue.
-  static_assert(!kSplit || (kBN == 256 && !kGated && !kFused && !kBatched && !kPair),
-                "the split form is the plain single-matrix GEMM on 256-column tiles");
+  static_assert(!kSplit || (kBN == 256 && !kFused && !kBatched && !kPair),
+                "the split form works on 256 accumulator columns of one matrix (plain or gated)");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -535,23 +536,31 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const float* parts = reinterpret_cast<const float*>(smem);
         const uint32_t part_words = partial_bytes / 4u;
         const int out_row = etid % rows;
-        for (int cb = etid / rows; cb < kBN / 8; cb += 128 / rows) {
+        // sum over the parts of eight accumulator columns from `first_col` on, own part first
+        auto summed = [&](int first_col, float (&x)[8]) {
+          const float4* own = reinterpret_cast<const float4*>(parts + (split_size - 1u) * part_words +
+                                                              out_row * kSplitPitch + first_col);
+          const float4 lo = own[0], hi = own[1];
+          x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+          x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+          for (uint32_t r = 1; r < split_size; ++r) {
+            const float4* theirs = reinterpret_cast<const float4*>(parts + (r - 1u) * part_words +
+                                                                   out_row * kSplitPitch + first_col);
+            const float4 tl = theirs[0], th = theirs[1];
+            x[0] += tl.x; x[1] += tl.y; x[2] += tl.z; x[3] += tl.w;
+            x[4] += th.x; x[5] += th.y; x[6] += th.z; x[7] += th.w;
+          }
+        };
+        for (int cb = etid / rows; cb < kOutN / 8; cb += 128 / rows) {
           const int col = cb * 8, gcol = n0 + col;
           if (gcol >= p.n) break;
           float x[8];
-          {
-            const float4* own = reinterpret_cast<const float4*>(parts + (split_size - 1u) * part_words +
-                                                                out_row * kSplitPitch + col);
-            const float4 lo = own[0], hi = own[1];
-            x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
-            x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
-          }
-          for (uint32_t r = 1; r < split_size; ++r) {
-            const float4* theirs = reinterpret_cast<const float4*>(parts + (r - 1u) * part_words +
-                                                                   out_row * kSplitPitch + col);
-            const float4 lo = theirs[0], hi = theirs[1];
-            x[0] += lo.x; x[1] += lo.y; x[2] += lo.z; x[3] += lo.w;
-            x[4] += hi.x; x[5] += hi.y; x[6] += hi.z; x[7] += hi.w;
+          summed(col, x);
+          if (kGated) {
+            float gate[8];
+            summed(kOutN + col, gate);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] *= gate[j] * fast_sigmoid(gate[j]);
           }
           if (out_row >= p.m) continue;
           const bool whole = gcol + 8 <= p.n;
@@ -577,7 +586,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 if (gcol + j < p.n) x[j] += __bfloat162float(src[j]);
             }
           }
-          if (p.activation != TRINITY_SM100_ACT_NONE) {
+          if (!kGated && p.activation != TRINITY_SM100_ACT_NONE) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) x[j] = apply_activation(x[j], p.activation);
           }
@@ -997,6 +1006,7 @@ int gemm_prepare_device() {
   TRINITY_OPT_IN(256, kPairStages, false, true, false, false, true) TRINITY_OPT_IN(256, kPairStages, false, false, false, false, true)
   TRINITY_OPT_IN(256, kPairStages, false, false, true, false, true)
   TRINITY_OPT_IN(256, 4, false, true, false, false, false, true) TRINITY_OPT_IN(256, 4, false, false, false, false, false, true)
+  TRINITY_OPT_IN(256, 4, true, true, false, false, false, true) TRINITY_OPT_IN(256, 4, true, false, false, false, false, true)
 #undef TRINITY_OPT_IN
   return rc;
 }
@@ -1079,7 +1089,23 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
   // SM pairs; an odd last row tile costs its pair half a tile of zero work.
   const long long pair_units = (row_tiles + 1) / 2 * ((g.n + (gated ? 127 : 255)) / (gated ? 128 : 256));
   const bool pairs = pairs_allowed() && row_tiles >= 2 && pair_units >= sm_count / 2;
+  // One row tile (decode-time GEMMs: a few output rows against a large weight) makes the kernel
+  // a weight stream.  An MMA with both operands in shared memory takes 128 cycles or more
+  // whatever its width (measured: 128 at 256 columns, 165 at 64), so only tiles of 256
+  // accumulator columns, 8 KB of weights per MMA, let an SM take in weights faster than its
+  // share of the memory bandwidth.  With fewer such tiles than half the SMs and at most 32 rows,
+  // the CTAs of a cluster share a tile and each walks a part of K (2, 4 or 8 parts, while every
+  // part keeps at least four K blocks and the parts' partial sums fit the stage ring).
+  const long long wide_tiles = row_tiles * ((g.n + (gated ? 127 : 255)) / (gated ? 128 : 256));
+  int split = 1;
+  if (row_tiles == 1 && g.m <= 32) {
+    const long long k_blocks = (g.k + kBK - 1) / kBK;
+    while (split < (g.m <= 16 ? 8 : 4) && wide_tiles * split * 2 <= sm_count && k_blocks >= split * 2 * 4) split *= 2;
+  }
   if (gated) {
+    if (split > 1)
+      return f32 ? launch_gemm<256, 4, true, true, false, false, false, true>(g, sm_count, stream, nullptr, nullptr, split)
+                 : launch_gemm<256, 4, true, false, false, false, false, true>(g, sm_count, stream, nullptr, nullptr, split);
     if (pairs && pairs_mode() == 2)
       return f32 ? launch_gemm<256, kPairStages, true, true, false, false, true>(g, sm_count, stream)
                  : launch_gemm<256, kPairStages, true, false, false, false, true>(g, sm_count, stream);
@@ -1089,20 +1115,7 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
   if (pairs)
     return f32 ? launch_gemm<256, kPairStages, false, true, false, false, true>(g, sm_count, stream)
                : launch_gemm<256, kPairStages, false, false, false, false, true>(g, sm_count, stream);
-  // One row tile (decode-time GEMMs: a few output rows against a large weight) makes the kernel
-  // a weight stream.  An MMA with both operands in shared memory takes 128 cycles or more
-  // whatever its width (measured: 128 at 256 columns, 165 at 64), so only 256-column tiles, 8 KB
-  // of weights per MMA, let an SM take in weights faster than its share of the memory
-  // bandwidth.  With fewer such tiles than half the SMs and at most 32 rows, the CTAs of a
-  // cluster share a tile and each walks a part of K (2, 4 or 8 parts, while every part keeps at
-  // least four K blocks and the parts' partial sums fit the stage ring).
-  const long long wide_tiles = row_tiles * ((g.n + 255) / 256);
   if (row_tiles == 1) {
-    const long long k_blocks = (g.k + kBK - 1) / kBK;
-    int split = 1;
-    while (g.m <= 32 && split < (g.m <= 16 ? 8 : 4) && wide_tiles * split * 2 <= sm_count &&
-           k_blocks >= split * 2 * 4)
-      split *= 2;
     if (split > 1)
       return f32 ? launch_gemm<256, 4, false, true, false, false, false, true>(g, sm_count, stream, nullptr, nullptr, split)
                  : launch_gemm<256, 4, false, false, false, false, false, true>(g, sm_count, stream, nullptr, nullptr, split);
