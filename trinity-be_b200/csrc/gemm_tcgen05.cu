@@ -333,6 +333,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   if (kPair || kSplit) cluster_sync_all();   // the other CTAs' barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  if (!kFused) {
+    // Set-up is done and has touched no operand: the next kernel of the stream may be scheduled,
+    // and this one goes on once the previous kernel's results are visible.  (The form with the
+    // cross-GPU sum is always launched the ordinary way.)
+    grid_dependents_may_launch();
+    grid_dependency_wait();
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -941,19 +948,8 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
     if (p.tiles_m != 1 || g.m > 32 || split < 2 || split > 8 || p.num_kb < split ||
         static_cast<size_t>(split) * p.split_rows * kSplitPitch * 4 > static_cast<size_t>(kStages) * stage_bytes<kBN>())
       return fail(TRINITY_SM100_E_INVALID, "gemm (split form): %d rows, %d K blocks, %d parts", int(g.m), p.num_kb, split);
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(p.num_tiles * split);
-    config.blockDim = dim3(kGemmThreads);
-    config.dynamicSmemBytes = kSmem;
-    config.stream = stream;
-    cudaLaunchAttribute cluster;
-    cluster.id = cudaLaunchAttributeClusterDimension;
-    cluster.val.clusterDim.x = split;
-    cluster.val.clusterDim.y = 1;
-    cluster.val.clusterDim.z = 1;
-    config.attrs = &cluster;
-    config.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_b2, map_out, p, peers);
+    KernelLaunch launch(dim3(p.num_tiles * split), dim3(kGemmThreads), kSmem, stream, unsigned(split));
+    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, map_a, map_b, map_b2, map_out, p, peers);
     if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "gemm_bf16_tcgen05 (split) launch: %s", cudaGetErrorString(e));
     count_launch();
     return check_launch("gemm_bf16_tcgen05");
@@ -964,26 +960,18 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
     if ((rc = resident_pairs<kBN, kStages, kGated, kOutF32, kFused>(&pairs))) return rc;
     const int units = (p.tiles_m + 1) / 2 * p.tiles_n;
     if (units < pairs) pairs = units;
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(2 * pairs);
-    config.blockDim = dim3(kFused ? kGemmFusedThreads : kGemmThreads);
-    config.dynamicSmemBytes = kSmem;
-    config.stream = stream;
-    cudaLaunchAttribute cluster;
-    cluster.id = cudaLaunchAttributeClusterDimension;
-    cluster.val.clusterDim.x = 2;
-    cluster.val.clusterDim.y = 1;
-    cluster.val.clusterDim.z = 1;
-    config.attrs = &cluster;
-    config.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_a, map_b, map_b2, map_out, p, peers);
+    KernelLaunch launch(dim3(2 * pairs), dim3(kFused ? kGemmFusedThreads : kGemmThreads), kSmem, stream, 2);
+    if (kFused) launch.config.numAttrs = 1;   // the cluster only: no early start beside a cross-GPU exchange
+    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, map_a, map_b, map_b2, map_out, p, peers);
     if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "gemm_bf16_tcgen05 (pairs) launch: %s", cudaGetErrorString(e));
     count_launch();
     return check_launch("gemm_bf16_tcgen05");
   }
   const int grid = p.num_tiles < sm_count ? p.num_tiles : sm_count;
-  kernel<<<grid, kFused ? kGemmFusedThreads : kGemmThreads, kSmem, stream>>>(map_a, map_b, map_b2,
-                                                                            map_out, p, peers);
+  KernelLaunch launch(dim3(grid), dim3(kFused ? kGemmFusedThreads : kGemmThreads), kSmem, stream);
+  if (kFused) launch.config.numAttrs = 0;
+  cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, map_a, map_b, map_b2, map_out, p, peers);
+  if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "gemm_bf16_tcgen05 launch: %s", cudaGetErrorString(e));
   count_launch();
   return check_launch("gemm_bf16_tcgen05");
 }

@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "sm100_ptx.cuh"
@@ -98,6 +99,34 @@ int check_launch(const char* what) {
   if (e != cudaSuccess)
     return fail(TRINITY_SM100_E_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
   return 0;
+}
+
+bool dependent_launch_enabled() {
+  const char* v = getenv("TRINITY_SM100_DEPENDENT_LAUNCH");
+  return !(v && v[0] == '0');
+}
+
+KernelLaunch::KernelLaunch(dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream, unsigned cluster_x) {
+  config = cudaLaunchConfig_t{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared_bytes;
+  config.stream = stream;
+  unsigned count = 0;
+  if (cluster_x > 1) {
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = cluster_x;
+    attributes[count].val.clusterDim.y = 1;
+    attributes[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  if (dependent_launch_enabled()) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
 }
 
 int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,

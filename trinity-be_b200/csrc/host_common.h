@@ -31,6 +31,19 @@ int opt_in_shared_memory(const void* kernel, int bytes, unsigned long long* done
 int gemm_prepare_device();
 int mla_prepare_device();
 
+// Launch configuration of the single-GPU kernels: optional cluster width, and (unless
+// TRINITY_SM100_DEPENDENT_LAUNCH=0) programmatic dependent launch, with which the kernel's thread
+// blocks may start while the previous kernel of the stream is still draining.  Every kernel
+// launched this way runs only its set-up (barriers, tensor memory, descriptor prefetch) before
+// `griddepcontrol.wait`, which returns once the previous kernel has completed and its writes are
+// visible; nothing before the wait reads or writes memory another kernel produces.
+struct KernelLaunch {
+  cudaLaunchConfig_t config;
+  cudaLaunchAttribute attributes[2];
+  KernelLaunch(dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream, unsigned cluster_x = 1);
+};
+bool dependent_launch_enabled();
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // 2-D tiled tensor map over a row-major matrix: `inner` contiguous elements per row,

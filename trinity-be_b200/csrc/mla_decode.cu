@@ -308,6 +308,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap map_cache,
   cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // set-up done, no operand touched yet (see KernelLaunch)
+  grid_dependents_may_launch();
+  grid_dependency_wait();
   Segment seg;
 
   if (warp == 0) {
@@ -854,6 +857,8 @@ mla_combine_kernel(const float* __restrict__ partial_o, const float* __restrict_
                    __nv_bfloat16* __restrict__ out, int rows, int heads, int pieces, int balanced,
                    int chunks_per_seq, int clusters, long long units) {
   // one warp per (sequence, head): lane l owns columns [4 l, 4 l + 4) of each 128-column quarter
+  grid_dependents_may_launch();
+  grid_dependency_wait();   // the partial results come from the decode kernel launched just before
   const int bh = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (bh >= rows) return;
@@ -1124,28 +1129,24 @@ extern "C" int trinity_sm100_mla_decode_bf16(const trinity_sm100_mla* args, void
   p.units = schedule.units;
   p.scale_log2 = fabsf(a.scale) * 1.4426950408889634f;
   p.negate = a.scale < 0.0f ? 1 : 0;
-  cudaLaunchConfig_t config = {};
-  config.gridDim = balanced ? dim3(2, schedule.clusters, 1) : dim3(2, splits, a.batch);
-  config.blockDim = dim3(kMlaThreads);
-  config.dynamicSmemBytes = kMlaSmem;
-  config.stream = stream;
-  cudaLaunchAttribute cluster;
-  cluster.id = cudaLaunchAttributeClusterDimension;
-  cluster.val.clusterDim.x = 2;   // the two feature halves of one (batch, split)
-  cluster.val.clusterDim.y = 1;
-  cluster.val.clusterDim.z = 1;
-  config.attrs = &cluster;
-  config.numAttrs = 1;
-  cudaError_t launch_error = cudaLaunchKernelEx(&config, mla_decode_kernel, map_cache, map_rope, map_query, p);
+  // clusters of two: the two feature halves of one (batch, split)
+  KernelLaunch launch(balanced ? dim3(2, schedule.clusters, 1) : dim3(2, splits, a.batch), dim3(kMlaThreads),
+                      kMlaSmem, stream, 2);
+  cudaError_t launch_error =
+      cudaLaunchKernelEx(&launch.config, mla_decode_kernel, map_cache, map_rope, map_query, p);
   if (launch_error != cudaSuccess)
     return fail(TRINITY_SM100_E_CUDA, "mla_decode launch: %s", cudaGetErrorString(launch_error));
   count_launch();
   if ((rc = check_launch("mla_decode"))) return rc;
   if (splits > 1) {
     const int rows = a.batch * a.heads;
-    mla_combine_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(p.partial_o, p.partial_lse, p.out, rows,
-                                                           a.heads, splits, p.balanced,
-                                                           p.chunks_per_seq, p.clusters, p.units);
+    KernelLaunch merge(dim3((rows + 3) / 4), dim3(128), 0, stream);
+    launch_error = cudaLaunchKernelEx(&merge.config, mla_combine_kernel, static_cast<const float*>(p.partial_o),
+                                      static_cast<const float*>(p.partial_lse), p.out, rows, int(a.heads), int(splits),
+                                      int(p.balanced), int(p.chunks_per_seq), int(p.clusters),
+                                      static_cast<long long>(p.units));
+    if (launch_error != cudaSuccess)
+      return fail(TRINITY_SM100_E_CUDA, "mla_combine launch: %s", cudaGetErrorString(launch_error));
     count_launch();
     if ((rc = check_launch("mla_combine"))) return rc;
   }

@@ -70,6 +70,8 @@ __device__ __forceinline__ void pw_load8(const PwOperand& o, long long r, long l
 }
 
 __global__ void __launch_bounds__(kPwThreads) pointwise_kernel(const PwParams p, int vector) {
+  grid_dependents_may_launch();
+  grid_dependency_wait();
   const long long groups_per_row = (p.cols + 7) / 8;
   const long long total = p.rows * groups_per_row;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -141,6 +143,8 @@ __global__ void __launch_bounds__(kPwThreads) pointwise_kernel(const PwParams p,
 __global__ void __launch_bounds__(256) row_reduce_sum_kernel(const void* x, int dtype, float* y,
                                                              long long rows, long long cols,
                                                              int square, int vector) {
+  grid_dependents_may_launch();
+  grid_dependency_wait();
   const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -218,8 +222,9 @@ extern "C" int trinity_sm100_pointwise(const trinity_sm100_pointwise_args* args,
   long long blocks = (groups + kPwThreads - 1) / kPwThreads;
   const long long cap = static_cast<long long>(sm_count) * 16;
   if (blocks > cap) blocks = cap;
-  pointwise_kernel<<<unsigned(blocks), kPwThreads, 0, static_cast<cudaStream_t>(stream_handle)>>>(
-      p, vector ? 1 : 0);
+  KernelLaunch launch(dim3(unsigned(blocks)), dim3(kPwThreads), 0, static_cast<cudaStream_t>(stream_handle));
+  cudaError_t e = cudaLaunchKernelEx(&launch.config, pointwise_kernel, p, vector ? 1 : 0);
+  if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "pointwise launch: %s", cudaGetErrorString(e));
   count_launch();
   return check_launch("pointwise");
 }
@@ -232,8 +237,11 @@ extern "C" int trinity_sm100_row_reduce_sum(const void* x, int32_t x_dtype, void
   if (int rc = require_sm100(nullptr)) return rc;
   const bool vector = cols % 8 == 0 && vector_ok(x, x_dtype);
   const unsigned grid = unsigned((rows + 7) / 8);
-  row_reduce_sum_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_handle)>>>(
-      x, x_dtype, static_cast<float*>(y), rows, cols, square, vector ? 1 : 0);
+  KernelLaunch launch(dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream_handle));
+  cudaError_t e = cudaLaunchKernelEx(&launch.config, row_reduce_sum_kernel, x, int(x_dtype), static_cast<float*>(y),
+                                     static_cast<long long>(rows), static_cast<long long>(cols), int(square),
+                                     vector ? 1 : 0);
+  if (e != cudaSuccess) return fail(TRINITY_SM100_E_CUDA, "row_reduce_sum launch: %s", cudaGetErrorString(e));
   count_launch();
   return check_launch("row_reduce_sum");
 }

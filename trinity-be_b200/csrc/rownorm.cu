@@ -57,6 +57,8 @@ rmsnorm_rows_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gain,
   constexpr int kBlock = kThreads > kRowBlock ? kThreads : kRowBlock;
   constexpr int kRowsPerCta = kBlock / kThreads;
   __shared__ float scratch[kBlock / 32];
+  grid_dependents_may_launch();
+  grid_dependency_wait();   // the previous kernel of the stream may have produced x
   const int lane = threadIdx.x % kThreads;
   const long long row = static_cast<long long>(blockIdx.x) * kRowsPerCta + threadIdx.x / kThreads;
   const bool live = row < rows;
@@ -112,6 +114,8 @@ softmax_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, long lon
   constexpr int kBlock = kThreads > kRowBlock ? kThreads : kRowBlock;
   constexpr int kRowsPerCta = kBlock / kThreads;
   __shared__ float scratch[kBlock / 32];
+  grid_dependents_may_launch();
+  grid_dependency_wait();   // the previous kernel of the stream may have produced x
   const int lane = threadIdx.x % kThreads;
   const long long row = static_cast<long long>(blockIdx.x) * kRowsPerCta + threadIdx.x / kThreads;
   const bool live = row < rows;
@@ -206,14 +210,18 @@ extern "C" int trinity_sm100_rmsnorm_bf16(const void* x, const void* gain, void*
   const uint4* gp = static_cast<const uint4*>(gain);
   uint4* yp = static_cast<uint4*>(y);
   const RowShape shape = row_shape(cols);
+  cudaError_t launch_error = cudaSuccess;
 #define TRINITY_RMS(T, V)                                                                        \
   {                                                                                              \
     constexpr int block = (T) > kRowBlock ? (T) : kRowBlock;                                     \
     const unsigned grid = unsigned((rows + block / (T) - 1) / (block / (T)));                    \
+    KernelLaunch launch(dim3(grid), dim3(block), 0, stream);                                     \
     if (gain)                                                                                    \
-      rmsnorm_rows_kernel<T, V, true><<<grid, block, 0, stream>>>(xp, gp, yp, rows, int(cols), eps); \
+      launch_error = cudaLaunchKernelEx(&launch.config, rmsnorm_rows_kernel<T, V, true>, xp, gp, yp, \
+                                        static_cast<long long>(rows), int(cols), eps);          \
     else                                                                                         \
-      rmsnorm_rows_kernel<T, V, false><<<grid, block, 0, stream>>>(xp, gp, yp, rows, int(cols), eps); \
+      launch_error = cudaLaunchKernelEx(&launch.config, rmsnorm_rows_kernel<T, V, false>, xp, gp, yp, \
+                                        static_cast<long long>(rows), int(cols), eps);          \
   }
   if (shape.threads == 32 && shape.vec == 1) TRINITY_RMS(32, 1)
   else if (shape.threads == 32 && shape.vec == 2) TRINITY_RMS(32, 2)
@@ -222,6 +230,8 @@ extern "C" int trinity_sm100_rmsnorm_bf16(const void* x, const void* gain, void*
   else if (shape.threads == 128) TRINITY_RMS(128, 4)
   else TRINITY_RMS(256, 4)
 #undef TRINITY_RMS
+  if (launch_error != cudaSuccess)
+    return fail(TRINITY_SM100_E_CUDA, "rmsnorm_rows launch: %s", cudaGetErrorString(launch_error));
   count_launch();
   return check_launch("rmsnorm_rows");
 }
@@ -234,11 +244,14 @@ extern "C" int trinity_sm100_softmax_bf16(const void* x, void* y, int64_t rows, 
   const uint4* xp = static_cast<const uint4*>(x);
   uint4* yp = static_cast<uint4*>(y);
   const RowShape shape = row_shape(cols);
+  cudaError_t launch_error = cudaSuccess;
 #define TRINITY_SMX(T, V)                                                                  \
   {                                                                                        \
     constexpr int block = (T) > kRowBlock ? (T) : kRowBlock;                               \
     const unsigned grid = unsigned((rows + block / (T) - 1) / (block / (T)));              \
-    softmax_rows_kernel<T, V><<<grid, block, 0, stream>>>(xp, yp, rows, int(cols));        \
+    KernelLaunch launch(dim3(grid), dim3(block), 0, stream);                               \
+    launch_error = cudaLaunchKernelEx(&launch.config, softmax_rows_kernel<T, V>, xp, yp,   \
+                                      static_cast<long long>(rows), int(cols));            \
   }
   if (shape.threads == 32 && shape.vec == 1) TRINITY_SMX(32, 1)
   else if (shape.threads == 32 && shape.vec == 2) TRINITY_SMX(32, 2)
@@ -247,6 +260,8 @@ extern "C" int trinity_sm100_softmax_bf16(const void* x, void* y, int64_t rows, 
   else if (shape.threads == 128) TRINITY_SMX(128, 4)
   else TRINITY_SMX(256, 4)
 #undef TRINITY_SMX
+  if (launch_error != cudaSuccess)
+    return fail(TRINITY_SM100_E_CUDA, "softmax_rows launch: %s", cudaGetErrorString(launch_error));
   count_launch();
   return check_launch("softmax_rows");
 }

@@ -89,6 +89,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
   }
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with programmatic stream serialization starts while the previous kernel of
+// its stream is still running.  `grid_dependency_wait` returns once that kernel has completed and
+// its writes are visible (at once if the launch was an ordinary one); `grid_dependents_may_launch`
+// lets the next kernel's thread blocks be scheduled as soon as every block of this one has said so.
+__device__ __forceinline__ void grid_dependents_may_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
