@@ -67,7 +67,11 @@ enum trinity_sm100_activation {
  *   out [m,n]  bf16 or fp32 row-major, leading dimension ldo (bytes per row multiple of 16)
  *
  * All base pointers must be 16-byte aligned.  m, n, k need not be multiples of the tile:
- * loads past an edge read zero and stores past an edge are dropped.
+ * loads past an edge read zero and stores past an edge are dropped.  The launcher picks the
+ * form from the shape (CTA pairs on 256 x 256 tiles for large problems; 128-row tiles of 256,
+ * 128 or 64 columns otherwise; for at most 32 rows against a weight with few column tiles, a
+ * cluster of CTAs per tile that splits K and adds its partial sums in a fixed order), and every
+ * form sums in an order that does not depend on timing: two launches give the same bits.
  *
  * Replaces the Hopper WGMMA tile kernel plus its register "follower" epilogue
  * (src/emit/provider/cute/operator/gemm/hopper/mod.rs:32-157,
