@@ -69,7 +69,7 @@ enum trinity_sm100_activation {
  * All base pointers must be 16-byte aligned.  m, n, k need not be multiples of the tile:
  * loads past an edge read zero and stores past an edge are dropped.  The launcher picks the
  * form from the shape (CTA pairs on 256 x 256 tiles for large problems; 128-row tiles of 256,
- * 128 or 64 columns otherwise; for at most 32 rows against a weight with few column tiles, a
+ * 128 or 64 columns otherwise; for at most 64 rows against a weight with few column tiles, a
  * cluster of CTAs per tile that splits K and adds its partial sums in a fixed order), and every
  * form sums in an order that does not depend on timing: two launches give the same bits.
  *

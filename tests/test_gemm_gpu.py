@@ -130,10 +130,13 @@ def test_decode_time_shapes(m, n, k):
     (17, 8192, 4096),    # 17..32 rows: four parts at most, 32 rows handed over
     (32, 8200, 1000),    # ragged columns and a ragged last K block
     (9, 1032, 4104),     # five tiles, the last 8 columns wide; K blocks not a multiple of the parts
+    (33, 4096, 2048),    # 33..64 rows: two warps of each CTA hand rows over, two parts
+    (64, 8192, 1024),
+    (50, 1000, 4096),
 ])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_few_rows_split_over_k_bit_exact(m, n, k, out_dtype):
-    """Up to 32 output rows with fewer 256-column tiles than half the SMs: the CTAs of a cluster
+    """Up to 64 output rows with fewer 256-column tiles than half the SMs: the CTAs of a cluster
     share a tile, each sums a part of K, and the first adds the parts in a fixed order.  Exact
     operands, so the sum must not depend on how K was cut, and repeated launches must agree."""
     a, b = wl.dyadic_gemm_inputs(m, n, k)

@@ -22,9 +22,9 @@
 // accumulator rows into its own TMEM, and both CTAs run their own epilogue.  A stage is 32 KB
 // per CTA instead of 48, so every SM reads and writes a third less shared memory per FLOP.
 //
-// Few output rows against a large weight (at most 32 rows, fewer tiles of 256 accumulator columns
+// Few output rows against a large weight (at most 64 rows, fewer tiles of 256 accumulator columns
 // than half the SMs; plain or gated) run in the split form: a cluster of 2, 4 or 8 CTAs shares
-// one tile, each CTA streams its own part of K (32 rows of A per K block), and the partial sums
+// one tile, each CTA streams its own part of K (32 or 64 rows of A per K block), and the partial sums
 // meet in the first CTA's shared memory (one bulk copy per CTA), where they are added in a fixed
 // order before the epilogue.
 //
@@ -45,7 +45,7 @@ constexpr int kGemmThreads = 192;        // TMA producer, MMA issuer, four epilo
 constexpr int kGemmFusedThreads = 320;   // ... plus four warps that do the cross-GPU reduction
 constexpr int kGroupM = 16;           // tile rasterisation: 16 row blocks share B columns in L2
 constexpr int kStageBytesA = kBM * kBK * 2;
-constexpr int kSplitRowsA = 32;          // rows of A the split form loads per K block
+constexpr int kSplitRowsMax = 64;        // the split form serves up to this many output rows
 constexpr int kSplitPitch = 256 + 4;     // floats between rows of a partial sum in shared memory (16-byte
                                          // accesses by eight consecutive rows then fall into distinct banks)
 constexpr int kStoreBufBytes = 32 * 128;  // 32 rows x 128 B per epilogue warp
@@ -93,7 +93,8 @@ struct GemmParams {
   // batch axis comes before the row axis and the two coordinates swap places.
   int a_batch_inside, out_batch_inside;
   long long stride_bias;   // elements between the side operands of consecutive batch entries
-  int split_rows;          // split form: accumulator rows a CTA hands to its cluster's first CTA (16 or 32)
+  int split_rows;          // split form: accumulator rows a CTA hands to its cluster's first CTA (16, 32 or 64)
+  int split_a_rows;        // split form: rows of A loaded per K block (32 or 64)
   void* out;               // split form: the output, which its epilogue stores without a tensor map
   long long ldo;           // ... and its row pitch in elements
 };
@@ -376,9 +377,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             }
             continue;
           }
-          // (split form: the A box holds 32 rows; the MMA reads all 128 rows of the stage, and what
-          // rows 32-127 hold only reaches accumulator rows that are never stored)
-          mbar_arrive_expect_tx(full_bar(s), kSplit ? kStage - kStageBytesA + kSplitRowsA * kBK * 2 : kStage);
+          // (split form: the A box holds 32 or 64 rows; the MMA reads all 128 rows of the stage, and
+          // what the other rows hold only reaches accumulator rows that are never stored)
+          mbar_arrive_expect_tx(full_bar(s), kSplit ? kStage - kStageBytesA + p.split_a_rows * kBK * 2 : kStage);
           if (kBatched) {
             tma_load_3d(a_dst, &map_a, full_bar(s), kb * kBK, p.a_batch_inside ? z : m0,
                         p.a_batch_inside ? m0 : z);
@@ -479,26 +480,28 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       if (p.bias_mode == TRINITY_SM100_BIAS_ROW_VECTOR && row < p.m)
         row_bias = __bfloat162float(bias_base[row]);
       if (kSplit) {
-        // Split form.  The output has at most 32 rows, all in the TMEM lanes of quadrant 0, which
-        // only that quadrant's warp can read.  Every CTA of the cluster holds the sum over its own
-        // part of K; that warp lays it out in the CTA's idle stage ring as [row][column] FP32.
-        // The other CTAs send theirs into the first CTA's ring with one bulk copy each, once the
+        // Split form.  The output has at most 64 rows, in the TMEM lanes of the first one or two
+        // quadrants, which only those quadrants' warps can read.  Every CTA of the cluster holds
+        // the sum over its own part of K; those warps lay it out in the CTA's idle stage ring as
+        // [row][column] FP32.
+        // The other CTAs send theirs into the first CTA's ring with one bulk copy per warp, once the
         // first CTA says its ring is idle too (its own MMAs have completed).  There all four
         // epilogue warps add the parts in a fixed order (own, then by CTA rank), so the result
         // does not depend on timing, apply the epilogue and store eight columns per thread.
         const int rows = p.split_rows;
         float* mine = reinterpret_cast<float*>(smem) +
                       (split_rank == 0 ? (split_size - 1u) * (partial_bytes / 4u) : 0u);
-        if (quad == 0) {
-          if (split_rank == 0 && lane == 0)
-            for (uint32_t r = 1; r < split_size; ++r) mbar_arrive_cluster(map_to_peer(go_bar, r));
+        const bool stages = quad * 32 < rows;   // this warp's TMEM lanes hold output rows
+        if (split_rank == 0 && quad == 0 && lane == 0)
+          for (uint32_t r = 1; r < split_size; ++r) mbar_arrive_cluster(map_to_peer(go_bar, r));
+        if (stages) {
 #pragma unroll 1
           for (int c0 = 0; c0 < kBN; c0 += 32) {
             uint32_t v[32];
             tmem_ld_32x32b_x32(t_row + c0, v);
             tmem_ld_wait();
-            if (lane < rows) {
-              float4* dst = reinterpret_cast<float4*>(mine + lane * kSplitPitch + c0);
+            if (quad * 32 + lane < rows) {
+              float4* dst = reinterpret_cast<float4*>(mine + (quad * 32 + lane) * kSplitPitch + c0);
 #pragma unroll
               for (int q = 0; q < 8; ++q)
                 dst[q] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
@@ -507,15 +510,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           }
         }
         if (split_rank != 0) {
-          if (quad == 0) {
+          if (stages) {
+            // each warp sends the rows it laid out (a contiguous slab of the part)
             fence_async_smem();
             __syncwarp();
             if (!mbar_wait_cluster(go_bar, 0, 0x302)) { ok = false; break; }
             if (lane == 0) {
+              const uint32_t slab_rows = uint32_t(min(32, rows - quad * 32));
+              const uint32_t slab = uint32_t(quad) * 32u * kSplitPitch * 4u;
               asm volatile(
                   "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                  ::"r"(map_to_peer(smem_base + (split_rank - 1u) * partial_bytes, 0)), "r"(smem_base),
-                    "r"(partial_bytes), "r"(map_to_peer(partial_bar, 0))
+                  ::"r"(map_to_peer(smem_base + (split_rank - 1u) * partial_bytes + slab, 0)), "r"(smem_base + slab),
+                    "r"(slab_rows * kSplitPitch * 4u), "r"(map_to_peer(partial_bar, 0))
                   : "memory");
             }
           }
@@ -911,7 +917,8 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
       return rc;
     }
   } else {
-    if ((rc = make_tensor_map_2d(&map_a, g.a, 2, g.k, g.m, g.lda * 2, kBK, kSplit ? kSplitRowsA : kBM, true))) return rc;
+    if ((rc = make_tensor_map_2d(&map_a, g.a, 2, g.k, g.m, g.lda * 2, kBK, kSplit ? (g.m <= 32 ? 32 : 64) : kBM, true)))
+      return rc;
     if ((rc = make_tensor_map_2d(&map_b, g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK, true))) return rc;
     if ((rc = make_tensor_map_2d(&map_b2, kGated ? g.b2 : g.b, 2, g.n, g.k, g.ldb * 2, 64, kBK,
                                  true)))
@@ -938,14 +945,15 @@ int launch_gemm(const trinity_sm100_gemm& g, int sm_count, cudaStream_t stream, 
   p.stride_bias = kBatched ? batch->stride_bias : 0;
   p.num_kb = int((g.k + kBK - 1) / kBK);
   p.flag_tiles = (p.tiles_m + 1) / 2 * 2 * p.tiles_n;
-  p.split_rows = g.m <= 16 ? 16 : 32;
+  p.split_rows = g.m <= 16 ? 16 : g.m <= 32 ? 32 : 64;
+  p.split_a_rows = g.m <= 32 ? 32 : 64;
   p.out = g.out;
   p.ldo = g.ldo;
   GemmPeers peers = {};
   if (fused) peers = *fused;
   if constexpr (kSplit) {
     // one cluster of `split` CTAs per column tile, each CTA a part of K
-    if (p.tiles_m != 1 || g.m > 32 || split < 2 || split > 8 || p.num_kb < split ||
+    if (p.tiles_m != 1 || g.m > kSplitRowsMax || split < 2 || split > 8 || p.num_kb < split ||
         static_cast<size_t>(split) * p.split_rows * kSplitPitch * 4 > static_cast<size_t>(kStages) * stage_bytes<kBN>())
       return fail(TRINITY_SM100_E_INVALID, "gemm (split form): %d rows, %d K blocks, %d parts", int(g.m), p.num_kb, split);
     KernelLaunch launch(dim3(p.num_tiles * split), dim3(kGemmThreads), kSmem, stream, unsigned(split));
@@ -1081,14 +1089,15 @@ extern "C" int trinity_sm100_gemm_bf16(const trinity_sm100_gemm* args, void* str
   // a weight stream.  An MMA with both operands in shared memory takes 128 cycles or more
   // whatever its width (measured: 128 at 256 columns, 165 at 64), so only tiles of 256
   // accumulator columns, 8 KB of weights per MMA, let an SM take in weights faster than its
-  // share of the memory bandwidth.  With fewer such tiles than half the SMs and at most 32 rows,
-  // the CTAs of a cluster share a tile and each walks a part of K (2, 4 or 8 parts, while every
-  // part keeps at least four K blocks and the parts' partial sums fit the stage ring).
+  // share of the memory bandwidth.  With fewer such tiles than half the SMs and at most 64 rows,
+  // the CTAs of a cluster share a tile and each walks a part of K (up to 8 parts for 16 rows, 4
+  // for 32, 2 for 64, while every part keeps at least four K blocks: the parts' partial sums
+  // must fit the stage ring).
   const long long wide_tiles = row_tiles * ((g.n + (gated ? 127 : 255)) / (gated ? 128 : 256));
   int split = 1;
-  if (row_tiles == 1 && g.m <= 32) {
+  if (row_tiles == 1 && g.m <= kSplitRowsMax) {
     const long long k_blocks = (g.k + kBK - 1) / kBK;
-    while (split < (g.m <= 16 ? 8 : 4) && wide_tiles * split * 2 <= sm_count && k_blocks >= split * 2 * 4) split *= 2;
+    while (split < (g.m <= 16 ? 8 : g.m <= 32 ? 4 : 2) && wide_tiles * split * 2 <= sm_count && k_blocks >= split * 2 * 4) split *= 2;
   }
   if (gated) {
     if (split > 1)
