@@ -11,8 +11,9 @@
 //             buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps tile i+1
 //   warps 2-5 epilogue: tcgen05.ld 32 columns at a time, bias / activation in FP32, one
 //             rounding to the output type, 128B-swizzled staging and a TMA store per warp
-//   warps 6-9 only in the row-parallel form with the cross-GPU sum (320 threads): reducers that
+//   warps 6-9 only in the row-parallel form with the cross-GPU sum (352 threads): reducers that
 //             add the ranks' partial tiles over NVLink peer memory while the MMAs go on
+//   warp 10   (same form) tells the other GPUs' reducers which partial tiles are complete
 //
 //
 // Large problems run on CTA pairs (a cluster of two CTAs, tcgen05 cta_group::2): a pair owns a
@@ -42,7 +43,7 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;        // TMA producer, MMA issuer, four epilogue warps
-constexpr int kGemmFusedThreads = 320;   // ... plus four warps that do the cross-GPU reduction
+constexpr int kGemmFusedThreads = 352;   // ... plus four warps that do the cross-GPU reduction and one that signals
 constexpr int kGroupM = 16;           // tile rasterisation: 16 row blocks share B columns in L2
 constexpr int kStageBytesA = kBM * kBK * 2;
 constexpr int kSplitRowsMax = 64;        // the split form serves up to this many output rows
@@ -765,7 +766,35 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     if (lane == 0) tma_store_wait_all();
   }
-  if (kFused && warp >= 6) {
+  if (kFused && warp == 10) {
+    // ------------------------------------------------------------ signalling warp (fused all-reduce)
+    // Lane r tells rank r's reducer warps (this rank's own included) that this rank's partial of a
+    // tile is complete in memory, as soon as the epilogue warps' stores of the tile have landed.
+    // A warp of its own: the system-scope release of the flag store waits for the storing
+    // thread's earlier writes, and a reducer thread has 28 pushes across NVLink in flight per tile,
+    // which put a second round trip into every tile's chain while the reducers sent the flags.
+    // The give-up case is caught by the reducers' flag wait: nobody will have flagged the tile.
+    if (lane < peers.world) {
+      uint32_t local_tile = 0;
+      bool landed = true;
+      for (int unit = first_unit; unit < num_units && landed; unit += unit_stride, ++local_tile) {
+        int m_blk, n_blk, tile;
+        locate_tile<kPair>(p, unit, rank, m_blk, n_blk, tile);
+        const uint32_t target = 4u * (local_tile + 1u);
+        const long long start = clock64();
+        landed = false;
+        for (;;) {
+          uint32_t seen;
+          asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(stored_count) : "memory");
+          if (static_cast<int32_t>(seen - target) >= 0) { landed = true; break; }
+          if (clock64() - start > wait_budget()) { report_timeout(0x803); break; }
+          __nanosleep(100);
+        }
+        if (landed)
+          flag_store(peers.flags[lane] + static_cast<long long>(tile) * peers.world + peers.rank, peers.epoch);
+      }
+    }
+  } else if (kFused && warp >= 6) {
     // ------------------------------------------------------------ reducer warps (fused all-reduce)
     // They follow the CTA's own tile sequence: the same CTA index on every rank works on the same
     // tile at about the same time, so the partials of a tile arrive together.
@@ -775,23 +804,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     for (int unit = first_unit; unit < num_units && ok; unit += unit_stride, ++local_tile) {
       int m_blk, n_blk, tile;
       locate_tile<kPair>(p, unit, rank, m_blk, n_blk, tile);
-      if (rtid < peers.world) {
-        // This rank's partial of the tile is complete in memory (the epilogue warps' stores have
-        // landed) -> tell every rank's reducer warps, this CTA's own included.  The give-up case
-        // is caught by the flag wait that follows: nobody will have flagged the tile.
-        const uint32_t target = 4u * (local_tile + 1u);
-        const long long start = clock64();
-        bool landed = false;
-        for (;;) {
-          uint32_t seen;
-          asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(stored_count) : "memory");
-          if (static_cast<int32_t>(seen - target) >= 0) { landed = true; break; }
-          if (clock64() - start > wait_budget()) { report_timeout(0x803); break; }
-          __nanosleep(100);
-        }
-        if (landed)
-          flag_store(peers.flags[rtid] + static_cast<long long>(tile) * peers.world + peers.rank, peers.epoch);
-      }
       ok = reduce_owned_tile<kBN>(p, peers, tile, m_blk * kBM, n_blk * kBN, rtid, 2);
     }
     if (blockIdx.x == 0 && rtid == 0) g_fused_stamps[3] = global_ns();
