@@ -276,7 +276,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   volatile uint32_t* tmem_holder =
       reinterpret_cast<volatile uint32_t*>(staging + kStagingBytes + 8 * (2 * kStages + 4));
   // fused form: counts epilogue warps whose stores of a tile have landed (four per tile); a
-  // counter and not an mbarrier because the epilogue may run several tiles ahead of the reducers
+  // counter and not an mbarrier because the epilogue may run several tiles ahead of its reader
   const uint32_t stored_count = bar_base + 8u * (2 * kStages + 4) + 8u;
   // split form: partial_bar (first CTA) counts the bytes of the other CTAs' partial sums; go_bar
   // (other CTAs) is the first CTA's word that its stage ring is free to receive them
@@ -757,7 +757,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) {
           // Once this warp's part of the partial tile has landed in memory the warp is free for
           // the next tile; telling the other GPUs (a system-scope release, which waits for
-          // writes in flight) is left to the reducer warps, which wait for this tile anyway.
+          // writes in flight) is left to the signalling warp.
           tma_store_wait_all();
           asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(stored_count) : "memory");
         }
