@@ -912,7 +912,7 @@ struct Emitter {
     l.code = c.str();
     l.operations = {a.op, (*body)[1].operation};
     l.shared_memory_bytes = 230656;
-    l.block_threads = 320;
+    l.block_threads = 352;   // producer, issuer, four epilogue, four reducer warps, one signalling warp
     launches.push_back(std::move(l));
     return true;
   }
