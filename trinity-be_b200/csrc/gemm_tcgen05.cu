@@ -188,7 +188,7 @@ __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const Gem
   m0 += peers.rank * slice_rows;
 #pragma unroll 1
   for (int base = 0; base < slice_rows * kVecPerRow; base += 128 * kBatch) {
-    long long v[kBatch];
+    uint32_t v[kBatch];   // vector index in every rank's buffer (the launcher keeps it below 2^32)
     bool live[kBatch];
     uint4 part[kBatch][kGemmMaxWorld];
 #pragma unroll
@@ -197,7 +197,7 @@ __device__ __forceinline__ bool reduce_owned_tile(const GemmParams& p, const Gem
       const int row = m0 + idx / kVecPerRow;
       const int col = n0 + (idx % kVecPerRow) * 8;
       live[u] = idx < slice_rows * kVecPerRow && row < p.m && col < p.n;
-      v[u] = static_cast<long long>(row) * peers.ld_vectors + (col >> 3);
+      v[u] = static_cast<uint32_t>(static_cast<long long>(row) * peers.ld_vectors + (col >> 3));
     }
     // (register arrays are indexed statically on purpose: a dynamically indexed destination would
     // consume each load at once and serialise the round trips)
@@ -1305,6 +1305,10 @@ extern "C" int trinity_sm100_gemm_allreduce_bf16(const trinity_sm100_gemm* args,
   peers.epoch = r.epoch;
   peers.epoch_counter = g_epoch_counter_for_next_launch;
   peers.ld_vectors = g.ldo / 8;
+  // the reducer threads index the buffers in 16-byte vectors with 32 bits
+  if (((g.m + kBM - 1) / kBM * kBM) * (g.ldo / 8) >= (1ll << 32))
+    return fail(TRINITY_SM100_E_UNSUPPORTED, "gemm_allreduce: output of %lld x %lld elements is too large", (long long)g.m,
+                (long long)g.ldo);
   int sm_count = 0;
   if (int rc = require_sm100(&sm_count)) return rc;
   // every CTA of the persistent grid is resident (one per SM), which the flag waits rely on
